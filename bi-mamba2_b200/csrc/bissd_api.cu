@@ -1,0 +1,356 @@
+// C ABI of libbissd (declared in include/bissd.h): argument validation, workspace layout, kernel sequencing.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "simt_kernels.cuh"
+
+namespace bissd {
+
+static thread_local char g_cuda_err[256] = "";
+
+static int note_cuda(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return BISSD_OK;
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+    return BISSD_ERR_LAUNCH;
+}
+
+// ---- tracing: optional CUDA-event brackets around every kernel launch, and a launch counter -------------
+struct TraceRec {
+    const char *name;
+    cudaEvent_t e0, e1;
+};
+static std::mutex g_trace_mu;
+static std::vector<TraceRec> g_trace;
+static std::atomic<int> g_trace_on{0};
+static std::atomic<unsigned long long> g_launches{0};
+
+struct TraceScope {
+    const char *name;
+    cudaStream_t s;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    TraceScope(const char *n, cudaStream_t st) : name(n), s(st) {
+        if (g_trace_on.load(std::memory_order_relaxed)) {
+            if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) cudaEventRecord(e0, s);
+            else e0 = e1 = nullptr;
+        }
+    }
+    void end() {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (e0 && e1) {
+            cudaEventRecord(e1, s);
+            std::lock_guard<std::mutex> lk(g_trace_mu);
+            g_trace.push_back(TraceRec{name, e0, e1});
+        }
+    }
+};
+
+// Launch `...` (a full kernel<<<>>>() expression) on stream `s`, count it, bracket it with events when tracing.
+#define BISSD_LAUNCH(name, ...)                                   \
+    do {                                                          \
+        TraceScope ts_(name, s);                                  \
+        __VA_ARGS__;                                              \
+        ts_.end();                                                \
+        int rc_ = note_cuda(cudaGetLastError(), name);            \
+        if (rc_ != BISSD_OK) return rc_;                          \
+    } while (0)
+
+static int make_dims(const bissd_problem &p, Dims *d) {
+    if (p.batch <= 0 || p.seqlen <= 0 || p.nheads <= 0 || p.headdim <= 0 || p.ngroups <= 0 || p.dstate <= 0)
+        return BISSD_ERR_SHAPE;
+    if (p.nheads % p.ngroups != 0) return BISSD_ERR_SHAPE;
+    // the reference requires chunk_size >= 32 (src/ssd/bi/ssd_combined.py:306); 256 is this library's ceiling
+    if (p.chunk_size < 32 || p.chunk_size > 256) return BISSD_ERR_SHAPE;
+    if (p.x_dtype < BISSD_F32 || p.x_dtype > BISSD_F16 || p.dt_dtype < BISSD_F32 || p.dt_dtype > BISSD_F16)
+        return BISSD_ERR_DTYPE;
+    d->b = p.batch; d->L = p.seqlen; d->H = p.nheads; d->P = p.headdim; d->G = p.ngroups; d->N = p.dstate;
+    d->Q = p.chunk_size; d->nc = ceil_div(p.seqlen, p.chunk_size); d->R = p.nheads / p.ngroups;
+    d->has_D = p.has_D; d->D_hdim = p.D_has_hdim; d->has_z = p.has_z; d->has_bias = p.has_dt_bias;
+    d->softplus = p.dt_softplus; d->dt_min = p.dt_min; d->dt_max = p.dt_max;
+    return BISSD_OK;
+}
+
+static inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Workspace carving.  All regions are fp32.
+struct FwdWs {
+    size_t loc, cb, total;
+};
+struct BwdWs {
+    size_t cb, gloc, E, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    int nblk, nlt;
+};
+
+static FwdWs fwd_layout(const Dims &d) {
+    FwdWs w;
+    size_t o = 0;
+    const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
+    w.loc = o; o = align256(o + 2 * st * 4);
+    w.cb = o; o = align256(o + (size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
+    w.total = o;
+    return w;
+}
+
+static BwdWs bwd_layout(const Dims &d) {
+    BwdWs w;
+    size_t o = 0;
+    const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
+    const size_t hq = (size_t)d.b * d.H * d.nc * d.Q;
+    w.nblk = ceil_div(d.P * d.N, simt::TB);
+    w.nlt = ceil_div(d.Q, simt::TILE);
+    auto take = [&](size_t bytes) { size_t at = o; o = align256(o + bytes); return at; };
+    w.cb = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
+    w.gloc = take(2 * st * 4);
+    w.E = take(2 * st * 4);
+    w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
+    w.ddt_out = take(hq * 4); w.nf = take(hq * 4); w.nb = take(hq * 4); w.pf = take(hq * 4); w.pb = take(hq * 4);
+    w.da_f = take(hq * 4); w.da_b = take(hq * 4);
+    w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
+    w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
+    w.dCB = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
+    w.dDpart = take((size_t)d.b * d.nc * d.H * w.nlt * d.P * 4);
+    w.dApart = take((size_t)d.b * d.nc * d.H * 4);
+    w.dbiaspart = take((size_t)d.b * d.nc * d.H * 4);
+    w.total = o;
+    return w;
+}
+
+static View view_of(const bissd_tensor &t) { return View{t.ptr, t.stride_batch, t.stride_seq, t.stride_head}; }
+static MutView mview_of(const bissd_tensor &t) { return MutView{t.ptr, t.stride_batch, t.stride_seq, t.stride_head}; }
+
+template <class K> static int allow_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return BISSD_OK;
+    return note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
+                     "cudaFuncSetAttribute");
+}
+
+template <class T>
+static int forward_simt(const bissd_fwd_args &a, const Dims &d, char *ws, cudaStream_t s) {
+    using namespace simt;
+    const FwdWs w = fwd_layout(d);
+    float *loc = reinterpret_cast<float *>(ws + w.loc);
+    float *CB = reinterpret_cast<float *>(ws + w.cb);
+    const View x = view_of(a.x), Bm = view_of(a.B), Cm = view_of(a.C), z = view_of(a.z);
+    const int bch = d.b * d.nc * d.H;
+    if (a.phases & BISSD_PHASE_LOCAL) {
+        BISSD_LAUNCH("cumsum_fwd", cumsum_fwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), TB, 8 * d.Q * sizeof(float), s>>>(
+            d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
+            a.cs_f, a.cs_b));
+        BISSD_LAUNCH("chunk_state", chunk_state<T><<<dim3(bch, ceil_div(d.P, TILE), ceil_div(2 * d.N, TILE)), TB, 2 * d.Q * sizeof(float), s>>>(
+            d, x, Bm, a.dt_out, a.cs_f, a.cs_b, loc));
+    }
+    // the recurrence runs in both phases: from zero (or init_*) in LOCAL, again with init_* in FINISH
+    const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.init_f || a.init_b);
+    if (need_pass) {
+        BISSD_LAUNCH("state_passing_fwd", state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, TB), 2), TB, 0, s>>>(
+            d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
+    }
+    if (a.phases & BISSD_PHASE_FINISH) {
+        BISSD_LAUNCH("bmm_cb", bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, TILE), ceil_div(d.Q, TILE)), TB, 0, s>>>(d, Cm, Bm, CB));
+        BISSD_LAUNCH("chunk_scan", chunk_scan<T><<<dim3(bch, ceil_div(d.Q, TILE), ceil_div(d.P, TILE)), TB, 3 * d.Q * sizeof(float), s>>>(
+            d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x)));
+    }
+    return BISSD_OK;
+}
+
+template <class T>
+static int backward_simt(const bissd_bwd_args &a, const Dims &d, char *ws, cudaStream_t s) {
+    using namespace simt;
+    const BwdWs w = bwd_layout(d);
+    auto F = [&](size_t off) { return reinterpret_cast<float *>(ws + off); };
+    const View x = view_of(a.x), Bm = view_of(a.B), Cm = view_of(a.C), z = view_of(a.z), dout = view_of(a.dout),
+               out_x = view_of(a.out_x);
+    const int bch = d.b * d.nc * d.H;
+    const size_t q3 = 3 * d.Q * sizeof(float);
+    if (a.phases & BISSD_PHASE_LOCAL) {
+        BISSD_LAUNCH("dstates", dstates<T><<<dim3(bch, ceil_div(d.P, TILE), ceil_div(2 * d.N, TILE)), TB, 2 * d.Q * sizeof(float), s>>>(
+            d, dout, z, Cm, a.cs_f, a.cs_b, F(w.gloc)));
+    }
+    const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.dfinal_f || a.dfinal_b);
+    if (need_pass) {
+        BISSD_LAUNCH("state_passing_bwd", state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), TB, 0, s>>>(d, F(w.gloc), a.states_f, a.states_b, a.cs_f,
+                                                                      a.cs_b, a.dfinal_f, a.dfinal_b, F(w.E),
+                                                                      F(w.dTpart), a.dinit_f, a.dinit_b));
+    }
+    if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
+    BISSD_LAUNCH("bmm_cb", bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, TILE), ceil_div(d.Q, TILE)), TB, 0, s>>>(d, Cm, Bm, F(w.cb)));
+    BISSD_LAUNCH("dx_kernel", dx_kernel<T><<<dim3(bch, w.nlt), TB, q3, s>>>(d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb),
+                                                  F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart)));
+    BISSD_LAUNCH("dbc_states", dbc_states<T><<<dim3(bch, w.nlt, 2), TB, q3, s>>>(d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E),
+                                                      a.states_f, a.states_b, F(w.dB_part), F(w.dC_part), F(w.nf),
+                                                      F(w.nb), F(w.pf), F(w.pb)));
+    BISSD_LAUNCH("dcb_kernel", dcb_kernel<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), TB, 0, s>>>(d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB)));
+    {
+        const size_t smem = (3 * d.Q + 2 * TILE * (d.Q + 1)) * sizeof(float);
+        int rc = allow_smem(intra_decay_grad<T>, smem);
+        if (rc != BISSD_OK) return rc;
+        BISSD_LAUNCH("intra_decay_grad", intra_decay_grad<T><<<bch, TB, smem, s>>>(d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b)));
+    }
+    BISSD_LAUNCH("bmm_bwd", bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, TILE)), TB, 0, s>>>(d, Bm, Cm, F(w.dCB), F(w.dB_part),
+                                                                                    F(w.dC_part), a.dB, a.dC));
+    BISSD_LAUNCH("cumsum_bwd", cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), TB, 8 * d.Q * sizeof(float), s>>>(
+        d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
+        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), w.nblk, a.ddt,
+        F(w.dApart), F(w.dbiaspart)));
+    BISSD_LAUNCH("final_reduce", final_reduce<<<d.H, TB, 0, s>>>(d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, w.nlt, a.dA,
+                                    d.has_bias ? a.ddt_bias : nullptr, d.has_D ? a.dD : nullptr));
+    return BISSD_OK;
+}
+
+static int check_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return BISSD_ERR_LAUNCH;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return BISSD_ERR_LAUNCH;
+    return major == 10 ? BISSD_OK : BISSD_ERR_ARCH;
+}
+
+}  // namespace bissd
+
+using namespace bissd;
+
+extern "C" {
+
+int bissd_abi_version(void) { return BISSD_ABI_VERSION; }
+
+const char *bissd_strerror(int status) {
+    switch (status) {
+        case BISSD_OK: return "ok";
+        case BISSD_ERR_NULL: return "a required pointer is NULL";
+        case BISSD_ERR_SHAPE: return "inconsistent or unsupported sizes (need nheads % ngroups == 0, 32 <= chunk_size <= 256)";
+        case BISSD_ERR_DTYPE: return "unsupported dtype";
+        case BISSD_ERR_ALIGN: return "pointer or stride not sufficiently aligned";
+        case BISSD_ERR_WORKSPACE: return "workspace too small or misaligned";
+        case BISSD_ERR_LAUNCH: return "CUDA launch or API call failed";
+        case BISSD_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+        case BISSD_ERR_PHASE: return "invalid phase mask";
+        default: return "unknown status";
+    }
+}
+
+const char *bissd_last_cuda_error(void) { return g_cuda_err; }
+
+int bissd_workspace_bytes(const bissd_problem *p, size_t *fwd_bytes, size_t *bwd_bytes) {
+    if (!p) return BISSD_ERR_NULL;
+    Dims d;
+    int rc = make_dims(*p, &d);
+    if (rc != BISSD_OK) return rc;
+    if (fwd_bytes) *fwd_bytes = fwd_layout(d).total;
+    if (bwd_bytes) *bwd_bytes = bwd_layout(d).total;
+    return BISSD_OK;
+}
+
+unsigned long long bissd_launch_count(void) { return g_launches.load(); }
+
+int bissd_trace_enable(int on) {
+    std::lock_guard<std::mutex> lk(g_trace_mu);
+    for (auto &r : g_trace) {
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    g_trace.clear();
+    g_trace_on.store(on ? 1 : 0);
+    return BISSD_OK;
+}
+
+int bissd_trace_read(char *names, size_t names_cap, float *total_ms, int *launches, int cap, int *count) {
+    if (!names || !total_ms || !launches || !count) return BISSD_ERR_NULL;
+    std::lock_guard<std::mutex> lk(g_trace_mu);
+    std::vector<const char *> keys;
+    std::vector<float> ms;
+    std::vector<int> cnt;
+    for (auto &r : g_trace) {
+        if (cudaEventSynchronize(r.e1) != cudaSuccess) return note_cuda(cudaGetLastError(), "trace sync");
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, r.e0, r.e1) != cudaSuccess) return note_cuda(cudaGetLastError(), "trace elapsed");
+        size_t k = 0;
+        for (; k < keys.size(); ++k)
+            if (strcmp(keys[k], r.name) == 0) break;
+        if (k == keys.size()) { keys.push_back(r.name); ms.push_back(0.f); cnt.push_back(0); }
+        ms[k] += t;
+        cnt[k] += 1;
+    }
+    size_t used = 0;
+    int n = 0;
+    names[0] = 0;
+    for (size_t k = 0; k < keys.size() && n < cap; ++k) {
+        const size_t len = strlen(keys[k]);
+        if (used + len + 2 > names_cap) break;
+        memcpy(names + used, keys[k], len);
+        used += len;
+        names[used++] = ';';
+        names[used] = 0;
+        total_ms[n] = ms[k];
+        launches[n] = cnt[k];
+        ++n;
+    }
+    *count = n;
+    return BISSD_OK;
+}
+
+const char *bissd_kernel_path(const bissd_problem *p) {
+    (void)p;
+    return "simt";
+}
+
+int bissd_forward(const bissd_fwd_args *a, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!a) return BISSD_ERR_NULL;
+    Dims d;
+    int rc = make_dims(a->p, &d);
+    if (rc != BISSD_OK) return rc;
+    if (a->phases < 1 || a->phases > BISSD_PHASE_ALL) return BISSD_ERR_PHASE;
+    if (!a->x.ptr || !a->B.ptr || !a->C.ptr || !a->dt.ptr || !a->A || !a->dt_out || !a->cs_f || !a->cs_b ||
+        !a->states_f || !a->states_b)
+        return BISSD_ERR_NULL;
+    if ((a->phases & BISSD_PHASE_FINISH) && !a->out.ptr) return BISSD_ERR_NULL;
+    if (a->p.has_z && (!a->z.ptr || ((a->phases & BISSD_PHASE_FINISH) && !a->out_x.ptr))) return BISSD_ERR_NULL;
+    if (a->p.has_D && !a->D) return BISSD_ERR_NULL;
+    if (a->p.has_dt_bias && !a->dt_bias) return BISSD_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < fwd_layout(d).total)
+        return BISSD_ERR_WORKSPACE;
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    switch (a->p.x_dtype) {
+        case BISSD_F32: return forward_simt<float>(*a, d, ws, s);
+        case BISSD_BF16: return forward_simt<__nv_bfloat16>(*a, d, ws, s);
+        default: return forward_simt<__half>(*a, d, ws, s);
+    }
+}
+
+int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!a) return BISSD_ERR_NULL;
+    Dims d;
+    int rc = make_dims(a->p, &d);
+    if (rc != BISSD_OK) return rc;
+    if (a->phases < 1 || a->phases > BISSD_PHASE_ALL) return BISSD_ERR_PHASE;
+    if (!a->x.ptr || !a->B.ptr || !a->C.ptr || !a->dt.ptr || !a->dout.ptr || !a->A || !a->dt_out || !a->cs_f ||
+        !a->cs_b || !a->states_f || !a->states_b)
+        return BISSD_ERR_NULL;
+    if (a->phases & BISSD_PHASE_FINISH) {
+        if (!a->dx || !a->dB || !a->dC || !a->ddt || !a->dA) return BISSD_ERR_NULL;
+        if (a->p.has_z && (!a->dz || !a->out_x.ptr)) return BISSD_ERR_NULL;
+        if (a->p.has_D && !a->dD) return BISSD_ERR_NULL;
+        if (a->p.has_dt_bias && !a->ddt_bias) return BISSD_ERR_NULL;
+    }
+    if (a->p.has_z && !a->z.ptr) return BISSD_ERR_NULL;
+    if (a->p.has_D && !a->D) return BISSD_ERR_NULL;
+    if (a->p.has_dt_bias && !a->dt_bias) return BISSD_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < bwd_layout(d).total)
+        return BISSD_ERR_WORKSPACE;
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    switch (a->p.x_dtype) {
+        case BISSD_F32: return backward_simt<float>(*a, d, ws, s);
+        case BISSD_BF16: return backward_simt<__nv_bfloat16>(*a, d, ws, s);
+        default: return backward_simt<__half>(*a, d, ws, s);
+    }
+}
+
+}  // extern "C"

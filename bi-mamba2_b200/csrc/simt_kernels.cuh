@@ -1,0 +1,960 @@
+// General-shape CUDA-core kernels for every phase of the bidirectional SSD chunk scan.
+//
+// These accept any headdim / dstate / chunk_size (<= 256) / dtype, ragged sequence tails, and compute all
+// products in fp32 - they are the path for fp32 inputs and for shapes the tcgen05 kernels do not cover, and
+// the on-device cross-check for those kernels.  Every contraction goes through one shared-memory tiled
+// 64x64 block GEMM whose operands are produced by functors, so decay factors, masks and the two scan
+// directions are folded into the operand loads (the K index simply runs over [forward | reverse | intra]).
+//
+// Notation: Delta = dt_out, a = Delta*A, cs_f[l] = sum_{j<=l} a_j, cs_b[l] = sum_{j>=l} a_j within a chunk,
+// T = cs_f[Q-1] = cs_b[0].
+#pragma once
+#include "common.cuh"
+
+namespace bissd {
+namespace simt {
+
+constexpr int TB = 256;      // threads per block in every kernel of this file
+constexpr int TILE = 64;     // block GEMM tile edge
+constexpr int TK = 16;       // block GEMM K step
+constexpr int LDS = TILE + 4;
+
+struct GemmSmem {
+    float a[TK * LDS];
+    float b[TK * LDS];
+};
+
+// acc[i][j] += sum_k A(ty*4+i, k) * B(k, tx*4+j) over k in [0,K).  fa(m,k), fb(k,n) return 0 out of range.
+// AKF / BKF: whether consecutive threads walk k (true) or m/n (false) when filling - pick what coalesces.
+template <bool AKF, bool BKF, class FA, class FB>
+__device__ __forceinline__ void block_gemm(float (&acc)[4][4], int K, FA fa, FB fb, GemmSmem &s) {
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+        for (int i = tid; i < TILE * TK; i += TB) {
+            int m, k;
+            if (AKF) { k = i & (TK - 1); m = i >> 4; } else { m = i & (TILE - 1); k = i >> 6; }
+            s.a[k * LDS + m] = (k0 + k < K) ? fa(m, k0 + k) : 0.f;
+        }
+#pragma unroll
+        for (int i = tid; i < TILE * TK; i += TB) {
+            int n, k;
+            if (BKF) { k = i & (TK - 1); n = i >> 4; } else { n = i & (TILE - 1); k = i >> 6; }
+            s.b[k * LDS + n] = (k0 + k < K) ? fb(k0 + k, n) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = s.a[kk * LDS + ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bv[j] = s.b[kk * LDS + tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ void zero_acc(float (&acc)[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+}
+
+// sum over the 16 consecutive lanes that share ty (one tile row group)
+__device__ __forceinline__ float row_reduce16(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_incl_scan(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Discretisation + both cumulative sums.  One warp per (batch, chunk, head).
+// Takes over _chunk_cumsum_fwd_kernel (src/ssd/bi/ssd_chunk_state.py:34-91).
+// dynamic smem: 8 * Q floats.
+__global__ void __launch_bounds__(TB) cumsum_fwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
+                                                 long long dsh, const float *A, const float *dt_bias, float *dt_out,
+                                                 float *cs_f, float *cs_b) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
+    const int h = blockIdx.y * 8 + warp;
+    if (h >= d.H) return;
+    float *sa = sm + warp * d.Q;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const float Ah = A[h];
+    const float bias = d.has_bias ? dt_bias[h] : 0.f;
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    float carry = 0.f;
+    for (int l0 = 0; l0 < d.Q; l0 += 32) {
+        const int l = l0 + lane;
+        float v = 0.f;
+        if (l < lim) {
+            v = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
+            if (d.softplus) v = softplus_ref(v);
+            v = fminf(fmaxf(v, d.dt_min), d.dt_max);
+        }
+        const float a = v * Ah;
+        const float inc = warp_incl_scan(a, lane) + carry;
+        carry = __shfl_sync(0xffffffffu, inc, 31);
+        if (l < d.Q) {
+            dt_out[base + l] = v;
+            cs_f[base + l] = inc;
+            sa[l] = a;
+        }
+    }
+    __syncwarp();
+    carry = 0.f;
+    const int ntile = ceil_div(d.Q, 32);
+    for (int t = ntile - 1; t >= 0; --t) {
+        const int l = t * 32 + (31 - lane);            // lane 0 holds the last element of the tile
+        const float a = (l < d.Q) ? sa[l] : 0.f;
+        const float inc = warp_incl_scan(a, lane) + carry;
+        carry = __shfl_sync(0xffffffffu, inc, 31);
+        if (l < d.Q) cs_b[base + l] = inc;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Local chunk states for both directions: loc[dir][b,c,h,p,n] = sum_l x[l,p] B[l,n] Delta[l] e^{T - cs_dir[l]}.
+// Takes over _chunk_state_fwd_kernel (src/ssd/bi/ssd_chunk_state.py:187-263).
+// grid (b*nc*H, ceil(P/64), ceil(2N/64)); dynamic smem 2*Q floats.
+template <class T>
+__global__ void __launch_bounds__(TB) chunk_state(Dims d, View x, View Bm, const float *dt_out, const float *cs_f,
+                                                  const float *cs_b, float *loc) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    float *wf = sm, *wb = sm + d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    const float Tf = cs_f[base + d.Q - 1], Tb = cs_b[base];
+    for (int l = threadIdx.x; l < d.Q; l += TB) {
+        const float dl = dt_out[base + l];
+        wf[l] = expf(Tf - cs_f[base + l]) * dl;
+        wb[l] = expf(Tb - cs_b[base + l]) * dl;
+    }
+    __syncthreads();
+    const int p0 = blockIdx.y * TILE, n0 = blockIdx.z * TILE;
+    float acc[4][4];
+    zero_acc(acc);
+    auto fa = [&](int m, int k) -> float {
+        const int p = p0 + m;
+        return (p < d.P && k < lim) ? ldv<T>(x, b, c * d.Q + k, h, p) : 0.f;
+    };
+    auto fb = [&](int k, int n) -> float {
+        const int nn = n0 + n;
+        if (nn >= 2 * d.N || k >= lim) return 0.f;
+        const int dir = nn >= d.N, ns = nn - dir * d.N;
+        return ldv<T>(Bm, b, c * d.Q + k, g, ns) * (dir ? wb[k] : wf[k]);
+    };
+    block_gemm<false, false>(acc, d.Q, fa, fb, gs);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const long long per_dir = (long long)d.b * d.nc * d.H * d.P * d.N;
+    const long long tile_base = ((long long)(b * d.nc + c) * d.H + h) * d.P * d.N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = p0 + ty * 4 + i;
+        if (p >= d.P) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nn = n0 + tx * 4 + j;
+            if (nn >= 2 * d.N) continue;
+            const int dir = nn >= d.N, ns = nn - dir * d.N;
+            loc[dir * per_dir + tile_base + (long long)p * d.N + ns] = acc[i][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Inter-chunk recurrence, both directions in one launch (blockIdx.z = direction).
+// Forward: S_0 = init_f; S_{c+1} = e^{T_c} S_c + loc_f[c]; states_f[c] = S_c; final_f = S_nc.
+// Reverse: R_{nc-1} = init_b; R_{c-1} = e^{T_c} R_c + loc_b[c]; states_b[c] = R_c; final_b = R_{-1}.
+// Takes over _state_passing_fwd_kernel (src/ssd/bi/ssd_state_passing.py:27-92), called twice by the reference.
+// grid (b*H, ceil(P*N/256), 2)
+template <class T>
+__global__ void __launch_bounds__(TB) state_passing_fwd(Dims d, const float *loc, const float *cs_f, const float *cs_b,
+                                                        const float *init_f, const float *init_b, void *states_f,
+                                                        void *states_b, float *final_f, float *final_b) {
+    const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
+    const int dir = blockIdx.z;
+    const int PN = d.P * d.N;
+    const int e = blockIdx.y * TB + threadIdx.x;
+    if (e >= PN) return;
+    const long long per_dir = (long long)d.b * d.nc * d.H * PN;
+    const float *lp = loc + dir * per_dir;
+    const float *init = dir ? init_b : init_f;
+    void *states = dir ? states_b : states_f;
+    float *fin = dir ? final_b : final_f;
+    float run = init ? init[(long long)(b * d.H + h) * PN + e] : 0.f;
+    for (int i = 0; i < d.nc; ++i) {
+        const int c = dir ? d.nc - 1 - i : i;
+        const long long off = ((long long)(b * d.nc + c) * d.H + h) * PN + e;
+        st<T>(states, off, run);
+        const long long cb = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+        const float dec = expf(dir ? cs_b[cb] : cs_f[cb + d.Q - 1]);
+        run = dec * run + lp[off];
+    }
+    if (fin) fin[(long long)(b * d.H + h) * PN + e] = run;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CB[b,c,g,l,s] = sum_n C[l,n] B[s,n].  Takes over _bmm_chunk_fwd_kernel (src/ssd/bi/ssd_bmm.py:34-91).
+// grid (b*nc*G, ceil(Q/64), ceil(Q/64))
+template <class T>
+__global__ void __launch_bounds__(TB) bmm_cb(Dims d, View Cm, View Bm, float *CB) {
+    __shared__ GemmSmem gs;
+    const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const int l0 = blockIdx.y * TILE, s0 = blockIdx.z * TILE;
+    float acc[4][4];
+    zero_acc(acc);
+    auto fa = [&](int m, int k) -> float { return (l0 + m < lim) ? ldv<T>(Cm, b, c * d.Q + l0 + m, g, k) : 0.f; };
+    auto fb = [&](int k, int n) -> float { return (s0 + n < lim) ? ldv<T>(Bm, b, c * d.Q + s0 + n, g, k) : 0.f; };
+    block_gemm<true, true>(acc, d.N, fa, fb, gs);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float *out = CB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int l = l0 + ty * 4 + i;
+        if (l >= d.Q) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int s = s0 + tx * 4 + j;
+            if (s < d.Q) out[(long long)l * d.Q + s] = acc[i][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Output: y[l,p] = e^{cs_f[l]} C[l].S_f[p] + e^{cs_b[l]} C[l].S_b[p] + sum_s M[l,s] x[s,p] + D x[l,p],
+// M[l,s] = CB[l,s] Delta[s] ([s<=l] e^{cs_f[l]-cs_f[s]} + [s>=l] e^{cs_b[l]-cs_b[s]}); out = y silu(z).
+// Takes over _chunk_scan_fwd_kernel (src/ssd/bi/ssd_chunk_scan.py:42-189).
+// grid (b*nc*H, ceil(Q/64), ceil(P/64)); dynamic smem 3*Q floats.
+template <class T>
+__global__ void __launch_bounds__(TB) chunk_scan(Dims d, View x, View Cm, View z, const float *D, const float *dt_out,
+                                                 const float *cs_f, const float *cs_b, const float *CB,
+                                                 const void *states_f, const void *states_b, MutView out,
+                                                 MutView out_x) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    float *sf = sm, *sb = sm + d.Q, *sd = sm + 2 * d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    for (int l = threadIdx.x; l < d.Q; l += TB) {
+        sf[l] = cs_f[base + l];
+        sb[l] = cs_b[base + l];
+        sd[l] = dt_out[base + l];
+    }
+    __syncthreads();
+    const int l0 = blockIdx.y * TILE, p0 = blockIdx.z * TILE;
+    const float *cb = CB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
+    const long long st_base = ((long long)(b * d.nc + c) * d.H + h) * d.P * d.N;
+    const int N = d.N;
+    float acc[4][4];
+    zero_acc(acc);
+    auto fa = [&](int m, int k) -> float {
+        const int l = l0 + m;
+        if (l >= lim) return 0.f;
+        if (k < N) return ldv<T>(Cm, b, c * d.Q + l, g, k) * expf(sf[l]);
+        if (k < 2 * N) return ldv<T>(Cm, b, c * d.Q + l, g, k - N) * expf(sb[l]);
+        const int s = k - 2 * N;
+        if (s >= lim) return 0.f;
+        float w = 0.f;
+        if (s <= l) w += expf(sf[l] - sf[s]);
+        if (s >= l) w += expf(sb[l] - sb[s]);
+        return cb[(long long)l * d.Q + s] * sd[s] * w;
+    };
+    auto fb = [&](int k, int n) -> float {
+        const int p = p0 + n;
+        if (p >= d.P) return 0.f;
+        if (k < N) return ld<T>(states_f, st_base + (long long)p * N + k);
+        if (k < 2 * N) return ld<T>(states_b, st_base + (long long)p * N + (k - N));
+        const int s = k - 2 * N;
+        return (s < lim) ? ldv<T>(x, b, c * d.Q + s, h, p) : 0.f;
+    };
+    block_gemm<true, false>(acc, 2 * N + d.Q, fa, fb, gs);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int l = l0 + ty * 4 + i;
+        if (l >= lim) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int p = p0 + tx * 4 + j;
+            if (p >= d.P) continue;
+            float y = acc[i][j];
+            if (d.has_D) y += (d.D_hdim ? D[h * d.P + p] : D[h]) * ldv<T>(x, b, c * d.Q + l, h, p);
+            if (d.has_z) {
+                stv<T>(out_x, b, c * d.Q + l, h, p, y);
+                const float zz = ldv<T>(z, b, c * d.Q + l, h, p);
+                y *= zz * sigmoidf_(zz);
+            }
+            stv<T>(out, b, c * d.Q + l, h, p, y);
+        }
+    }
+}
+
+// =========================================================================================================
+// Backward
+// =========================================================================================================
+
+// g = d(out)/d(y): dout, or dout * silu(z) when gated.
+template <class T> __device__ __forceinline__ float gate_grad(const Dims &d, const View &dout, const View &z, int b,
+                                                              int l, int h, int p) {
+    float g = ldv<T>(dout, b, l, h, p);
+    if (d.has_z) {
+        const float zz = ldv<T>(z, b, l, h, p);
+        g *= zz * sigmoidf_(zz);
+    }
+    return g;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Local state gradients: gloc[dir][b,c,h,p,n] = sum_l g[l,p] e^{cs_dir[l]} C[l,n].
+// Takes over _chunk_scan_bwd_dstates_kernel (src/ssd/bi/ssd_chunk_scan.py:457-522).
+// grid (b*nc*H, ceil(P/64), ceil(2N/64)); dynamic smem 2*Q floats.
+template <class T>
+__global__ void __launch_bounds__(TB) dstates(Dims d, View dout, View z, View Cm, const float *cs_f, const float *cs_b,
+                                              float *gloc) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    float *ef = sm, *eb = sm + d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    for (int l = threadIdx.x; l < d.Q; l += TB) {
+        ef[l] = expf(cs_f[base + l]);
+        eb[l] = expf(cs_b[base + l]);
+    }
+    __syncthreads();
+    const int p0 = blockIdx.y * TILE, n0 = blockIdx.z * TILE;
+    float acc[4][4];
+    zero_acc(acc);
+    auto fa = [&](int m, int k) -> float {
+        const int p = p0 + m;
+        return (p < d.P && k < lim) ? gate_grad<T>(d, dout, z, b, c * d.Q + k, h, p) : 0.f;
+    };
+    auto fb = [&](int k, int n) -> float {
+        const int nn = n0 + n;
+        if (nn >= 2 * d.N || k >= lim) return 0.f;
+        const int dir = nn >= d.N, ns = nn - dir * d.N;
+        return ldv<T>(Cm, b, c * d.Q + k, g, ns) * (dir ? eb[k] : ef[k]);
+    };
+    block_gemm<false, false>(acc, d.Q, fa, fb, gs);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const long long per_dir = (long long)d.b * d.nc * d.H * d.P * d.N;
+    const long long tile_base = ((long long)(b * d.nc + c) * d.H + h) * d.P * d.N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = p0 + ty * 4 + i;
+        if (p >= d.P) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nn = n0 + tx * 4 + j;
+            if (nn >= 2 * d.N) continue;
+            const int dir = nn >= d.N, ns = nn - dir * d.N;
+            gloc[dir * per_dir + tile_base + (long long)p * d.N + ns] = acc[i][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// State-passing backward, both directions (blockIdx.z).  Per element of the (P,N) state:
+//   forward dir: run = dfinal_f; for c = nc-1..0: E_f[c] = run; dT_f[c] += e^{T_c} S_f[c] run; run = e^{T_c} run + gloc_f[c]
+//   reverse dir: run = dfinal_b; for c = 0..nc-1: E_b[c] = run; dT_b[c] += e^{T_c} S_b[c] run; run = e^{T_c} run + gloc_b[c]
+// and dinit = run at the end.  E[c] is the gradient w.r.t. the local state of chunk c.
+// Takes over _state_passing_bwd_kernel (src/ssd/bi/ssd_state_passing.py:106-187); the per-block partial sums
+// of dT go to dTpart[dir][b,h,c][blk] and are added in a fixed order later (no atomics).
+// grid (b*H, nblk = ceil(P*N/256), 2)
+template <class T>
+__global__ void __launch_bounds__(TB) state_passing_bwd(Dims d, const float *gloc, const void *states_f,
+                                                        const void *states_b, const float *cs_f, const float *cs_b,
+                                                        const float *dfinal_f, const float *dfinal_b, float *E,
+                                                        float *dTpart, float *dinit_f, float *dinit_b) {
+    __shared__ float red[TB / 32];
+    const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
+    const int dir = blockIdx.z;
+    const int PN = d.P * d.N;
+    const int nblk = gridDim.y;
+    const int e = blockIdx.y * TB + threadIdx.x;
+    const bool on = e < PN;
+    const long long per_dir = (long long)d.b * d.nc * d.H * PN;
+    const float *gp = gloc + dir * per_dir;
+    float *Ep = E + dir * per_dir;
+    const void *states = dir ? states_b : states_f;
+    const float *dfin = dir ? dfinal_b : dfinal_f;
+    float *dinit = dir ? dinit_b : dinit_f;
+    float run = (on && dfin) ? dfin[(long long)(b * d.H + h) * PN + e] : 0.f;
+    for (int i = 0; i < d.nc; ++i) {
+        const int c = dir ? i : d.nc - 1 - i;
+        const long long off = ((long long)(b * d.nc + c) * d.H + h) * PN + e;
+        const long long cb = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+        const float dec = expf(dir ? cs_b[cb] : cs_f[cb + d.Q - 1]);
+        float part = 0.f;
+        if (on) {
+            Ep[off] = run;
+            part = dec * ld<T>(states, off) * run;
+            run = dec * run + gp[off];
+        }
+        part = warp_sum(part);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < TB / 32; ++w) s += red[w];
+            dTpart[((long long)dir * d.b * d.H * d.nc + (long long)(b * d.H + h) * d.nc + c) * nblk + blockIdx.y] = s;
+        }
+        __syncthreads();
+    }
+    if (on && dinit) dinit[(long long)(b * d.H + h) * PN + e] = run;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dx, ddt_out, dz and per-block dD partials.
+//   acc[l,p] = sum_n B[l,n] (E_f[p,n] e^{T-cs_f[l]} + E_b[p,n] e^{T-cs_b[l]})
+//            + sum_s CB[s,l] ([s>=l] e^{cs_f[s]-cs_f[l]} + [s<=l] e^{cs_b[s]-cs_b[l]}) g[s,p]
+//   dx = acc Delta[l] + D g;  ddt_out[l] = sum_p acc x[l,p];  dD[p] += sum_l g x
+// Takes over _chunk_scan_chunk_state_bwd_dx_kernel (src/ssd/bi/ssd_combined.py:59-232) and, for dz,
+// _chunk_scan_bwd_dz_kernel (src/ssd/bi/ssd_chunk_scan.py:357-440).
+// grid (b*nc*H, ceil(Q/64)); dynamic smem 3*Q floats.
+template <class T>
+__global__ void __launch_bounds__(TB) dx_kernel(Dims d, View x, View Bm, View z, View dout, View out_x, const float *D,
+                                                const float *dt_out, const float *cs_f, const float *cs_b,
+                                                const float *CB, const float *E, void *dx, void *dz, float *ddt_out,
+                                                float *dDpart) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    __shared__ float red[16][TILE];
+    float *sf = sm, *sb = sm + d.Q, *sd = sm + 2 * d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    for (int l = threadIdx.x; l < d.Q; l += TB) {
+        sf[l] = cs_f[base + l];
+        sb[l] = cs_b[base + l];
+        sd[l] = dt_out[base + l];
+    }
+    __syncthreads();
+    const float Tf = sf[d.Q - 1], Tb = sb[0];
+    const int l0 = blockIdx.y * TILE;
+    const int nlt = gridDim.y;
+    const float *cb = CB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
+    const long long per_dir = (long long)d.b * d.nc * d.H * d.P * d.N;
+    const long long st_base = ((long long)(b * d.nc + c) * d.H + h) * d.P * d.N;
+    const int N = d.N;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p0 = 0; p0 < d.P; p0 += TILE) {
+        float acc[4][4];
+        zero_acc(acc);
+        auto fa = [&](int m, int k) -> float {
+            const int l = l0 + m;
+            if (l >= lim) return 0.f;
+            if (k < N) return ldv<T>(Bm, b, c * d.Q + l, g, k) * expf(Tf - sf[l]);
+            if (k < 2 * N) return ldv<T>(Bm, b, c * d.Q + l, g, k - N) * expf(Tb - sb[l]);
+            const int s = k - 2 * N;
+            if (s >= lim) return 0.f;
+            float w = 0.f;
+            if (s >= l) w += expf(sf[s] - sf[l]);
+            if (s <= l) w += expf(sb[s] - sb[l]);
+            return cb[(long long)s * d.Q + l] * w;
+        };
+        auto fb = [&](int k, int n) -> float {
+            const int p = p0 + n;
+            if (p >= d.P) return 0.f;
+            if (k < N) return E[st_base + (long long)p * N + k];
+            if (k < 2 * N) return E[per_dir + st_base + (long long)p * N + (k - N)];
+            const int s = k - 2 * N;
+            return (s < lim) ? gate_grad<T>(d, dout, z, b, c * d.Q + s, h, p) : 0.f;
+        };
+        block_gemm<true, false>(acc, 2 * N + d.Q, fa, fb, gs);
+        float colsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int l = l0 + ty * 4 + i;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int p = p0 + tx * 4 + j;
+                if (l >= lim || p >= d.P) continue;
+                const int ls = c * d.Q + l;
+                const float xv = ldv<T>(x, b, ls, h, p);
+                const float dov = ldv<T>(dout, b, ls, h, p);
+                float gv = dov;
+                if (d.has_z) {
+                    const float zz = ldv<T>(z, b, ls, h, p);
+                    const float sg = sigmoidf_(zz);
+                    gv = dov * zz * sg;
+                    const float ox = ldv<T>(out_x, b, ls, h, p);
+                    st<T>(dz, ((long long)(b * d.L + ls) * d.H + h) * d.P + p, dov * ox * sg * (1.f + zz * (1.f - sg)));
+                }
+                float v = acc[i][j] * sd[l];
+                if (d.has_D) v += (d.D_hdim ? D[h * d.P + p] : D[h]) * gv;
+                st<T>(dx, ((long long)(b * d.L + ls) * d.H + h) * d.P + p, v);
+                rowsum[i] += acc[i][j] * xv;
+                colsum[j] += gv * xv;
+            }
+        }
+        if (d.has_D) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[ty][tx * 4 + j] = colsum[j];
+            __syncthreads();
+            if (threadIdx.x < TILE && p0 + threadIdx.x < d.P) {
+                float s = 0.f;
+                for (int r = 0; r < 16; ++r) s += red[r][threadIdx.x];
+                dDpart[(((long long)(b * d.nc + c) * d.H + h) * nlt + blockIdx.y) * d.P + p0 + threadIdx.x] = s;
+            }
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float r = row_reduce16(rowsum[i]);
+        const int l = l0 + ty * 4 + i;
+        if (tx == 0 && l < d.Q) ddt_out[base + l] = r;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Per-head "states" parts of dB / dC and the decay-gradient terms that come with them (blockIdx.z: 0 = dB, 1 = dC).
+//   dB: part[l,n] = Delta[l] sum_p x[l,p] (E_f[p,n] e^{T-cs_f[l]} + E_b[p,n] e^{T-cs_b[l]});
+//       nf[l] = sum_n (forward part) B[l,n], nb[l] likewise              ("next" terms)
+//   dC: part[l,n] = sum_p g[l,p] (S_f[p,n] e^{cs_f[l]} + S_b[p,n] e^{cs_b[l]});
+//       pf[l] = sum_n (forward part) C[l,n], pb[l] likewise              ("prev" terms)
+// Takes over _chunk_state_bwd_db_kernel (src/ssd/bi/ssd_chunk_state.py:379-495) and _chunk_scan_bwd_dc_kernel
+// (src/ssd/bi/ssd_chunk_scan.py:538-636); the sum over the heads of a group happens in bmm_bwd below.
+// part layout: [b, nc*Q, H, N] fp32.   grid (b*nc*H, ceil(Q/64), 2); dynamic smem 3*Q floats.
+template <class T>
+__global__ void __launch_bounds__(TB) dbc_states(Dims d, View x, View Bm, View Cm, View z, View dout,
+                                                 const float *dt_out, const float *cs_f, const float *cs_b,
+                                                 const float *E, const void *states_f, const void *states_b,
+                                                 float *dB_part, float *dC_part, float *nf, float *nb, float *pf,
+                                                 float *pb) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    float *sf = sm, *sb = sm + d.Q, *sd = sm + 2 * d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int which = blockIdx.z;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    for (int l = threadIdx.x; l < d.Q; l += TB) {
+        sf[l] = cs_f[base + l];
+        sb[l] = cs_b[base + l];
+        sd[l] = dt_out[base + l];
+    }
+    __syncthreads();
+    const float Tf = sf[d.Q - 1], Tb = sb[0];
+    const int l0 = blockIdx.y * TILE;
+    const long long per_dir = (long long)d.b * d.nc * d.H * d.P * d.N;
+    const long long st_base = ((long long)(b * d.nc + c) * d.H + h) * d.P * d.N;
+    const int N = d.N;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float rs_f[4] = {0.f, 0.f, 0.f, 0.f}, rs_b[4] = {0.f, 0.f, 0.f, 0.f};
+    float *part = which ? dC_part : dB_part;
+    const View &other = which ? Cm : Bm;
+    for (int n0 = 0; n0 < N; n0 += TILE) {
+        float af[4][4], ab[4][4];
+        zero_acc(af);
+        zero_acc(ab);
+        auto fa = [&](int m, int k) -> float {
+            const int l = l0 + m;
+            if (l >= lim || k >= d.P) return 0.f;
+            return which ? gate_grad<T>(d, dout, z, b, c * d.Q + l, h, k) : ldv<T>(x, b, c * d.Q + l, h, k);
+        };
+        auto fbf = [&](int k, int n) -> float {
+            const int nn = n0 + n;
+            if (nn >= N || k >= d.P) return 0.f;
+            const long long o = st_base + (long long)k * N + nn;
+            return which ? ld<T>(states_f, o) : E[o];
+        };
+        auto fbb = [&](int k, int n) -> float {
+            const int nn = n0 + n;
+            if (nn >= N || k >= d.P) return 0.f;
+            const long long o = st_base + (long long)k * N + nn;
+            return which ? ld<T>(states_b, o) : E[per_dir + o];
+        };
+        block_gemm<true, false>(af, d.P, fa, fbf, gs);
+        block_gemm<true, false>(ab, d.P, fa, fbb, gs);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int l = l0 + ty * 4 + i;
+            if (l >= lim) continue;
+            const float scf = which ? expf(sf[l]) : sd[l] * expf(Tf - sf[l]);
+            const float scb = which ? expf(sb[l]) : sd[l] * expf(Tb - sb[l]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int nn = n0 + tx * 4 + j;
+                if (nn >= N) continue;
+                const float vf = af[i][j] * scf, vb = ab[i][j] * scb;
+                const float o = ldv<T>(other, b, c * d.Q + l, g, nn);
+                rs_f[i] += vf * o;
+                rs_b[i] += vb * o;
+                part[(((long long)b * d.nc * d.Q + c * d.Q + l) * d.H + h) * N + nn] = vf + vb;
+            }
+        }
+    }
+    float *of = which ? pf : nf, *ob = which ? pb : nb;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float rf = row_reduce16(rs_f[i]), rb = row_reduce16(rs_b[i]);
+        const int l = l0 + ty * 4 + i;
+        if (tx == 0 && l < d.Q) {
+            of[base + l] = rf;
+            ob[base + l] = rb;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dCB[b,c,g,l,s] = sum_{h in g} (g[l].x[s]) Delta_h[s] ([s<=l] e^{cs_f[l]-cs_f[s]} + [s>=l] e^{cs_b[l]-cs_b[s]}).
+// Takes over _chunk_scan_bwd_dcb_kernel (src/ssd/bi/ssd_chunk_scan.py:776-859).
+// grid (b*nc*G, ceil(Q/64), ceil(Q/64))
+template <class T>
+__global__ void __launch_bounds__(TB) dcb_kernel(Dims d, View x, View z, View dout, const float *dt_out,
+                                                 const float *cs_f, const float *cs_b, float *dCB) {
+    __shared__ GemmSmem gs;
+    const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const int l0 = blockIdx.y * TILE, s0 = blockIdx.z * TILE;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float tot[4][4];
+    zero_acc(tot);
+    for (int r = 0; r < d.R; ++r) {
+        const int h = g * d.R + r;
+        float acc[4][4];
+        zero_acc(acc);
+        auto fa = [&](int m, int k) -> float {
+            return (l0 + m < lim && k < d.P) ? gate_grad<T>(d, dout, z, b, c * d.Q + l0 + m, h, k) : 0.f;
+        };
+        auto fb = [&](int k, int n) -> float {
+            return (s0 + n < lim && k < d.P) ? ldv<T>(x, b, c * d.Q + s0 + n, h, k) : 0.f;
+        };
+        block_gemm<true, true>(acc, d.P, fa, fb, gs);
+        const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int l = l0 + ty * 4 + i;
+            if (l >= lim) continue;
+            const float fl = cs_f[base + l], bl = cs_b[base + l];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int s = s0 + tx * 4 + j;
+                if (s >= lim) continue;
+                float w = 0.f;
+                if (s <= l) w += expf(fl - cs_f[base + s]);
+                if (s >= l) w += expf(bl - cs_b[base + s]);
+                tot[i][j] += acc[i][j] * dt_out[base + s] * w;
+            }
+        }
+    }
+    float *out = dCB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int l = l0 + ty * 4 + i;
+        if (l >= d.Q) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int s = s0 + tx * 4 + j;
+            if (s < d.Q) out[(long long)l * d.Q + s] = tot[i][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Intra-chunk decay gradients, per head:
+//   W_f[l,s] = (g[l].x[s]) CB[l,s] Delta[s] e^{cs_f[l]-cs_f[s]}  (s<l),   da_f[j] = sum_{l>=j} sum_{s<j} W_f[l,s]
+//   W_b[l,s] = (g[l].x[s]) CB[l,s] Delta[s] e^{cs_b[l]-cs_b[s]}  (s>l),   da_b[j] = sum_{l<=j} sum_{s>j} W_b[l,s]
+// evaluated as a row-wise exclusive prefix (suffix) followed by a masked column sum - the same order of
+// operations as the reference's "stable" kernels (_chunk_scan_bwd_ddAcs_stable_fwd_kernel,
+// src/ssd/bi/ssd_chunk_scan.py:1361-1446, and _bwd_kernel, :1078-1157).
+// grid (b*nc*H); dynamic smem (3*Q + 2*64*(Q+1)) floats.
+template <class T>
+__global__ void __launch_bounds__(TB) intra_decay_grad(Dims d, View x, View z, View dout, const float *dt_out,
+                                                       const float *cs_f, const float *cs_b, const float *CB,
+                                                       float *da_f, float *da_b) {
+    extern __shared__ float sm[];
+    __shared__ GemmSmem gs;
+    const int Q = d.Q, LW = Q + 1;
+    float *sf = sm, *sb = sm + Q, *sd = sm + 2 * Q;
+    float *Wf = sm + 3 * Q, *Wb = Wf + TILE * LW;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int g = h / d.R;
+    const int lim = min(Q, d.L - c * Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
+    for (int l = threadIdx.x; l < Q; l += TB) {
+        sf[l] = cs_f[base + l];
+        sb[l] = cs_b[base + l];
+        sd[l] = dt_out[base + l];
+    }
+    __syncthreads();
+    const float *cb = CB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float outf = 0.f, outb = 0.f;          // thread tid owns column j = tid (Q <= 256)
+    for (int l0 = 0; l0 < Q; l0 += TILE) {
+        for (int s0 = 0; s0 < Q; s0 += TILE) {
+            float acc[4][4];
+            zero_acc(acc);
+            auto fa = [&](int m, int k) -> float {
+                return (l0 + m < lim && k < d.P) ? gate_grad<T>(d, dout, z, b, c * Q + l0 + m, h, k) : 0.f;
+            };
+            auto fb = [&](int k, int n) -> float {
+                return (s0 + n < lim && k < d.P) ? ldv<T>(x, b, c * Q + s0 + n, h, k) : 0.f;
+            };
+            block_gemm<true, true>(acc, d.P, fa, fb, gs);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = ty * 4 + i, l = l0 + r;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int s = s0 + tx * 4 + j;
+                    if (s >= Q) continue;
+                    float vf = 0.f, vb = 0.f;
+                    if (l < lim && s < lim) {
+                        const float t = acc[i][j] * cb[(long long)l * Q + s] * sd[s];
+                        if (s < l) vf = t * expf(sf[l] - sf[s]);
+                        if (s > l) vb = t * expf(sb[l] - sb[s]);
+                    }
+                    Wf[r * LW + s] = vf;
+                    Wb[r * LW + s] = vb;
+                }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < TILE) {                       // exclusive prefix along the row
+            float *row = Wf + threadIdx.x * LW;
+            float run = 0.f;
+            for (int j = 0; j < Q; ++j) {
+                const float v = row[j];
+                row[j] = run;
+                run += v;
+            }
+        } else if (threadIdx.x < 2 * TILE) {            // exclusive suffix along the row
+            float *row = Wb + (threadIdx.x - TILE) * LW;
+            float run = 0.f;
+            for (int j = Q - 1; j >= 0; --j) {
+                const float v = row[j];
+                row[j] = run;
+                run += v;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < Q) {
+            const int j = threadIdx.x;
+            for (int r = 0; r < TILE; ++r) {
+                const int l = l0 + r;
+                if (l >= j) outf += Wf[r * LW + j];
+                if (l <= j) outb += Wb[r * LW + j];
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < Q) {
+        da_f[base + threadIdx.x] = outf;
+        da_b[base + threadIdx.x] = outb;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dB[s,n] = sum_l dCB[l,s] C[l,n] + sum_{h in g} dB_part[s,h,n];  dC[l,n] = sum_s dCB[l,s] B[s,n] + sum_h dC_part.
+// Takes over the two _bmm_chunk_bwd_kernel calls (src/ssd/bi/ssd_bmm.py:108-160; ssd_combined.py:441-442).
+// grid (b*nc*G*2, ceil(Q/64), ceil(N/64)); blockIdx.x & 1: 0 = dB, 1 = dC.
+template <class T>
+__global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const float *dCB, const float *dB_part,
+                                              const float *dC_part, void *dB, void *dC) {
+    __shared__ GemmSmem gs;
+    const int which = blockIdx.x & 1;
+    const int bx = blockIdx.x >> 1;
+    const int g = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const int r0 = blockIdx.y * TILE, n0 = blockIdx.z * TILE;
+    const float *dcb = dCB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
+    const int Q = d.Q;
+    float acc[4][4];
+    zero_acc(acc);
+    if (which == 0) {
+        auto fa = [&](int m, int k) -> float { return (r0 + m < lim && k < lim) ? dcb[(long long)k * Q + r0 + m] : 0.f; };
+        auto fb = [&](int k, int n) -> float {
+            return (n0 + n < d.N && k < lim) ? ldv<T>(Cm, b, c * Q + k, g, n0 + n) : 0.f;
+        };
+        block_gemm<false, false>(acc, Q, fa, fb, gs);
+    } else {
+        auto fa = [&](int m, int k) -> float { return (r0 + m < lim && k < lim) ? dcb[(long long)(r0 + m) * Q + k] : 0.f; };
+        auto fb = [&](int k, int n) -> float {
+            return (n0 + n < d.N && k < lim) ? ldv<T>(Bm, b, c * Q + k, g, n0 + n) : 0.f;
+        };
+        block_gemm<true, false>(acc, Q, fa, fb, gs);
+    }
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const float *part = which ? dC_part : dB_part;
+    void *out = which ? dC : dB;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int l = r0 + ty * 4 + i;
+        if (l >= lim) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= d.N) continue;
+            float v = acc[i][j];
+            const long long pb = (((long long)b * d.nc * Q + c * Q + l) * d.H + g * d.R) * d.N + n;
+            for (int r = 0; r < d.R; ++r) v += part[pb + (long long)r * d.N];
+            st<T>(out, (((long long)b * d.L + c * Q + l) * d.G + g) * d.N + n, v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Assemble d(a) from its six terms, go back through the discretisation.  One warp per (batch, chunk, head).
+//   ddA = da_f + da_b + exclcumsum(nf) + exclrevcumsum(nb) + revcumsum(pf, +dT_f at Q-1) + cumsum(pb, +dT_b at 0)
+//   ddt = (ddA A + ddt_out), zero where the clamp is active, times sigmoid(pre) when softplus (pre <= 20)
+// Takes over the host glue at src/ssd/bi/ssd_combined.py:456-466 and _chunk_cumsum_bwd_kernel
+// (src/ssd/bi/ssd_chunk_state.py:106-170).  dA / ddt_bias partials per (b,c,h) are reduced by final_reduce.
+// dynamic smem: 8 * Q floats.
+__global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
+                                                 long long dsh, const float *A, const float *dt_bias,
+                                                 const float *dt_out, const float *ddt_out, const float *nf,
+                                                 const float *nb, const float *pf, const float *pb, const float *da_f,
+                                                 const float *da_b, const float *dTpart, int nblk, void *ddt,
+                                                 float *dApart, float *dbiaspart) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
+    const int h = blockIdx.y * 8 + warp;
+    if (h >= d.H) return;
+    float *acc = sm + warp * d.Q;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    const long long tix = (long long)(b * d.H + h) * d.nc + c;
+    float dTf = 0.f, dTb = 0.f;
+    for (int k = 0; k < nblk; ++k) {
+        dTf += dTpart[tix * nblk + k];
+        dTb += dTpart[((long long)d.b * d.H * d.nc + tix) * nblk + k];
+    }
+    // ascending pass: exclusive cumsum of nf, inclusive cumsum of pb (+dT_b at index 0)
+    float c1 = 0.f, c2 = 0.f;
+    for (int l0 = 0; l0 < d.Q; l0 += 32) {
+        const int l = l0 + lane;
+        float v1 = 0.f, v2 = 0.f;
+        if (l < d.Q) {
+            v1 = nf[base + l];
+            v2 = pb[base + l] + (l == 0 ? dTb : 0.f);
+        }
+        const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
+        c1 = __shfl_sync(0xffffffffu, i1, 31);
+        c2 = __shfl_sync(0xffffffffu, i2, 31);
+        if (l < d.Q) acc[l] = (i1 - v1) + i2 + da_f[base + l] + da_b[base + l];
+    }
+    __syncwarp();
+    // descending pass: exclusive reverse cumsum of nb, inclusive reverse cumsum of pf (+dT_f at index Q-1)
+    c1 = 0.f;
+    c2 = 0.f;
+    float sumA = 0.f, sumB = 0.f;
+    const float Ah = A[h];
+    const float bias = d.has_bias ? dt_bias[h] : 0.f;
+    for (int t = ceil_div(d.Q, 32) - 1; t >= 0; --t) {
+        const int l = t * 32 + (31 - lane);
+        float v1 = 0.f, v2 = 0.f;
+        if (l < d.Q) {
+            v1 = nb[base + l];
+            v2 = pf[base + l] + (l == d.Q - 1 ? dTf : 0.f);
+        }
+        const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
+        c1 = __shfl_sync(0xffffffffu, i1, 31);
+        c2 = __shfl_sync(0xffffffffu, i2, 31);
+        if (l < lim) {
+            const float ddA = acc[l] + (i1 - v1) + i2;
+            float g = ddA * Ah + ddt_out[base + l];
+            const float pre = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
+            const float val = d.softplus ? softplus_ref(pre) : pre;
+            if (val < d.dt_min || val > d.dt_max) g = 0.f;
+            if (d.softplus && pre <= 20.f) g *= sigmoidf_(pre);
+            st_any(ddt, dt_dtype, ((long long)b * d.L + c * d.Q + l) * d.H + h, g);
+            sumA += ddA * dt_out[base + l];
+            sumB += g;
+        }
+    }
+    sumA = warp_sum(sumA);
+    sumB = warp_sum(sumB);
+    if (lane == 0) {
+        dApart[(long long)(b * d.nc + c) * d.H + h] = sumA;
+        dbiaspart[(long long)(b * d.nc + c) * d.H + h] = sumB;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fixed-order reduction of the per-block partials into dA (H), ddt_bias (H) and dD (H or H*P).  grid (H).
+__global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, const float *dbiaspart,
+                                                   const float *dDpart, int nlt, float *dA, float *ddt_bias, float *dD) {
+    __shared__ float red[TB];
+    const int h = blockIdx.x;
+    const int nbc = d.b * d.nc;
+    float sa = 0.f, sbias = 0.f;
+    for (int i = threadIdx.x; i < nbc; i += TB) {
+        sa += dApart[(long long)i * d.H + h];
+        sbias += dbiaspart[(long long)i * d.H + h];
+    }
+    red[threadIdx.x] = sa;
+    __syncthreads();
+    for (int o = TB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dA[h] = red[0];
+    __syncthreads();
+    red[threadIdx.x] = sbias;
+    __syncthreads();
+    for (int o = TB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = red[0];
+    __syncthreads();
+    if (dD && dDpart) {
+        float tot = 0.f;
+        for (int p = threadIdx.x; p < d.P; p += TB) {
+            float s = 0.f;
+            for (int i = 0; i < nbc * 1; ++i)
+                for (int t = 0; t < nlt; ++t) s += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
+            if (d.D_hdim) dD[h * d.P + p] = s;
+            tot += s;
+        }
+        if (!d.D_hdim) {
+            red[threadIdx.x] = tot;
+            __syncthreads();
+            for (int o = TB / 2; o > 0; o >>= 1) {
+                if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) dD[h] = red[0];
+        }
+    }
+}
+
+}  // namespace simt
+}  // namespace bissd

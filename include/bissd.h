@@ -1,0 +1,159 @@
+/*
+ * bissd.h - C ABI of libbissd: the bidirectional SSD chunk scan
+ *     y = SS(x) + flip(SS(flip(x))) + D*x   (optionally gated by z),   forward and backward,
+ * as hand-written CUDA for sm_100a (NVIDIA B200).
+ *
+ * The reference (Hprairie/Bi-Mamba2) is Python + Triton and has no native boundary; this header is the
+ * boundary a host binding (Python ctypes, a C++ extension, ...) uses in its place.  Each entry point names the
+ * reference function whose work it takes over.
+ *
+ * Conventions
+ *   - plain C types only: raw device pointers, sizes, element strides; no torch types.
+ *   - the caller owns every buffer (inputs, outputs, saved intermediates, workspace); unless an entry point
+ *     says otherwise the library never allocates or frees device memory, never synchronises the device and
+ *     never changes the current device.  All work is enqueued on the stream passed in (a cudaStream_t cast
+ *     to void*; NULL = the legacy default stream).
+ *   - every function returns BISSD_OK (0) or a negative bissd_status; no C++ exception crosses the boundary.
+ *   - tensors named like the reference's: x (batch, seqlen, nheads, headdim), dt (batch, seqlen, nheads),
+ *     A (nheads), B and C (batch, seqlen, ngroups, dstate), D (nheads) or (nheads, headdim),
+ *     z like x, dt_bias (nheads).  nchunks = ceil(seqlen / chunk_size).
+ */
+#ifndef BISSD_H_
+#define BISSD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BISSD_ABI_VERSION 1
+
+typedef enum bissd_status {
+    BISSD_OK = 0,
+    BISSD_ERR_NULL = -1,          /* a required pointer is NULL */
+    BISSD_ERR_SHAPE = -2,         /* inconsistent or unsupported sizes */
+    BISSD_ERR_DTYPE = -3,         /* unsupported dtype combination */
+    BISSD_ERR_ALIGN = -4,         /* pointer or stride not aligned as required */
+    BISSD_ERR_WORKSPACE = -5,     /* workspace smaller than bissd_workspace_bytes() reports */
+    BISSD_ERR_LAUNCH = -6,        /* a CUDA launch or API call failed (see bissd_last_cuda_error) */
+    BISSD_ERR_ARCH = -7,          /* the current device is not compute capability 10.x */
+    BISSD_ERR_PHASE = -8          /* invalid phase mask */
+} bissd_status;
+
+typedef enum bissd_dtype { BISSD_F32 = 0, BISSD_BF16 = 1, BISSD_F16 = 2 } bissd_dtype;
+
+/* Phases, for callers that shard the sequence over several GPUs and must exchange boundary states between
+ * the local part and the rest of a pass.  BISSD_PHASE_ALL runs a whole pass.  When a pass is split, the SAME
+ * workspace (contents preserved) must be passed to both calls. */
+enum {
+    BISSD_PHASE_LOCAL = 1,   /* fwd: discretise, local chunk states, state passing -> final states.
+                                bwd: gate, local state gradients, state-passing backward -> dinit_* */
+    BISSD_PHASE_FINISH = 2,  /* fwd: state passing again with init_* , then the chunk scan.
+                                bwd: state-passing backward again with dfinal_* , then all gradients */
+    BISSD_PHASE_ALL = 3
+};
+
+/* Sizes and switches of one call.  Mirrors the keyword arguments of
+ * bimamba_chunk_scan_combined (src/ssd/bi/ssd_combined.py:577) and the asserts of
+ * _mamba_chunk_scan_combined_fwd (src/ssd/bi/ssd_combined.py:297-320). */
+typedef struct bissd_problem {
+    int32_t batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size;
+    int32_t x_dtype;        /* bissd_dtype of x, z, out, out_x, dout, dx, dz, B, C, dB, dC and the saved states */
+    int32_t dt_dtype;       /* bissd_dtype of dt and ddt */
+    int32_t has_D;          /* D given */
+    int32_t D_has_hdim;     /* D is (nheads, headdim) instead of (nheads) */
+    int32_t has_z;          /* z given: out = y * silu(z), out_x = y */
+    int32_t has_dt_bias;
+    int32_t dt_softplus;
+    float dt_min, dt_max;   /* dt_limit; (0, +inf) by default */
+} bissd_problem;
+
+/* A (batch, seqlen, heads-or-groups, inner) tensor with a contiguous innermost dimension; strides in elements. */
+typedef struct bissd_tensor {
+    void *ptr;
+    int64_t stride_batch, stride_seq, stride_head;
+} bissd_tensor;
+
+/* Arguments of the forward pass: replaces _mamba_chunk_scan_combined_fwd (src/ssd/bi/ssd_combined.py:297-331),
+ * i.e. _chunk_cumsum_fwd (ssd_chunk_state.py:699), _chunk_state_fwd (:764), both _state_passing_fwd calls
+ * (ssd_state_passing.py:190), _bmm_chunk_fwd (ssd_bmm.py:163) and _chunk_scan_fwd (ssd_chunk_scan.py:1638). */
+typedef struct bissd_fwd_args {
+    bissd_problem p;
+    bissd_tensor x, B, C, z;              /* z.ptr NULL unless p.has_z */
+    bissd_tensor dt;                      /* (batch, seqlen, nheads): stride_head is the stride of the head index */
+    const float *A, *D, *dt_bias;         /* fp32; D / dt_bias NULL when absent */
+    bissd_tensor out;                     /* like x */
+    bissd_tensor out_x;                   /* like x; written only when p.has_z */
+    /* saved for the backward pass, contiguous: */
+    float *dt_out, *cs_f, *cs_b;          /* (batch, nheads, nchunks, chunk_size) fp32 */
+    void *states_f, *states_b;            /* (batch, nchunks, nheads, headdim, dstate), x_dtype: state entering
+                                             each chunk from the left (f) / from the right (b) */
+    float *final_f, *final_b;             /* (batch, nheads, headdim, dstate) fp32; may be NULL */
+    const float *init_f, *init_b;         /* optional (batch, nheads, headdim, dstate) fp32 incoming states:
+                                             init_f precedes token 0, init_b follows the last token */
+    int32_t phases;                       /* BISSD_PHASE_* mask */
+} bissd_fwd_args;
+
+/* Arguments of the backward pass: replaces _mamba_chunk_scan_combined_bwd (src/ssd/bi/ssd_combined.py:334-475):
+ * _chunk_scan_bwd_dz, _chunk_scan_bwd_dstates, both _state_passing_bwd calls,
+ * _chunk_scan_chunk_state_bwd_dx, _chunk_state_bwd_db, _chunk_scan_bwd_dC, _chunk_scan_bwd_dcb, both
+ * _bmm_chunk_bwd calls, _chunk_scan_bwd_ddAcs_stable_fwd/_bwd, the host glue at :456-466 and _chunk_cumsum_bwd. */
+typedef struct bissd_bwd_args {
+    bissd_problem p;
+    bissd_tensor x, B, C, z, dout;
+    bissd_tensor out_x;                   /* the forward's pre-gate output; read only when p.has_z */
+    bissd_tensor dt;
+    const float *A, *D, *dt_bias;
+    const float *dt_out, *cs_f, *cs_b;    /* as written by the forward */
+    const void *states_f, *states_b;      /* as written by the forward */
+    /* gradients, all contiguous in the layout of the tensor they belong to: */
+    void *dx, *dz;                        /* x_dtype; dz NULL unless p.has_z */
+    void *dB, *dC;                        /* x_dtype */
+    void *ddt;                            /* dt_dtype, (batch, seqlen, nheads) */
+    float *dA, *dD, *ddt_bias;            /* fp32: (nheads), (nheads[, headdim]), (nheads); dD / ddt_bias may be NULL */
+    const float *dfinal_f, *dfinal_b;     /* optional gradients of final_f / final_b */
+    float *dinit_f, *dinit_b;             /* optional outputs: gradients w.r.t. init_f / init_b */
+    int32_t phases;
+} bissd_bwd_args;
+
+/* ABI version of the loaded library (== BISSD_ABI_VERSION of the header it was built from). */
+int bissd_abi_version(void);
+
+/* Human-readable text for a status code. */
+const char *bissd_strerror(int status);
+
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *bissd_last_cuda_error(void);
+
+/* Bytes of scratch each pass needs for `p` (either pointer may be NULL).  The reference allocates the same
+ * kind of temporaries with torch.empty inside every wrapper (e.g. ssd_chunk_state.py:775-776). */
+int bissd_workspace_bytes(const bissd_problem *p, size_t *fwd_bytes, size_t *bwd_bytes);
+
+/* Forward pass.  workspace must be 256-byte aligned. */
+int bissd_forward(const bissd_fwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Backward pass. */
+int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
+const char *bissd_kernel_path(const bissd_problem *p);
+
+/* ---- tracing (the reference has none beyond triton.testing.do_bench in benchmark/*.py) ----------------------- */
+
+/* Number of kernels this library has launched in this process so far. */
+unsigned long long bissd_launch_count(void);
+
+/* on != 0: from now on bracket every kernel launch with a pair of CUDA events on the launching stream (and drop
+ * earlier records); on == 0: stop and drop the records. */
+int bissd_trace_enable(int on);
+
+/* Wait for the recorded events and sum them per kernel name.  `names` receives the names separated by ';',
+ * total_ms[i] / launches[i] the summed device time and launch count of the i-th name, *count how many names. */
+int bissd_trace_read(char *names, size_t names_cap, float *total_ms, int *launches, int cap, int *count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BISSD_H_ */

@@ -1,0 +1,105 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports what include/bissd.h declares, the ctypes
+structs have the C layout, and argument validation answers without touching a GPU."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+from conftest import ROOT
+
+sys.path.insert(0, os.path.join(ROOT, "bi-mamba2_b200"))
+from ssd import _cabi  # noqa: E402
+
+HEADER = os.path.join(ROOT, "include", "bissd.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bissd_build", os.path.join(ROOT, "bi-mamba2_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+    return _cabi.load()
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bissd_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_functions()
+    assert set(_cabi.EXPORTS) <= set(names)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/bissd.h but not exported by libbissd.so"
+
+
+def test_abi_version(lib):
+    assert lib.bissd_abi_version() == _cabi.ABI_VERSION
+
+
+def test_struct_layout_matches_c_header():
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "bissd.h"
+int main(void) {
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(bissd_problem), sizeof(bissd_tensor), sizeof(bissd_fwd_args),
+         sizeof(bissd_bwd_args), offsetof(bissd_fwd_args, dt_out), offsetof(bissd_fwd_args, phases),
+         offsetof(bissd_bwd_args, dx), offsetof(bissd_bwd_args, phases));
+  return 0; }
+'''
+    with tempfile.TemporaryDirectory() as td:
+        cpath, exe = os.path.join(td, "t.c"), os.path.join(td, "t")
+        open(cpath, "w").write(src)
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), cpath, "-o", exe])
+        got = [int(v) for v in subprocess.check_output([exe]).split()]
+    want = [ctypes.sizeof(_cabi.Problem), ctypes.sizeof(_cabi.Tensor), ctypes.sizeof(_cabi.FwdArgs),
+            ctypes.sizeof(_cabi.BwdArgs), _cabi.FwdArgs.dt_out.offset, _cabi.FwdArgs.phases.offset,
+            _cabi.BwdArgs.dx.offset, _cabi.BwdArgs.phases.offset]
+    assert got == want
+
+
+def _problem(**kw):
+    base = dict(batch=2, seqlen=128, nheads=4, headdim=16, ngroups=2, dstate=16, chunk_size=64, x_dtype=0, dt_dtype=0,
+                has_D=1, D_has_hdim=0, has_z=0, has_dt_bias=0, dt_softplus=1, dt_min=0.0, dt_max=float("inf"))
+    base.update(kw)
+    return _cabi.Problem(**base)
+
+
+def test_workspace_bytes_and_validation(lib):
+    f, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem()), ctypes.byref(f), ctypes.byref(b)) == 0
+    assert f.value > 0 and b.value > f.value
+    assert f.value % 256 == 0 and b.value % 256 == 0
+    # nheads not divisible by ngroups; chunk below the reference's minimum of 32; bad dtype
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem(ngroups=3)), None, None) == -2
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem(chunk_size=16)), None, None) == -2
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem(x_dtype=7)), None, None) == -3
+    assert lib.bissd_workspace_bytes(None, None, None) == -1
+
+
+def test_forward_rejects_bad_arguments_before_any_launch(lib):
+    args = _cabi.FwdArgs()
+    args.p = _problem()
+    args.phases = 3
+    assert lib.bissd_forward(ctypes.byref(args), None, 0, None) == -1          # NULL tensors
+    args.phases = 0
+    assert lib.bissd_forward(ctypes.byref(args), None, 0, None) == -8          # bad phase mask
+    assert lib.bissd_forward(None, None, 0, None) == -1
+    assert b"NULL" in lib.bissd_strerror(-1)
+
+
+def test_operator_refuses_cpu_tensors(lib):
+    import torch
+    from ssd.bi.ssd_combined import bimamba_chunk_scan_combined
+    x = torch.randn(1, 64, 2, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        bimamba_chunk_scan_combined(x, torch.rand(1, 64, 2), -torch.ones(2), torch.randn(1, 64, 1, 8),
+                                    torch.randn(1, 64, 1, 8), 32)
