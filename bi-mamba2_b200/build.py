@@ -33,7 +33,7 @@ def build(force=False, verbose=False):
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
            "--expt-relaxed-constexpr", "--extended-lambda", "-Xcompiler", "-fPIC", "-shared",
-           "-o", OUT] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcuda"]
+           "-o", OUT] + [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

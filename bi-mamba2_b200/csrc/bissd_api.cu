@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "tc_selftest.cuh"
 
 namespace bissd {
 
@@ -288,6 +289,36 @@ int bissd_trace_read(char *names, size_t names_cap, float *total_ms, int *launch
         ++n;
     }
     *count = n;
+    return BISSD_OK;
+}
+
+int bissd_selftest_gemm(int dtype, int a_mn_major, int b_mn_major, int n, int k, const void *A, const void *B, float *C,
+                        int *status_dev, void *stream) {
+    if (!A || !B || !C || !status_dev) return BISSD_ERR_NULL;
+    if (dtype != BISSD_BF16 && dtype != BISSD_F16) return BISSD_ERR_DTYPE;
+    if (n < 16 || n > 256 || (n % 16) || k < 8 || (k % 8)) return BISSD_ERR_SHAPE;
+    int rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t smem = 2 * tc::kAStageBytes + 2 * 256 * 128 + 1024;
+#define BISSD_SELFTEST(T, AM, BM)                                                                          \
+    do {                                                                                                   \
+        rc = allow_smem(tc::selftest_gemm<T, AM, BM>, smem);                                               \
+        if (rc != BISSD_OK) return rc;                                                                     \
+        BISSD_LAUNCH("selftest_gemm", tc::selftest_gemm<T, AM, BM><<<1, tc::kThreads, smem, s>>>(          \
+                                          static_cast<const T *>(A), static_cast<const T *>(B), C, n, k, status_dev)); \
+    } while (0)
+#define BISSD_SELFTEST_T(T)                                        \
+    do {                                                           \
+        if (a_mn_major && b_mn_major) BISSD_SELFTEST(T, true, true);   \
+        else if (a_mn_major) BISSD_SELFTEST(T, true, false);       \
+        else if (b_mn_major) BISSD_SELFTEST(T, false, true);       \
+        else BISSD_SELFTEST(T, false, false);                      \
+    } while (0)
+    if (dtype == BISSD_BF16) BISSD_SELFTEST_T(__nv_bfloat16);
+    else BISSD_SELFTEST_T(__half);
+#undef BISSD_SELFTEST_T
+#undef BISSD_SELFTEST
     return BISSD_OK;
 }
 

@@ -140,6 +140,15 @@ int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace
 /* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
 const char *bissd_kernel_path(const bissd_problem *p);
 
+/* ---- self test -------------------------------------------------------------------------------------------- */
+
+/* Runs C[128][n] = A * B^T (fp32 result) on the library's tcgen05 block-GEMM engine with one CTA, so a test can
+ * compare the tensor-core plumbing with a host GEMM.  A is [128][k] (or [k][128] if a_mn_major), B is [n][k] (or
+ * [k][n] if b_mn_major), 16-bit `dtype`; n a multiple of 16 up to 256, k a multiple of 8.  *status_dev (a device
+ * int the caller zeroes) becomes nonzero if a bounded device-side wait ran out.  No reference counterpart. */
+int bissd_selftest_gemm(int dtype, int a_mn_major, int b_mn_major, int n, int k, const void *A, const void *B, float *C,
+                        int *status_dev, void *stream);
+
 /* ---- tracing (the reference has none beyond triton.testing.do_bench in benchmark/*.py) ----------------------- */
 
 /* Number of kernels this library has launched in this process so far. */
