@@ -1,5 +1,7 @@
 // C ABI of libbissd (declared in include/bissd.h): argument validation, workspace layout, kernel sequencing.
+#include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -7,6 +9,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "tc_kernels.cuh"
 #include "tc_selftest.cuh"
 
 namespace bissd {
@@ -76,18 +79,20 @@ static int make_dims(const bissd_problem &p, Dims *d) {
 
 static inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
-// Workspace carving.  All regions are fp32.
+// Workspace carving.  The first 256 bytes hold the device status word (nonzero = a bounded device-side wait ran
+// out); everything after it is fp32 scratch.
+constexpr size_t kWsHeader = 256;
 struct FwdWs {
     size_t loc, cb, total;
 };
 struct BwdWs {
     size_t cb, gloc, E, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
-    int nblk, nlt;
+    int nblk, nlt, nsplit;
 };
 
 static FwdWs fwd_layout(const Dims &d) {
     FwdWs w;
-    size_t o = 0;
+    size_t o = kWsHeader;
     const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
     w.loc = o; o = align256(o + 2 * st * 4);
     w.cb = o; o = align256(o + (size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
@@ -97,17 +102,20 @@ static FwdWs fwd_layout(const Dims &d) {
 
 static BwdWs bwd_layout(const Dims &d) {
     BwdWs w;
-    size_t o = 0;
+    size_t o = kWsHeader;
     const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
     const size_t hq = (size_t)d.b * d.H * d.nc * d.Q;
     w.nblk = ceil_div(d.P * d.N, simt::TB);
     w.nlt = ceil_div(d.Q, simt::TILE);
+    w.nsplit = ceil_div(d.N, 128);
     auto take = [&](size_t bytes) { size_t at = o; o = align256(o + bytes); return at; };
     w.cb = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
     w.gloc = take(2 * st * 4);
     w.E = take(2 * st * 4);
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
-    w.ddt_out = take(hq * 4); w.nf = take(hq * 4); w.nb = take(hq * 4); w.pf = take(hq * 4); w.pb = take(hq * 4);
+    w.ddt_out = take(hq * 4);
+    w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
+    w.pf = take(hq * 4 * w.nsplit); w.pb = take(hq * 4 * w.nsplit);
     w.da_f = take(hq * 4); w.da_b = take(hq * 4);
     w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
@@ -128,76 +136,174 @@ template <class K> static int allow_smem(K kernel, size_t bytes) {
                      "cudaFuncSetAttribute");
 }
 
+// ---- which kernel family ---------------------------------------------------------------------------------
+static bool tc_shape_ok(const bissd_problem &p) {
+    return (p.x_dtype == BISSD_BF16 || p.x_dtype == BISSD_F16) && p.headdim % 8 == 0 && p.dstate % 8 == 0 &&
+           p.chunk_size % 8 == 0 && p.headdim <= 256 && p.dstate <= 256;
+}
+static bool aligned16(const bissd_tensor &t) {
+    if (!t.ptr) return true;
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && t.stride_batch % 8 == 0 && t.stride_seq % 8 == 0 &&
+           t.stride_head % 8 == 0;
+}
+static bool force_simt() {
+    static const bool v = [] { const char *e = getenv("BISSD_FORCE_SIMT"); return e && e[0] == '1'; }();
+    return v;
+}
+
+#define BISSD_ALLOW(kernel, bytes)                   \
+    do {                                             \
+        int rc_ = allow_smem(kernel, bytes);         \
+        if (rc_ != BISSD_OK) return rc_;             \
+    } while (0)
+
+template <class T> struct TcKernels {   // 16-bit types only; the fp32 specialisation below never launches them
+    static constexpr bool available = true;
+};
+template <> struct TcKernels<float> { static constexpr bool available = false; };
+
 template <class T>
-static int forward_simt(const bissd_fwd_args &a, const Dims &d, char *ws, cudaStream_t s) {
-    using namespace simt;
+static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaStream_t s, bool tcp) {
     const FwdWs w = fwd_layout(d);
+    int *status = reinterpret_cast<int *>(ws);
     float *loc = reinterpret_cast<float *>(ws + w.loc);
     float *CB = reinterpret_cast<float *>(ws + w.cb);
     const View x = view_of(a.x), Bm = view_of(a.B), Cm = view_of(a.C), z = view_of(a.z);
     const int bch = d.b * d.nc * d.H;
+    const int ntP = tc::round_up(d.P, 16), ntQ = tc::round_up(d.Q, 16);
     if (a.phases & BISSD_PHASE_LOCAL) {
-        BISSD_LAUNCH("cumsum_fwd", cumsum_fwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), TB, 8 * d.Q * sizeof(float), s>>>(
+        int rc = note_cuda(cudaMemsetAsync(ws, 0, kWsHeader, s), "cudaMemsetAsync");
+        if (rc != BISSD_OK) return rc;
+        BISSD_LAUNCH("cumsum_fwd", simt::cumsum_fwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
             d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
             a.cs_f, a.cs_b));
-        BISSD_LAUNCH("chunk_state", chunk_state<T><<<dim3(bch, ceil_div(d.P, TILE), ceil_div(2 * d.N, TILE)), TB, 2 * d.Q * sizeof(float), s>>>(
-            d, x, Bm, a.dt_out, a.cs_f, a.cs_b, loc));
+        if constexpr (TcKernels<T>::available) {
+            if (tcp) {
+                const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
+                BISSD_ALLOW((tc::state_gemm<T, 0>), smem);
+                BISSD_LAUNCH("tc_chunk_state", tc::state_gemm<T, 0><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                    d, Bm, x, z, a.dt_out, a.cs_f, a.cs_b, loc, status));
+            }
+        }
+        if (!tcp) {
+            BISSD_LAUNCH("chunk_state", simt::chunk_state<T><<<dim3(bch, ceil_div(d.P, simt::TILE), ceil_div(2 * d.N, simt::TILE)), simt::TB, 2 * d.Q * sizeof(float), s>>>(
+                d, x, Bm, a.dt_out, a.cs_f, a.cs_b, loc));
+        }
     }
     // the recurrence runs in both phases: from zero (or init_*) in LOCAL, again with init_* in FINISH
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.init_f || a.init_b);
     if (need_pass) {
-        BISSD_LAUNCH("state_passing_fwd", state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, TB), 2), TB, 0, s>>>(
+        BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, simt::TB), 2), simt::TB, 0, s>>>(
             d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
     }
     if (a.phases & BISSD_PHASE_FINISH) {
-        BISSD_LAUNCH("bmm_cb", bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, TILE), ceil_div(d.Q, TILE)), TB, 0, s>>>(d, Cm, Bm, CB));
-        BISSD_LAUNCH("chunk_scan", chunk_scan<T><<<dim3(bch, ceil_div(d.Q, TILE), ceil_div(d.P, TILE)), TB, 3 * d.Q * sizeof(float), s>>>(
-            d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x)));
+        if constexpr (TcKernels<T>::available) {
+            if (tcp) {
+                const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_sc = tc::smem_bytes(ntP, 3 * d.Q);
+                BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
+                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, status));
+                BISSD_ALLOW(tc::chunk_scan<T>, smem_sc);
+                BISSD_LAUNCH("tc_chunk_scan", tc::chunk_scan<T><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_sc, s>>>(
+                    d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x), status));
+            }
+        }
+        if (!tcp) {
+            BISSD_LAUNCH("bmm_cb", simt::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, simt::TILE), ceil_div(d.Q, simt::TILE)), simt::TB, 0, s>>>(d, Cm, Bm, CB));
+            BISSD_LAUNCH("chunk_scan", simt::chunk_scan<T><<<dim3(bch, ceil_div(d.Q, simt::TILE), ceil_div(d.P, simt::TILE)), simt::TB, 3 * d.Q * sizeof(float), s>>>(
+                d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x)));
+        }
     }
     return BISSD_OK;
 }
 
 template <class T>
-static int backward_simt(const bissd_bwd_args &a, const Dims &d, char *ws, cudaStream_t s) {
-    using namespace simt;
+static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaStream_t s, bool tcp) {
     const BwdWs w = bwd_layout(d);
+    int *status = reinterpret_cast<int *>(ws);
     auto F = [&](size_t off) { return reinterpret_cast<float *>(ws + off); };
     const View x = view_of(a.x), Bm = view_of(a.B), Cm = view_of(a.C), z = view_of(a.z), dout = view_of(a.dout),
                out_x = view_of(a.out_x);
     const int bch = d.b * d.nc * d.H;
     const size_t q3 = 3 * d.Q * sizeof(float);
+    const int ntP = tc::round_up(d.P, 16), ntQ = tc::round_up(d.Q, 16), ntN = std::min(tc::round_up(d.N, 16), 128);
+    const int nlt_tc = ceil_div(d.Q, tc::kTileM);
     if (a.phases & BISSD_PHASE_LOCAL) {
-        BISSD_LAUNCH("dstates", dstates<T><<<dim3(bch, ceil_div(d.P, TILE), ceil_div(2 * d.N, TILE)), TB, 2 * d.Q * sizeof(float), s>>>(
-            d, dout, z, Cm, a.cs_f, a.cs_b, F(w.gloc)));
+        int rc = note_cuda(cudaMemsetAsync(ws, 0, kWsHeader, s), "cudaMemsetAsync");
+        if (rc != BISSD_OK) return rc;
+        if constexpr (TcKernels<T>::available) {
+            if (tcp) {
+                const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
+                BISSD_ALLOW((tc::state_gemm<T, 1>), smem);
+                BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                    d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+            }
+        }
+        if (!tcp) {
+            BISSD_LAUNCH("dstates", simt::dstates<T><<<dim3(bch, ceil_div(d.P, simt::TILE), ceil_div(2 * d.N, simt::TILE)), simt::TB, 2 * d.Q * sizeof(float), s>>>(
+                d, dout, z, Cm, a.cs_f, a.cs_b, F(w.gloc)));
+        }
     }
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.dfinal_f || a.dfinal_b);
     if (need_pass) {
-        BISSD_LAUNCH("state_passing_bwd", state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), TB, 0, s>>>(d, F(w.gloc), a.states_f, a.states_b, a.cs_f,
-                                                                      a.cs_b, a.dfinal_f, a.dfinal_b, F(w.E),
-                                                                      F(w.dTpart), a.dinit_f, a.dinit_b));
+        BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), simt::TB, 0, s>>>(
+            d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, F(w.E), F(w.dTpart), a.dinit_f, a.dinit_b));
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
-    BISSD_LAUNCH("bmm_cb", bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, TILE), ceil_div(d.Q, TILE)), TB, 0, s>>>(d, Cm, Bm, F(w.cb)));
-    BISSD_LAUNCH("dx_kernel", dx_kernel<T><<<dim3(bch, w.nlt), TB, q3, s>>>(d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb),
-                                                  F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart)));
-    BISSD_LAUNCH("dbc_states", dbc_states<T><<<dim3(bch, w.nlt, 2), TB, q3, s>>>(d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E),
-                                                      a.states_f, a.states_b, F(w.dB_part), F(w.dC_part), F(w.nf),
-                                                      F(w.nb), F(w.pf), F(w.pb)));
-    BISSD_LAUNCH("dcb_kernel", dcb_kernel<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), TB, 0, s>>>(d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB)));
-    {
-        const size_t smem = (3 * d.Q + 2 * TILE * (d.Q + 1)) * sizeof(float);
-        int rc = allow_smem(intra_decay_grad<T>, smem);
-        if (rc != BISSD_OK) return rc;
-        BISSD_LAUNCH("intra_decay_grad", intra_decay_grad<T><<<bch, TB, smem, s>>>(d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b)));
+    int nlt = w.nlt, nsplit = 1, part_heads = d.H;
+    if constexpr (TcKernels<T>::available) {
+        if (tcp) {
+            nlt = nlt_tc;
+            nsplit = w.nsplit;
+            part_heads = d.G;
+            const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
+            BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
+            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), status));
+            BISSD_ALLOW(tc::dx_kernel<T>, smem_dx);
+            BISSD_LAUNCH("tc_dx", tc::dx_kernel<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
+                d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+            BISSD_ALLOW(tc::dbc_states<T>, smem_n);
+            BISSD_LAUNCH("tc_dbc_states", tc::dbc_states<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_n, s>>>(
+                d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E), a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
+                F(w.nf), F(w.nb), F(w.pf), F(w.pb), status));
+        }
     }
-    BISSD_LAUNCH("bmm_bwd", bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, TILE)), TB, 0, s>>>(d, Bm, Cm, F(w.dCB), F(w.dB_part),
-                                                                                    F(w.dC_part), a.dB, a.dC));
-    BISSD_LAUNCH("cumsum_bwd", cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), TB, 8 * d.Q * sizeof(float), s>>>(
+    if (!tcp) {
+        BISSD_LAUNCH("bmm_cb", simt::bmm_cb<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), simt::TB, 0, s>>>(d, Cm, Bm, F(w.cb)));
+        BISSD_LAUNCH("dx_kernel", simt::dx_kernel<T><<<dim3(bch, w.nlt), simt::TB, q3, s>>>(
+            d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart)));
+        BISSD_LAUNCH("dbc_states", simt::dbc_states<T><<<dim3(bch, w.nlt, 2), simt::TB, q3, s>>>(
+            d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E), a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
+            F(w.nf), F(w.nb), F(w.pf), F(w.pb)));
+    }
+    BISSD_LAUNCH("dcb_kernel", simt::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), simt::TB, 0, s>>>(
+        d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB)));
+    {
+        const size_t smem = (3 * d.Q + 2 * simt::TILE * (d.Q + 1)) * sizeof(float);
+        BISSD_ALLOW(simt::intra_decay_grad<T>, smem);
+        BISSD_LAUNCH("intra_decay_grad", simt::intra_decay_grad<T><<<bch, simt::TB, smem, s>>>(
+            d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b)));
+    }
+    bool bmm_tc = false;
+    if constexpr (TcKernels<T>::available) {
+        if (tcp) {
+            bmm_tc = true;
+            const size_t smem_n = tc::smem_bytes(ntN, 0);
+            BISSD_ALLOW(tc::bmm_bwd<T>, smem_n);
+            BISSD_LAUNCH("tc_bmm_bwd", tc::bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, nlt_tc, w.nsplit), tc::kThreads, smem_n, s>>>(
+                d, Bm, Cm, F(w.dCB), F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC, status));
+        }
+    }
+    if (!bmm_tc) {
+        BISSD_LAUNCH("bmm_bwd", simt::bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, simt::TILE)), simt::TB, 0, s>>>(
+            d, Bm, Cm, F(w.dCB), F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC));
+    }
+    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
-        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), w.nblk, a.ddt,
+        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), w.nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
-    BISSD_LAUNCH("final_reduce", final_reduce<<<d.H, TB, 0, s>>>(d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, w.nlt, a.dA,
-                                    d.has_bias ? a.ddt_bias : nullptr, d.has_D ? a.dD : nullptr));
+    BISSD_LAUNCH("final_reduce", simt::final_reduce<<<d.H, simt::TB, 0, s>>>(
+        d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,
+        d.has_D ? a.dD : nullptr));
     return BISSD_OK;
 }
 
@@ -323,8 +429,16 @@ int bissd_selftest_gemm(int dtype, int a_mn_major, int b_mn_major, int n, int k,
 }
 
 const char *bissd_kernel_path(const bissd_problem *p) {
-    (void)p;
-    return "simt";
+    if (!p) return "";
+    return (!force_simt() && tc_shape_ok(*p)) ? "tcgen05" : "simt";
+}
+
+int bissd_read_status(const void *workspace, void *stream, int *status_out) {
+    if (!workspace || !status_out) return BISSD_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = note_cuda(cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync");
+    if (rc != BISSD_OK) return rc;
+    return note_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
 }
 
 int bissd_forward(const bissd_fwd_args *a, void *workspace, size_t workspace_bytes, void *stream) {
@@ -346,10 +460,12 @@ int bissd_forward(const bissd_fwd_args *a, void *workspace, size_t workspace_byt
     if (rc != BISSD_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     char *ws = static_cast<char *>(workspace);
+    const bool tcp = !force_simt() && tc_shape_ok(a->p) && aligned16(a->x) && aligned16(a->B) && aligned16(a->C) &&
+                     aligned16(a->z) && aligned16(a->out) && aligned16(a->out_x);
     switch (a->p.x_dtype) {
-        case BISSD_F32: return forward_simt<float>(*a, d, ws, s);
-        case BISSD_BF16: return forward_simt<__nv_bfloat16>(*a, d, ws, s);
-        default: return forward_simt<__half>(*a, d, ws, s);
+        case BISSD_F32: return forward_impl<float>(*a, d, ws, s, false);
+        case BISSD_BF16: return forward_impl<__nv_bfloat16>(*a, d, ws, s, tcp);
+        default: return forward_impl<__half>(*a, d, ws, s, tcp);
     }
 }
 
@@ -377,10 +493,12 @@ int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_by
     if (rc != BISSD_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     char *ws = static_cast<char *>(workspace);
+    const bool tcp = !force_simt() && tc_shape_ok(a->p) && aligned16(a->x) && aligned16(a->B) && aligned16(a->C) &&
+                     aligned16(a->z) && aligned16(a->dout) && aligned16(a->out_x);
     switch (a->p.x_dtype) {
-        case BISSD_F32: return backward_simt<float>(*a, d, ws, s);
-        case BISSD_BF16: return backward_simt<__nv_bfloat16>(*a, d, ws, s);
-        default: return backward_simt<__half>(*a, d, ws, s);
+        case BISSD_F32: return backward_impl<float>(*a, d, ws, s, false);
+        case BISSD_BF16: return backward_impl<__nv_bfloat16>(*a, d, ws, s, tcp);
+        default: return backward_impl<__half>(*a, d, ws, s, tcp);
     }
 }
 

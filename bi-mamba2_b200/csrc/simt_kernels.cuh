@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(TB) intra_decay_grad(Dims d, View x, View z, V
 // grid (b*nc*G*2, ceil(Q/64), ceil(N/64)); blockIdx.x & 1: 0 = dB, 1 = dC.
 template <class T>
 __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const float *dCB, const float *dB_part,
-                                              const float *dC_part, void *dB, void *dC) {
+                                              const float *dC_part, int part_heads, void *dB, void *dC) {
     __shared__ GemmSmem gs;
     const int which = blockIdx.x & 1;
     const int bx = blockIdx.x >> 1;
@@ -822,8 +822,9 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
             const int n = n0 + tx * 4 + j;
             if (n >= d.N) continue;
             float v = acc[i][j];
-            const long long pb = (((long long)b * d.nc * Q + c * Q + l) * d.H + g * d.R) * d.N + n;
-            for (int r = 0; r < d.R; ++r) v += part[pb + (long long)r * d.N];
+            const int rp = part_heads / d.G;      // partial results per group: one per head, or already summed
+            const long long pb = (((long long)b * d.nc * Q + c * Q + l) * part_heads + g * rp) * d.N + n;
+            for (int r = 0; r < rp; ++r) v += part[pb + (long long)r * d.N];
             st<T>(out, (((long long)b * d.L + c * Q + l) * d.G + g) * d.N + n, v);
         }
     }
@@ -840,8 +841,8 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
                                                  long long dsh, const float *A, const float *dt_bias,
                                                  const float *dt_out, const float *ddt_out, const float *nf,
                                                  const float *nb, const float *pf, const float *pb, const float *da_f,
-                                                 const float *da_b, const float *dTpart, int nblk, void *ddt,
-                                                 float *dApart, float *dbiaspart) {
+                                                 const float *da_b, const float *dTpart, int nblk, int nsplit,
+                                                 void *ddt, float *dApart, float *dbiaspart) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
@@ -851,6 +852,7 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
     const int lim = min(d.Q, d.L - c * d.Q);
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
     const long long tix = (long long)(b * d.H + h) * d.nc + c;
+    const long long split_stride = (long long)d.b * d.H * d.nc * d.Q;   // nf/nb/pf/pb hold nsplit partial copies
     float dTf = 0.f, dTb = 0.f;
     for (int k = 0; k < nblk; ++k) {
         dTf += dTpart[tix * nblk + k];
@@ -862,8 +864,11 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
         const int l = l0 + lane;
         float v1 = 0.f, v2 = 0.f;
         if (l < d.Q) {
-            v1 = nf[base + l];
-            v2 = pb[base + l] + (l == 0 ? dTb : 0.f);
+            for (int k = 0; k < nsplit; ++k) {
+                v1 += nf[k * split_stride + base + l];
+                v2 += pb[k * split_stride + base + l];
+            }
+            if (l == 0) v2 += dTb;
         }
         const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
         c1 = __shfl_sync(0xffffffffu, i1, 31);
@@ -881,8 +886,11 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
         const int l = t * 32 + (31 - lane);
         float v1 = 0.f, v2 = 0.f;
         if (l < d.Q) {
-            v1 = nb[base + l];
-            v2 = pf[base + l] + (l == d.Q - 1 ? dTf : 0.f);
+            for (int k = 0; k < nsplit; ++k) {
+                v1 += nb[k * split_stride + base + l];
+                v2 += pf[k * split_stride + base + l];
+            }
+            if (l == d.Q - 1) v2 += dTf;
         }
         const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
         c1 = __shfl_sync(0xffffffffu, i1, 31);

@@ -10,6 +10,7 @@ PyTorch custom ops, `bissd::scan_fwd` and `bissd::scan_bwd`.  There is no Triton
 without the library, or on CPU tensors, the operator raises.
 """
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -17,6 +18,20 @@ import torch
 from .. import _cabi
 
 _DTYPES = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+
+# With BISSD_CHECK_STATUS=1 every pass is followed by a (synchronising) read of the library's device status word
+# and raises if a bounded device-side wait ran out.  Meant for tests and debugging; off by default.
+CHECK_STATUS = os.environ.get("BISSD_CHECK_STATUS", "0") == "1"
+
+
+def _check_status(ws, stream):
+    if not CHECK_STATUS:
+        return
+    import ctypes
+    st = ctypes.c_int(0)
+    _cabi.check(_cabi.load().bissd_read_status(ws.data_ptr(), stream, ctypes.byref(st)))
+    if st.value != 0:
+        raise _cabi.BissdError(f"libbissd device status {st.value}: a device-side wait ran out; results are invalid")
 
 
 def _ptr(t):
@@ -109,6 +124,7 @@ def scan_fwd(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _cabi.check(lib.bissd_forward(ctypes.byref(args), ws.data_ptr(), nbytes, stream))
+        _check_status(ws, stream)
     return out, out_x, dt_out, cs_f, cs_b, states_f, states_b, final_f, final_b
 
 
@@ -171,6 +187,7 @@ def scan_bwd(dout: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, A: torch.Ten
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _cabi.check(lib.bissd_backward(ctypes.byref(args), ws.data_ptr(), nbytes, stream))
+        _check_status(ws, stream)
     return dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinit_f, dinit_b
 
 

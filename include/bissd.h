@@ -140,6 +140,12 @@ int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace
 /* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
 const char *bissd_kernel_path(const bissd_problem *p);
 
+/* Copies the device status word of `workspace` (written by the last pass that used it) to *status_out and
+ * WAITS for `stream` - the one call in this library that synchronises.  0 = no device-side wait ran out.  The
+ * tensor-core kernels bound every wait on an mbarrier; when one gives up the kernel records it here, frees its
+ * tensor memory and returns, and the results of that pass are invalid.  No reference counterpart. */
+int bissd_read_status(const void *workspace, void *stream, int *status_out);
+
 /* ---- self test -------------------------------------------------------------------------------------------- */
 
 /* Runs C[128][n] = A * B^T (fp32 result) on the library's tcgen05 block-GEMM engine with one CTA, so a test can

@@ -12,6 +12,9 @@ for p in (ROOT, PKG):
     if p not in sys.path:
         sys.path.insert(0, p)
 
+# make every operator call in the tests verify the library's device status word (bounded waits that ran out)
+os.environ.setdefault("BISSD_CHECK_STATUS", "1")
+
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
 
