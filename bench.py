@@ -346,7 +346,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (for profiling runs)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the batch size (profiling captures on a reduced case; not a benchmark number)")
     args = ap.parse_args()
+    if args.batch is not None:
+        CONFIG["batch"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "tc_intra.cuh"
 #include "tc_kernels.cuh"
 #include "tc_selftest.cuh"
 
@@ -275,9 +276,23 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E), a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
             F(w.nf), F(w.nb), F(w.pf), F(w.pb)));
     }
-    BISSD_LAUNCH("dcb_kernel", simt::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), simt::TB, 0, s>>>(
-        d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB)));
-    {
+    bool intra_tc = false;
+    if constexpr (TcKernels<T>::available) {
+        if (tcp) {
+            intra_tc = true;
+            const int ntQ128 = std::min(ntQ, 128);
+            const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 3 * d.Q + tc::kTileM * 8);
+            BISSD_ALLOW(tc::dcb_kernel<T>, smem_dcb);
+            BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
+                d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+            BISSD_ALLOW(tc::intra_decay_grad<T>, smem_in);
+            BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
+                d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
+        }
+    }
+    if (!intra_tc) {
+        BISSD_LAUNCH("dcb_kernel", simt::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, w.nlt, w.nlt), simt::TB, 0, s>>>(
+            d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB)));
         const size_t smem = (3 * d.Q + 2 * simt::TILE * (d.Q + 1)) * sizeof(float);
         BISSD_ALLOW(simt::intra_decay_grad<T>, smem);
         BISSD_LAUNCH("intra_decay_grad", simt::intra_decay_grad<T><<<bch, simt::TB, smem, s>>>(

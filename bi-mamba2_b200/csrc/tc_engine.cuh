@@ -280,6 +280,21 @@ __device__ __forceinline__ bool umma_gemm(Pipe &p, uint32_t d_tmem, int n_tile, 
     return true;
 }
 
+// Issue the four K=16 MMAs of one K=64 stage whose tiles the caller has already written (and fenced with
+// fence_async_smem + a CTA barrier).  One thread calls this.  ab_fmt: 1 = bf16, 0 = f16.
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void umma_issue_stage(uint32_t d_tmem, int n_tile, int ab_fmt, const uint8_t *a_tile,
+                                                 const uint8_t *b_tile, uint32_t first_accumulate) {
+    const uint32_t idesc = instr_desc(ab_fmt, A_MN, B_MN, n_tile);
+    const uint32_t a0 = smem_u32(a_tile), b0 = smem_u32(b_tile);
+#pragma unroll
+    for (int kk = 0; kk < kStageK / 16; ++kk) {
+        const uint64_t ad = A_MN ? smem_desc(a0 + kk * 2048, 8192, 1024) : smem_desc(a0 + kk * 32, 16, 1024);
+        const uint64_t bd = B_MN ? smem_desc(b0 + kk * 2048, 8192, 1024) : smem_desc(b0 + kk * 32, 16, 1024);
+        umma(d_tmem, ad, bd, idesc, kk > 0 ? 1u : first_accumulate);
+    }
+}
+
 // Wait until every MMA issued so far has completed, so the accumulators can be read with tmem_ld32.
 __device__ __forceinline__ bool umma_drain(Pipe &p) {
     if (threadIdx.x == 0) umma_commit(&p.sh->done_bar);
