@@ -349,6 +349,7 @@ const char *bissd_strerror(int status) {
         case BISSD_ERR_LAUNCH: return "CUDA launch or API call failed";
         case BISSD_ERR_ARCH: return "device is not compute capability 10.x (B200)";
         case BISSD_ERR_PHASE: return "invalid phase mask";
+        case BISSD_ERR_TOO_LARGE: return "problem needs more scratch than the fixed array of bissd_forward_static_scratch holds";
         default: return "unknown status";
     }
 }
@@ -482,6 +483,53 @@ int bissd_forward(const bissd_fwd_args *a, void *workspace, size_t workspace_byt
         case BISSD_BF16: return forward_impl<__nv_bfloat16>(*a, d, ws, s, tcp);
         default: return forward_impl<__half>(*a, d, ws, s, tcp);
     }
+}
+
+// ---- forward pass on library-owned scratch -------------------------------------------------------------------
+// Some hosts may not allocate device memory when they reach this operator: an inference server that hands each
+// plug-in a fixed set of buffers and forbids cudaMalloc after start-up, or code that runs while the allocator is
+// locked.  For them the scratch of the forward pass lives in this fixed array, part of the library's device image:
+// every GPU context that loads libbissd holds these 16 MiB until the process exits, whether or not it uses them.
+constexpr size_t kStaticScratchBytes = BISSD_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the name g_static_scratch is only a handle for the symbol, not a device address; the address on
+// the current device comes from cudaGetSymbolAddress, asked once per device and remembered.
+static std::mutex g_static_mu;
+static void *g_static_addr[64] = {};
+
+static int static_scratch_on_current_device(void **out) {
+    int dev = -1;
+    int rc = note_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc != BISSD_OK) return rc;
+    if (dev < 0 || dev >= 64) return BISSD_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) {
+        void *ptr = nullptr;
+        rc = note_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress");
+        if (rc != BISSD_OK) return rc;
+        if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 255)) return BISSD_ERR_WORKSPACE;
+        g_static_addr[dev] = ptr;
+    }
+    *out = g_static_addr[dev];
+    return BISSD_OK;
+}
+
+int bissd_forward_static_scratch(const bissd_fwd_args *a, void *stream) {
+    if (!a) return BISSD_ERR_NULL;
+    Dims d;
+    int rc = make_dims(a->p, &d);
+    if (rc != BISSD_OK) return rc;
+    if (a->phases != BISSD_PHASE_ALL) return BISSD_ERR_PHASE;      // a split pass needs scratch the caller keeps
+    if (fwd_layout(d).total > kStaticScratchBytes) return BISSD_ERR_TOO_LARGE;
+    void *scratch = nullptr;
+    rc = static_scratch_on_current_device(&scratch);
+    if (rc != BISSD_OK) return rc;
+    // The array still holds whatever the previous call left.  Only the status word at its start is read before it
+    // is written, so that is what gets cleared; every other region is fully rewritten by the kernels that use it.
+    rc = note_cuda(cudaMemsetAsync(scratch, 0, kWsHeader, static_cast<cudaStream_t>(stream)), "cudaMemsetAsync");
+    if (rc != BISSD_OK) return rc;
+    return bissd_forward(a, scratch, kStaticScratchBytes, stream);
 }
 
 int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_bytes, void *stream) {

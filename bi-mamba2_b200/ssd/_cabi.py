@@ -47,7 +47,11 @@ class BwdArgs(C.Structure):
 
 
 EXPORTS = ("bissd_abi_version", "bissd_strerror", "bissd_last_cuda_error", "bissd_workspace_bytes", "bissd_forward",
-           "bissd_backward", "bissd_kernel_path", "bissd_launch_count", "bissd_trace_enable", "bissd_trace_read", "bissd_selftest_gemm", "bissd_read_status")
+           "bissd_backward", "bissd_kernel_path", "bissd_launch_count", "bissd_trace_enable", "bissd_trace_read", "bissd_selftest_gemm", "bissd_read_status",
+           "bissd_forward_static_scratch")
+
+STATIC_SCRATCH_BYTES = 16 << 20      # BISSD_STATIC_SCRATCH_BYTES
+ERR_TOO_LARGE = -9
 
 _lib = None
 
@@ -83,6 +87,8 @@ def load():
     lib.bissd_trace_read.restype = C.c_int
     lib.bissd_trace_read.argtypes = [C.c_char_p, C.c_size_t, C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_int,
                                      C.POINTER(C.c_int)]
+    lib.bissd_forward_static_scratch.restype = C.c_int
+    lib.bissd_forward_static_scratch.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.bissd_read_status.restype = C.c_int
     lib.bissd_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]
     lib.bissd_selftest_gemm.restype = C.c_int

@@ -39,7 +39,8 @@ typedef enum bissd_status {
     BISSD_ERR_WORKSPACE = -5,     /* workspace smaller than bissd_workspace_bytes() reports */
     BISSD_ERR_LAUNCH = -6,        /* a CUDA launch or API call failed (see bissd_last_cuda_error) */
     BISSD_ERR_ARCH = -7,          /* the current device is not compute capability 10.x */
-    BISSD_ERR_PHASE = -8          /* invalid phase mask */
+    BISSD_ERR_PHASE = -8,         /* invalid phase mask */
+    BISSD_ERR_TOO_LARGE = -9      /* needs more scratch than bissd_forward_static_scratch's fixed array holds */
 } bissd_status;
 
 typedef enum bissd_dtype { BISSD_F32 = 0, BISSD_BF16 = 1, BISSD_F16 = 2 } bissd_dtype;
@@ -133,6 +134,22 @@ int bissd_workspace_bytes(const bissd_problem *p, size_t *fwd_bytes, size_t *bwd
 
 /* Forward pass.  workspace must be 256-byte aligned. */
 int bissd_forward(const bissd_fwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Forward pass for callers that cannot allocate device memory at the point where they run this operator - for
+ * example a serving process that gives every plug-in its buffers up front and forbids cudaMalloc afterwards, or a
+ * host whose allocator is locked while the model runs.  It has no counterpart in the reference (whose wrappers
+ * call torch.empty freely).  Same arguments and results as bissd_forward with phases == BISSD_PHASE_ALL, but the
+ * scratch is a fixed array of BISSD_STATIC_SCRATCH_BYTES inside the library's device image, so:
+ *   - a problem whose bissd_workspace_bytes() forward size exceeds that limit is refused with BISSD_ERR_TOO_LARGE;
+ *   - every GPU context that loads the library holds the array until the process exits;
+ *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress) and remembers it:
+ *     make that first call with the intended device current, and before starting any stream capture;
+ *   - all calls on a device share the one array (it keeps the previous call's contents; the status word at its
+ *     start is cleared on entry, everything else is rewritten before it is read), so two calls whose GPU work can
+ *     overlap - different streams, or threads - race on it: serialise them.
+ * The function itself calls no cudaMalloc / cudaFree or any other allocating routine. */
+#define BISSD_STATIC_SCRATCH_BYTES ((size_t)16 << 20)
+int bissd_forward_static_scratch(const bissd_fwd_args *args, void *stream);
 
 /* Backward pass. */
 int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
