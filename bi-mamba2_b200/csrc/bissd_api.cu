@@ -181,9 +181,15 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
         if constexpr (TcKernels<T>::available) {
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
-                BISSD_ALLOW((tc::state_gemm<T, 0>), smem);
-                BISSD_LAUNCH("tc_chunk_state", tc::state_gemm<T, 0><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
-                    d, Bm, x, z, a.dt_out, a.cs_f, a.cs_b, loc, status));
+                if (ntP <= 64) {
+                    BISSD_ALLOW((tc::state_gemm<T, 0, 2>), smem);
+                    BISSD_LAUNCH("tc_chunk_state", tc::state_gemm<T, 0, 2><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                        d, Bm, x, z, a.dt_out, a.cs_f, a.cs_b, loc, status));
+                } else {
+                    BISSD_ALLOW((tc::state_gemm<T, 0, 8>), smem);
+                    BISSD_LAUNCH("tc_chunk_state", tc::state_gemm<T, 0, 8><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                        d, Bm, x, z, a.dt_out, a.cs_f, a.cs_b, loc, status));
+                }
             }
         }
         if (!tcp) {
@@ -203,9 +209,15 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                 const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_sc = tc::smem_bytes(ntP, 3 * d.Q);
                 BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
                 BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, status));
-                BISSD_ALLOW(tc::chunk_scan<T>, smem_sc);
-                BISSD_LAUNCH("tc_chunk_scan", tc::chunk_scan<T><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_sc, s>>>(
-                    d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x), status));
+                if (ntP <= 64) {
+                    BISSD_ALLOW((tc::chunk_scan<T, 2>), smem_sc);
+                    BISSD_LAUNCH("tc_chunk_scan", tc::chunk_scan<T, 2><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_sc, s>>>(
+                        d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x), status));
+                } else {
+                    BISSD_ALLOW((tc::chunk_scan<T, 8>), smem_sc);
+                    BISSD_LAUNCH("tc_chunk_scan", tc::chunk_scan<T, 8><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_sc, s>>>(
+                        d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x), status));
+                }
             }
         }
         if (!tcp) {
@@ -234,9 +246,15 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         if constexpr (TcKernels<T>::available) {
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
-                BISSD_ALLOW((tc::state_gemm<T, 1>), smem);
-                BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
-                    d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                if (ntP <= 64) {
+                    BISSD_ALLOW((tc::state_gemm<T, 1, 2>), smem);
+                    BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1, 2><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                        d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                } else {
+                    BISSD_ALLOW((tc::state_gemm<T, 1, 8>), smem);
+                    BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1, 8><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
+                        d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                }
             }
         }
         if (!tcp) {
@@ -259,9 +277,15 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), status));
-            BISSD_ALLOW(tc::dx_kernel<T>, smem_dx);
-            BISSD_LAUNCH("tc_dx", tc::dx_kernel<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
-                d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+            if (ntP <= 64) {
+                BISSD_ALLOW((tc::dx_kernel<T, 2>), smem_dx);
+                BISSD_LAUNCH("tc_dx", tc::dx_kernel<T, 2><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
+                    d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+            } else {
+                BISSD_ALLOW((tc::dx_kernel<T, 8>), smem_dx);
+                BISSD_LAUNCH("tc_dx", tc::dx_kernel<T, 8><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
+                    d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+            }
             BISSD_ALLOW(tc::dbc_states<T>, smem_n);
             BISSD_LAUNCH("tc_dbc_states", tc::dbc_states<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_n, s>>>(
                 d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E), a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),

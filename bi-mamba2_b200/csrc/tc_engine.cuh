@@ -218,46 +218,71 @@ __device__ __forceinline__ void pipe_destroy(Pipe &p, uint32_t ncols) {
 //   fb(r, k): same for B, r in [0, n_tile).  Functors return zeros outside the problem.
 //   n_tile: multiple of 16, 16..256.   first_accumulate: 0 overwrites the accumulator at the first k-step.
 // Returns false (uniformly over the CTA) if a wait ran out; the status word is set.
-template <class T, bool A_MN, bool B_MN, class FA, class FB>
+template <class T, bool A_MN, bool B_MN, int BCH = 8, class FA, class FB>
 __device__ __forceinline__ bool umma_gemm(Pipe &p, uint32_t d_tmem, int n_tile, int K, uint32_t first_accumulate, FA fa,
                                           FB fb) {
+    // BCH: 16-byte pieces of the B tile each thread stages per step; needs n_tile <= 32 * BCH.
     const uint32_t idesc = instr_desc(AbFmt<T>::v, A_MN, B_MN, n_tile);
     const int tid = threadIdx.x;
+    const int nb_chunks = n_tile * 8;
+    const int nrc = n_tile >> 3;
+    uint4 ra[4], rb[BCH];
+    // The operand pieces of step k0+64 are fetched into registers while step k0 is being handed to the tensor core,
+    // so the global-memory latency of one step hides behind the barrier and the MMA issue of the previous one.
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int q = tid + i * kThreads;
+            if (!A_MN) ra[i] = fa(q >> 3, k0 + (q & 7) * 8);
+            else ra[i] = fa((q & 15) * 8, k0 + (q >> 4));
+        }
+#pragma unroll
+        for (int i = 0; i < BCH; ++i) {
+            const int q = tid + i * kThreads;
+            if (q < nb_chunks) {
+                if (!B_MN) rb[i] = fb(q >> 3, k0 + (q & 7) * 8);
+                else rb[i] = fb((q % nrc) * 8, k0 + q / nrc);
+            }
+        }
+    };
+    auto stash = [&](int st) {
+        uint8_t *as = p.a_stage[st], *bs = p.b_stage[st];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int q = tid + i * kThreads;
+            if (!A_MN) {
+                const int r = q >> 3, c = q & 7;
+                *reinterpret_cast<uint4 *>(as + r * 128 + ((c ^ (r & 7)) << 4)) = ra[i];
+            } else {
+                const int rc = q & 15, k = q >> 4;          // rc: 8-row chunk index
+                *reinterpret_cast<uint4 *>(as + (rc >> 3) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 +
+                                           (((rc & 7) ^ (k & 7)) << 4)) = ra[i];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < BCH; ++i) {
+            const int q = tid + i * kThreads;
+            if (q < nb_chunks) {
+                if (!B_MN) {
+                    const int r = q >> 3, c = q & 7;
+                    *reinterpret_cast<uint4 *>(bs + r * 128 + ((c ^ (r & 7)) << 4)) = rb[i];
+                } else {
+                    const int rc = q % nrc, k = q / nrc;
+                    *reinterpret_cast<uint4 *>(bs + (rc >> 3) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 +
+                                               (((rc & 7) ^ (k & 7)) << 4)) = rb[i];
+                }
+            }
+        }
+    };
+    fetch(0);
     for (int k0 = 0; k0 < K; k0 += kStageK) {
         const int st = p.iter & 1;
         bool ok = true;
         if (p.iter >= 2) ok = mbar_wait(&p.sh->free_bar[st], ((p.iter >> 1) - 1) & 1);
         if (ok) {
-            uint8_t *as = p.a_stage[st];
-            if (!A_MN) {
-#pragma unroll
-                for (int q = tid; q < kTileM * 8; q += kThreads) {
-                    const int r = q >> 3, c = q & 7;
-                    *reinterpret_cast<uint4 *>(as + r * 128 + ((c ^ (r & 7)) << 4)) = fa(r, k0 + c * 8);
-                }
-            } else {
-#pragma unroll
-                for (int q = tid; q < (kTileM / 8) * kStageK; q += kThreads) {
-                    const int rc = q & 15, k = q >> 4;      // rc: 8-row chunk index
-                    *reinterpret_cast<uint4 *>(as + (rc >> 3) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 +
-                                               (((rc & 7) ^ (k & 7)) << 4)) = fa(rc * 8, k0 + k);
-                }
-            }
-            uint8_t *bs = p.b_stage[st];
-            if (!B_MN) {
-                for (int q = tid; q < n_tile * 8; q += kThreads) {
-                    const int r = q >> 3, c = q & 7;
-                    *reinterpret_cast<uint4 *>(bs + r * 128 + ((c ^ (r & 7)) << 4)) = fb(r, k0 + c * 8);
-                }
-            } else {
-                const int nrc = n_tile >> 3;
-                for (int q = tid; q < nrc * kStageK; q += kThreads) {
-                    const int rc = q % nrc, k = q / nrc;
-                    *reinterpret_cast<uint4 *>(bs + (rc >> 3) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 +
-                                               (((rc & 7) ^ (k & 7)) << 4)) = fb(rc * 8, k0 + k);
-                }
-            }
+            stash(st);
             fence_async_smem();
+            if (k0 + kStageK < K) fetch(k0 + kStageK);
         }
         ok = __syncthreads_and(ok);
         if (!ok) {

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kThreads) dcb_kernel(Dims d, View x, View z, V
         auto fb = [&](int r, int k) -> uint4 {
             return (s0 + r < lim && k < d.P) ? ld8v<T>(x, b, c * Q + s0 + r, h, k) : zero8();
         };
-        ok = umma_gemm<T, false, false>(p, p.tmem, nt, d.P, 0u, fa, fb);     // its barrier also publishes the tables
+        ok = umma_gemm<T, false, false, 4>(p, p.tmem, nt, d.P, 0u, fa, fb);  // its barrier also publishes the tables
         ok = ok && umma_drain(p);
         if (ok) {
             const float fl = (l < lim) ? sf[l] : 0.f, bl = (l < lim) ? sb[l] : 0.f;

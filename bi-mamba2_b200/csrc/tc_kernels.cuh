@@ -102,8 +102,8 @@ __global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, flo
 //   MODE 0 (chunk_state): out[dir][p][n] = sum_l (B[l,n] Delta[l] e^{T-cs_dir[l]}) x[l,p]
 //   MODE 1 (dstates):     out[dir][p][n] = sum_l (C[l,n] e^{cs_dir[l]})            g[l,p]
 // D rows m = dir*N + n, D columns p.   grid (b*nc*H, ceil(2N/128)); n_tile = round16(P); tables: 2*Q floats.
-template <class T, int MODE>
-__global__ void __launch_bounds__(kThreads) state_gemm(Dims d, View rowsrc /* B or C */, View colsrc /* x or dout */,
+template <class T, int MODE, int BCH>
+__global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) state_gemm(Dims d, View rowsrc /* B or C */, View colsrc /* x or dout */,
                                                        View z, const float *dt_out, const float *cs_f,
                                                        const float *cs_b, float *out, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kThreads) state_gemm(Dims d, View rowsrc /* B 
         if (r >= d.P || k >= lim) return zero8();
         return MODE == 0 ? ld8v<T>(colsrc, b, c * d.Q + k, h, r) : gate8<T>(d, colsrc, z, b, c * d.Q + k, h, r);
     };
-    bool ok = umma_gemm<T, true, true>(p, p.tmem, nt, d.Q, 0u, fa, fb);
+    bool ok = umma_gemm<T, true, true, BCH>(p, p.tmem, nt, d.Q, 0u, fa, fb);
     ok = ok && umma_drain(p);
     if (ok) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(kThreads) state_gemm(Dims d, View rowsrc /* B 
 // Forward output (see simt::chunk_scan for the formula).  One accumulator, three K-segments:
 //   [C e^{cs_f} | S_f]  [C e^{cs_b} | S_b]  [CB Delta (L_f+L_b) | x]
 // grid (b*nc*H, ceil(Q/128)); n_tile = round16(P); tables: 3*Q floats.
-template <class T>
-__global__ void __launch_bounds__(kThreads) chunk_scan(Dims d, View x, View Cm, View z, const float *D,
+template <class T, int BCH>
+__global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) chunk_scan(Dims d, View x, View Cm, View z, const float *D,
                                                        const float *dt_out, const float *cs_f, const float *cs_b,
                                                        const float *CB, const void *states_f, const void *states_b,
                                                        MutView out, MutView out_x, int *status) {
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kThreads) chunk_scan(Dims d, View x, View Cm, 
         auto fb = [&](int r, int k) -> uint4 {
             return (r < d.P && k < N) ? ldg8(st, st_base + (long long)r * N + k) : zero8();
         };
-        ok = umma_gemm<T, false, false>(p, p.tmem, nt, N, dir ? 1u : 0u, fa, fb);
+        ok = umma_gemm<T, false, false, BCH>(p, p.tmem, nt, N, dir ? 1u : 0u, fa, fb);
     }
     if (ok) {
         auto fa = [&](int r, int k) -> uint4 {                          // K-major: M[l][s..s+7]
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kThreads) chunk_scan(Dims d, View x, View Cm, 
         auto fb = [&](int r, int k) -> uint4 {                          // MN-major: x[s][p..p+7]
             return (r < d.P && k < lim) ? ld8v<T>(x, b, c * Q + k, h, r) : zero8();
         };
-        ok = umma_gemm<T, false, true>(p, p.tmem, nt, Q, 1u, fa, fb);
+        ok = umma_gemm<T, false, true, BCH>(p, p.tmem, nt, Q, 1u, fa, fb);
     }
     ok = ok && umma_drain(p);
     if (ok) {
@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(kThreads) chunk_scan(Dims d, View x, View Cm, 
 // dx, ddt_out, dz, dD partials (see simt::dx_kernel).  One accumulator, three K-segments:
 //   [B e^{T-cs_f} | E_f]  [B e^{T-cs_b} | E_b]  [CB^T (L_f+L_b)^T | g]
 // grid (b*nc*H, ceil(Q/128)); n_tile = round16(P); tables: 3*Q floats.
-template <class T>
-__global__ void __launch_bounds__(kThreads) dx_kernel(Dims d, View x, View Bm, View z, View dout, View out_x,
+template <class T, int BCH>
+__global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) dx_kernel(Dims d, View x, View Bm, View z, View dout, View out_x,
                                                       const float *D, const float *dt_out, const float *cs_f,
                                                       const float *cs_b, const float *CB, const float *E, void *dx,
                                                       void *dz, float *ddt_out, float *dDpart, int *status) {
@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(kThreads) dx_kernel(Dims d, View x, View Bm, V
             return scale8<T>(ld8v<T>(Bm, b, c * Q + l, g, k), __expf(T0 - cs[l]));
         };
         auto fb = [&](int r, int k) -> uint4 { return (r < d.P && k < N) ? pack8f<T>(Ed + (long long)r * N + k) : zero8(); };
-        ok = umma_gemm<T, false, false>(p, p.tmem, nt, N, dir ? 1u : 0u, fa, fb);
+        ok = umma_gemm<T, false, false, BCH>(p, p.tmem, nt, N, dir ? 1u : 0u, fa, fb);
     }
     if (ok) {
         auto fa = [&](int r, int k) -> uint4 {                          // MN-major: rows l..l+7 at column s = k
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(kThreads) dx_kernel(Dims d, View x, View Bm, V
         auto fb = [&](int r, int k) -> uint4 {                          // MN-major: g[s][p..p+7]
             return (r < d.P && k < lim) ? gate8<T>(d, dout, z, b, c * Q + k, h, r) : zero8();
         };
-        ok = umma_gemm<T, true, true>(p, p.tmem, nt, Q, 1u, fa, fb);
+        ok = umma_gemm<T, true, true, BCH>(p, p.tmem, nt, Q, 1u, fa, fb);
     }
     ok = ok && umma_drain(p);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(kThreads) dbc_states(Dims d, View x, View Bm, 
                 if (which) return ldg8(dir ? states_b : states_f, o);
                 return pack8f<T>(E + dir * per_dir + o);
             };
-            ok = umma_gemm<T, false, true>(p, p.tmem + dir * 128, nt, d.P, 0u, fa, fb);
+            ok = umma_gemm<T, false, true, 4>(p, p.tmem + dir * 128, nt, d.P, 0u, fa, fb);
         }
         ok = ok && umma_drain(p);
         float rs_f = 0.f, rs_b = 0.f;
@@ -561,12 +561,12 @@ __global__ void __launch_bounds__(kThreads) bmm_bwd(Dims d, View Bm, View Cm, co
         auto fa = [&](int rr, int k) -> uint4 {                         // MN-major: dCB[l = k][s..s+7]
             return (r0 + rr < Q && k < lim) ? pack8f<T>(dcb + (long long)k * Q + r0 + rr) : zero8();
         };
-        ok = umma_gemm<T, true, true>(p, p.tmem, nt, Q, 0u, fa, fb);
+        ok = umma_gemm<T, true, true, 4>(p, p.tmem, nt, Q, 0u, fa, fb);
     } else {
         auto fa = [&](int rr, int k) -> uint4 {                         // K-major: dCB[l][s..s+7]
             return (r0 + rr < lim && k < Q) ? pack8f<T>(dcb + (long long)(r0 + rr) * Q + k) : zero8();
         };
-        ok = umma_gemm<T, false, true>(p, p.tmem, nt, Q, 0u, fa, fb);
+        ok = umma_gemm<T, false, true, 4>(p, p.tmem, nt, Q, 0u, fa, fb);
     }
     ok = ok && umma_drain(p);
     if (ok) {
