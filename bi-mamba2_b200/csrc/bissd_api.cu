@@ -11,6 +11,7 @@
 #include "simt_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_kernels.cuh"
+#include "tc_scan_tma.cuh"
 #include "tc_selftest.cuh"
 
 namespace bissd {
@@ -152,7 +153,12 @@ static bool force_simt() {
     return v;
 }
 
-#define BISSD_ALLOW(kernel, bytes)                   \
+static bool no_tma() {   // BISSD_NO_TMA=1: keep the thread-staged tcgen05 kernels (for A/B comparisons)
+    static const bool v = [] { const char *e = getenv("BISSD_NO_TMA"); return e && e[0] == '1'; }();
+    return v;
+}
+
+#define BISSD_ALLOW(kernel, bytes)                  \
     do {                                             \
         int rc_ = allow_smem(kernel, bytes);         \
         if (rc_ != BISSD_OK) return rc_;             \
@@ -209,7 +215,28 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                 const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_sc = tc::smem_bytes(ntP, 3 * d.Q);
                 BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
                 BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, status));
-                if (ntP <= 64) {
+                bool tma_done = false;
+                if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+                    CUtensorMap mC, mSf, mSb, mX;
+                    const unsigned long long dC[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                    const unsigned long long sC[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+                    const unsigned bC[4] = {64, 1, 128, 1};
+                    const unsigned long long dX[4] = {(unsigned long long)d.P, (unsigned long long)d.H, (unsigned long long)d.L, (unsigned long long)d.b};
+                    const unsigned long long sX[3] = {(unsigned long long)a.x.stride_head * 2, (unsigned long long)a.x.stride_seq * 2, (unsigned long long)a.x.stride_batch * 2};
+                    const unsigned bX[4] = {64, 1, (unsigned)d.Q, 1};
+                    const unsigned long long rows = (unsigned long long)d.b * d.nc * d.H * d.P;
+                    if (tc::make_map4(&mC, a.p.x_dtype, a.C.ptr, dC, sC, bC) && tc::make_map4(&mX, a.p.x_dtype, a.x.ptr, dX, sX, bX) &&
+                        tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
+                        tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P)) {
+                        const size_t smem_t = tc::scan_tma_smem(d.P, d.N, d.Q);
+                        BISSD_ALLOW(tc::chunk_scan_tma<T>, smem_t);
+                        BISSD_LAUNCH("tc_chunk_scan_tma", tc::chunk_scan_tma<T><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_t, s>>>(
+                            d, mC, mSf, mSb, mX, x, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, mview_of(a.out), mview_of(a.out_x), status));
+                        tma_done = true;
+                    }
+                }
+                if (tma_done) {
+                } else if (ntP <= 64) {
                     BISSD_ALLOW((tc::chunk_scan<T, 2>), smem_sc);
                     BISSD_LAUNCH("tc_chunk_scan", tc::chunk_scan<T, 2><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_sc, s>>>(
                         d, x, Cm, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, a.states_f, a.states_b, mview_of(a.out), mview_of(a.out_x), status));
