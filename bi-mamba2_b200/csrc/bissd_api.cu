@@ -11,6 +11,7 @@
 #include "simt_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_kernels.cuh"
+#include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
 #include "tc_selftest.cuh"
 
@@ -88,7 +89,7 @@ struct FwdWs {
     size_t loc, cb, total;
 };
 struct BwdWs {
-    size_t cb, gloc, E, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    size_t cb, cbt, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
     int nblk, nlt, nsplit;
 };
 
@@ -114,6 +115,9 @@ static BwdWs bwd_layout(const Dims &d) {
     w.cb = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
     w.gloc = take(2 * st * 4);
     w.E = take(2 * st * 4);
+    w.E16 = take(2 * st * 2);                                        // passed state gradients in the input dtype
+    w.g = take((size_t)d.b * d.L * d.H * d.P * 2);                   // gated output gradient dout * silu(z)
+    w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
     w.ddt_out = take(hq * 4);
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
@@ -214,7 +218,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
             if (tcp) {
                 const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_sc = tc::smem_bytes(ntP, 3 * d.Q);
                 BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
-                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, status));
+                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, nullptr, status));
                 bool tma_done = false;
                 if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                     CUtensorMap mC, mSf, mSb, mX;
@@ -267,20 +271,34 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     const size_t q3 = 3 * d.Q * sizeof(float);
     const int ntP = tc::round_up(d.P, 16), ntQ = tc::round_up(d.Q, 16), ntN = std::min(tc::round_up(d.N, 16), 128);
     const int nlt_tc = ceil_div(d.Q, tc::kTileM);
+    // Tensor-core family: the gate is applied once (gate_bwd writes g = dout * silu(z) and dz); every later kernel
+    // then sees an ungated problem whose output gradient is g.
+    Dims dg = d;
+    View gv = dout;
+    void *E16 = ws + w.E16;
+    if (tcp && d.has_z) {
+        dg.has_z = 0;
+        gv = View{ws + w.g, (long long)d.L * d.H * d.P, (long long)d.H * d.P, (long long)d.P};
+    }
     if (a.phases & BISSD_PHASE_LOCAL) {
         int rc = note_cuda(cudaMemsetAsync(ws, 0, kWsHeader, s), "cudaMemsetAsync");
         if (rc != BISSD_OK) return rc;
         if constexpr (TcKernels<T>::available) {
+            if (tcp && d.has_z) {
+                const long long chunks = (long long)d.b * d.L * d.H * (d.P / 8);
+                BISSD_LAUNCH("gate_bwd", tc::gate_bwd<T><<<(unsigned)((chunks + 255) / 256), 256, 0, s>>>(
+                    d, dout, z, out_x, ws + w.g, a.dz));
+            }
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
                 if (ntP <= 64) {
                     BISSD_ALLOW((tc::state_gemm<T, 1, 2>), smem);
                     BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1, 2><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
-                        d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                        dg, Cm, gv, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
                 } else {
                     BISSD_ALLOW((tc::state_gemm<T, 1, 8>), smem);
                     BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1, 8><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
-                        d, Cm, dout, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                        dg, Cm, gv, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
                 }
             }
         }
@@ -292,7 +310,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.dfinal_f || a.dfinal_b);
     if (need_pass) {
         BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), simt::TB, 0, s>>>(
-            d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, F(w.E), F(w.dTpart), a.dinit_f, a.dinit_b));
+            d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, tcp ? nullptr : F(w.E), tcp ? E16 : nullptr, F(w.dTpart), a.dinit_f, a.dinit_b));
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
@@ -303,19 +321,42 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             part_heads = d.G;
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
-            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), status));
-            if (ntP <= 64) {
+            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), F(w.cbt), status));
+            bool dx_done = false;
+            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+                CUtensorMap mB, mEf, mEb, mG;
+                const unsigned long long dB4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
+                const unsigned bB4[4] = {64, 1, 128, 1};
+                const unsigned long long dG4[4] = {(unsigned long long)d.P, (unsigned long long)d.H, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sG4[3] = {(unsigned long long)gv.sh * 2, (unsigned long long)gv.sl * 2, (unsigned long long)gv.sb * 2};
+                const unsigned bG4[4] = {64, 1, (unsigned)d.Q, 1};
+                const unsigned long long rows = (unsigned long long)d.b * d.nc * d.H * d.P;
+                const char *e16 = static_cast<const char *>(E16);
+                if (tc::make_map4(&mB, a.p.x_dtype, a.B.ptr, dB4, sB4, bB4) && tc::make_map4(&mG, a.p.x_dtype, gv.ptr, dG4, sG4, bG4) &&
+                    tc::make_map2(&mEf, a.p.x_dtype, e16, d.N, rows, 64, d.P) &&
+                    tc::make_map2(&mEb, a.p.x_dtype, e16 + rows * d.N * 2, d.N, rows, 64, d.P)) {
+                    const size_t smem_t = tc::dx_tma_smem(d.P, d.N, d.Q);
+                    BISSD_ALLOW(tc::dx_tma<T>, smem_t);
+                    BISSD_LAUNCH("tc_dx_tma", tc::dx_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_t, s>>>(
+                        d, mB, mEf, mEb, mG, x, gv, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cbt), a.dx, F(w.ddt_out), F(w.nf), F(w.nb),
+                        F(w.dDpart), status));
+                    dx_done = true;
+                }
+            }
+            if (dx_done) {
+            } else if (ntP <= 64) {
                 BISSD_ALLOW((tc::dx_kernel<T, 2>), smem_dx);
                 BISSD_LAUNCH("tc_dx", tc::dx_kernel<T, 2><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
-                    d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+                    dg, x, Bm, z, gv, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), E16, a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
             } else {
                 BISSD_ALLOW((tc::dx_kernel<T, 8>), smem_dx);
                 BISSD_LAUNCH("tc_dx", tc::dx_kernel<T, 8><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
-                    d, x, Bm, z, dout, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.E), a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
+                    dg, x, Bm, z, gv, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), E16, a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
             }
             BISSD_ALLOW(tc::dbc_states<T>, smem_n);
             BISSD_LAUNCH("tc_dbc_states", tc::dbc_states<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_n, s>>>(
-                d, x, Bm, Cm, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.E), a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
+                dg, x, Bm, Cm, z, gv, a.dt_out, a.cs_f, a.cs_b, E16, a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
                 F(w.nf), F(w.nb), F(w.pf), F(w.pb), status));
         }
     }
@@ -335,10 +376,10 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 3 * d.Q + tc::kTileM * 8);
             BISSD_ALLOW(tc::dcb_kernel<T>, smem_dcb);
             BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
-                d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+                dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
             BISSD_ALLOW(tc::intra_decay_grad<T>, smem_in);
             BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
-                d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
+                dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
         }
     }
     if (!intra_tc) {

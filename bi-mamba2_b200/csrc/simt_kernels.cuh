@@ -395,7 +395,7 @@ template <class T>
 __global__ void __launch_bounds__(TB) state_passing_bwd(Dims d, const float *gloc, const void *states_f,
                                                         const void *states_b, const float *cs_f, const float *cs_b,
                                                         const float *dfinal_f, const float *dfinal_b, float *E,
-                                                        float *dTpart, float *dinit_f, float *dinit_b) {
+                                                        void *E16, float *dTpart, float *dinit_f, float *dinit_b) {
     __shared__ float red[TB / 32];
     const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
     const int dir = blockIdx.z;
@@ -417,7 +417,8 @@ __global__ void __launch_bounds__(TB) state_passing_bwd(Dims d, const float *glo
         const float dec = expf(dir ? cs_b[cb] : cs_f[cb + d.Q - 1]);
         float part = 0.f;
         if (on) {
-            Ep[off] = run;
+            if (E) Ep[off] = run;                                    // fp32 copy for the CUDA-core kernels
+            if (E16) st<T>(E16, dir * per_dir + off, run);           // input-dtype copy for the tensor-core kernels
             part = dec * ld<T>(states, off) * run;
             run = dec * run + gp[off];
         }

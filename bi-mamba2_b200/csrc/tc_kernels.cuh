@@ -63,7 +63,7 @@ template <class T> __device__ __forceinline__ uint4 pack8f(const float *p) {
 // ---------------------------------------------------------------------------------------------------------
 // CB[b,c,g,l,s] = C[l].B[s]  (fp32).   grid (b*nc*G, ceil(Q/128)); n_tile = round16(Q); tables: none.
 template <class T>
-__global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, float *CB, int *status) {
+__global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, float *CB, float *CBt, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
     const int nt = round_up(d.Q, 16);
@@ -91,6 +91,12 @@ __global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, flo
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     if (c0 + j < d.Q) *reinterpret_cast<float4 *>(out + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (CBt) {                                              // transposed copy: lanes write consecutive l
+                    float *ot = CBt + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q + l;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < d.Q) ot[(long long)(c0 + j) * d.Q] = v[j];
+                }
             }
         }
     }
@@ -276,7 +282,7 @@ __global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) chunk_scan(Dims d,
 template <class T, int BCH>
 __global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) dx_kernel(Dims d, View x, View Bm, View z, View dout, View out_x,
                                                       const float *D, const float *dt_out, const float *cs_f,
-                                                      const float *cs_b, const float *CB, const float *E, void *dx,
+                                                      const float *cs_b, const float *CB, const void *E16, void *dx,
                                                       void *dz, float *ddt_out, float *dDpart, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
@@ -308,13 +314,13 @@ __global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) dx_kernel(Dims d, 
     for (int dir = 0; dir < 2 && ok; ++dir) {
         const float *cs = dir ? sb : sf;
         const float T0 = dir ? Tb : Tf;
-        const float *Ed = E + dir * per_dir + st_base;
+        const long long eoff = dir * per_dir + st_base;
         auto fa = [&](int r, int k) -> uint4 {
             const int l = l0 + r;
             if (l >= lim || k >= N) return zero8();
             return scale8<T>(ld8v<T>(Bm, b, c * Q + l, g, k), __expf(T0 - cs[l]));
         };
-        auto fb = [&](int r, int k) -> uint4 { return (r < d.P && k < N) ? pack8f<T>(Ed + (long long)r * N + k) : zero8(); };
+        auto fb = [&](int r, int k) -> uint4 { return (r < d.P && k < N) ? ldg8(E16, eoff + (long long)r * N + k) : zero8(); };
         ok = umma_gemm<T, false, false, BCH>(p, p.tmem, nt, N, dir ? 1u : 0u, fa, fb);
     }
     if (ok) {
@@ -417,7 +423,7 @@ __global__ void __launch_bounds__(kThreads, BCH <= 2 ? 2 : 1) dx_kernel(Dims d, 
 template <class T>
 __global__ void __launch_bounds__(kThreads) dbc_states(Dims d, View x, View Bm, View Cm, View z, View dout,
                                                        const float *dt_out, const float *cs_f, const float *cs_b,
-                                                       const float *E, const void *states_f, const void *states_b,
+                                                       const void *E16, const void *states_f, const void *states_b,
                                                        float *dB_part, float *dC_part, float *nf, float *nb, float *pf,
                                                        float *pb, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -460,7 +466,7 @@ __global__ void __launch_bounds__(kThreads) dbc_states(Dims d, View x, View Bm, 
                 if (rr >= nvalid || k >= d.P) return zero8();
                 const long long o = st_base + (long long)k * N + n0 + rr;
                 if (which) return ldg8(dir ? states_b : states_f, o);
-                return pack8f<T>(E + dir * per_dir + o);
+                return ldg8(E16, dir * per_dir + o);
             };
             ok = umma_gemm<T, false, true, 4>(p, p.tmem + dir * 128, nt, d.P, 0u, fa, fb);
         }
