@@ -11,6 +11,7 @@
 #include "simt_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_kernels.cuh"
+#include "tc_dcb_tma.cuh"
 #include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
 #include "tc_selftest.cuh"
@@ -374,9 +375,26 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             intra_tc = true;
             const int ntQ128 = std::min(ntQ, 128);
             const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 3 * d.Q + tc::kTileM * 8);
-            BISSD_ALLOW(tc::dcb_kernel<T>, smem_dcb);
-            BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
-                dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+            bool dcb_done = false;
+            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+                CUtensorMap mG, mX;
+                const unsigned long long dX4[4] = {(unsigned long long)d.P, (unsigned long long)d.H, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sX4[3] = {(unsigned long long)a.x.stride_head * 2, (unsigned long long)a.x.stride_seq * 2, (unsigned long long)a.x.stride_batch * 2};
+                const unsigned long long sG4[3] = {(unsigned long long)gv.sh * 2, (unsigned long long)gv.sl * 2, (unsigned long long)gv.sb * 2};
+                const unsigned bx4[4] = {64, 1, 128, 1};
+                if (tc::make_map4(&mX, a.p.x_dtype, a.x.ptr, dX4, sX4, bx4) && tc::make_map4(&mG, a.p.x_dtype, gv.ptr, dX4, sG4, bx4)) {
+                    const size_t smem_t = tc::dcb_tma_smem(d.P, d.Q);
+                    BISSD_ALLOW(tc::dcb_tma<T>, smem_t);
+                    BISSD_LAUNCH("tc_dcb_tma", tc::dcb_tma<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_t, s>>>(
+                        d, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+                    dcb_done = true;
+                }
+            }
+            if (!dcb_done) {
+                BISSD_ALLOW(tc::dcb_kernel<T>, smem_dcb);
+                BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
+                    dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+            }
             BISSD_ALLOW(tc::intra_decay_grad<T>, smem_in);
             BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
                 dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));

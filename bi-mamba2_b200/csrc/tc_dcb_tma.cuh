@@ -1,0 +1,150 @@
+// dCB[l,s] = sum_{h in group} (g_h[l].x_h[s]) Delta_h[s] ([s<=l] e^{cs_f[l]-cs_f[s]} + [s>=l] e^{cs_b[l]-cs_b[s]}),
+// TMA-fed and software-pipelined over the heads of a group (see simt::dcb_kernel for the reference line numbers).
+//
+// Per CTA: one (batch, chunk, group), a 128 x 128 tile of (l, s).  For every head the g and x tiles arrive by TMA into a
+// three-deep ring; G2_h = g_h x_h^T goes into one of two TMEM accumulators, so the MMA of head h+1 runs while the
+// threads weight head h with its decay factors (log2-domain tables, double buffered, built one head ahead) and add it
+// to the running sum they keep in registers.
+#pragma once
+#include "tc_scan_tma.cuh"
+
+namespace bissd {
+namespace tc {
+
+struct DcbShared {
+    uint64_t full[3], mma_done[2];
+    uint32_t tmem_base;
+};
+
+inline size_t dcb_tma_smem(int P, int Q) { return 1024 + 3 * 2 * (size_t)(P / 64) * 16384 + 2 * 4 * (size_t)Q * 4; }
+
+template <class T>
+__global__ void __launch_bounds__(kThreads, 1)
+dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
+        const float *cs_f, const float *cs_b, float *dCB, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ DcbShared sh;
+    const int P = d.P, Q = d.Q, R = d.R;
+    const int npb = P / 64;
+    const int stage_bytes = 2 * npb * 16384;
+    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    float *tabs = reinterpret_cast<float *>(base_sm + 3 * stage_bytes);          // [2][4][Q]: f2, b2, tf, tb
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
+    const int l0 = blockIdx.y * kTileM, s0 = blockIdx.z * 128;
+    const int quad = warp & 3, half = warp >> 2;
+    const int l = l0 + quad * 32 + lane;
+    const int wl_min = l0 + quad * 32, wl_max = wl_min + 31;
+    if (warp == 0) tmem_alloc(&sh.tmem_base, 256);
+    if (tid == 32) {
+        for (int i = 0; i < 3; ++i) mbar_init(&sh.full[i], 1);
+        mbar_init(&sh.mma_done[0], 1);
+        mbar_init(&sh.mma_done[1], 1);
+        fence_mbar_init();
+    }
+    auto build_tables = [&](int hr) {
+        const int h = g * R + hr;
+        const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
+        float *t = tabs + (hr & 1) * 4 * Q;
+        for (int i = tid; i < Q; i += kThreads) {
+            const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
+            const float lg = __log2f(dt_out[base + i]);
+            t[i] = cf;
+            t[Q + i] = cb_;
+            t[2 * Q + i] = cf - lg;
+            t[3 * Q + i] = cb_ - lg;
+        }
+    };
+    auto load_head = [&](int hr) {                              // thread 0: both tiles of head hr into ring slot hr % 3
+        const int h = g * R + hr, slot = hr % 3;
+        uint8_t *sg = base_sm + slot * stage_bytes, *sx = sg + npb * 16384;
+        mbar_expect_tx(&sh.full[slot], (uint32_t)stage_bytes);
+        for (int j = 0; j < npb; ++j) {
+            tma_load4(sg + j * 16384, &tmG, j * 64, h, c * Q + l0, b, &sh.full[slot]);
+            tma_load4(sx + j * 16384, &tmX, j * 64, h, c * Q + s0, b, &sh.full[slot]);
+        }
+    };
+    auto issue_head = [&](int hr, uint32_t tmem) -> bool {      // thread 0: G2 of head hr into accumulator hr & 1
+        const int slot = hr % 3;
+        if (!mbar_wait(&sh.full[slot], (hr / 3) & 1)) return false;
+        tc_fence_after();
+        const uint8_t *sg = base_sm + slot * stage_bytes, *sx = sg + npb * 16384;
+        const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, 128);
+        for (int j = 0; j < npb; ++j)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                umma(tmem + (hr & 1) * 128, smem_desc(smem_u32(sg + j * 16384) + kk * 32, 16, 1024),
+                     smem_desc(smem_u32(sx + j * 16384) + kk * 32, 16, 1024), idesc, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&sh.mma_done[hr & 1]);
+        return true;
+    };
+    build_tables(0);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    bool ok = true;
+    if (tid == 0) {
+        for (int hr = 0; hr < 3 && hr < R; ++hr) load_head(hr);
+        ok = issue_head(0, tmem);
+    }
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    const uint32_t tl = tmem_lane_base(tmem);
+#pragma unroll 1
+    for (int hr = 0; hr < R; ++hr) {
+        if (tid == 0 && ok && hr + 1 < R) ok = issue_head(hr + 1, tmem);
+        if (hr + 1 < R) build_tables(hr + 1);
+        if (ok) ok = mbar_wait(&sh.mma_done[hr & 1], (hr >> 1) & 1);
+        if (ok) {
+            tc_fence_after();
+            const float *t = tabs + (hr & 1) * 4 * Q;
+            const float fl = t[min(l, Q - 1)], bl = t[Q + min(l, Q - 1)];
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                const int c0 = half * 32 + ch * 64;
+                const int sb0 = s0 + c0;
+                float v[32];
+                tmem_ld32(tl + (hr & 1) * 128 + c0, v);
+                if (sb0 + 31 < wl_min) {                        // whole strip left of the diagonal for every row here
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(v[j], ex2_approx(fl - t[2 * Q + sb0 + j]), acc[ch * 32 + j]);
+                } else if (sb0 > wl_max) {                      // whole strip right of it
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(v[j], ex2_approx(bl - t[3 * Q + sb0 + j]), acc[ch * 32 + j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int s = sb0 + j;
+                        float a = (s <= l) ? fl - t[2 * Q + s] : bl - t[3 * Q + s];
+                        if (s == l) a += 1.f;                   // the diagonal counts once per direction
+                        acc[ch * 32 + j] = fmaf(v[j], ex2_approx(a), acc[ch * 32 + j]);
+                    }
+                }
+            }
+        }
+        if (tid == 0 && ok && hr + 3 < R) load_head(hr + 3);   // slot hr % 3 is free: the MMA that read it has completed
+        tc_fence_before();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+    }
+    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
+    if (ok && l < Q) {
+        float *out = dCB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0;
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+            const int c0 = half * 32 + ch * 64;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4 *>(out + c0 + j) =
+                    make_float4(acc[ch * 32 + j], acc[ch * 32 + j + 1], acc[ch * 32 + j + 2], acc[ch * 32 + j + 3]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace tc
+}  // namespace bissd
