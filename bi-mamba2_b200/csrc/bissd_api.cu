@@ -11,6 +11,7 @@
 #include "simt_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_kernels.cuh"
+#include "tc_dbc_tma.cuh"
 #include "tc_dcb_tma.cuh"
 #include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
@@ -355,10 +356,36 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                 BISSD_LAUNCH("tc_dx", tc::dx_kernel<T, 8><<<dim3(bch, nlt_tc), tc::kThreads, smem_dx, s>>>(
                     dg, x, Bm, z, gv, out_x, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cb), E16, a.dx, a.dz, F(w.ddt_out), F(w.dDpart), status));
             }
-            BISSD_ALLOW(tc::dbc_states<T>, smem_n);
-            BISSD_LAUNCH("tc_dbc_states", tc::dbc_states<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_n, s>>>(
-                dg, x, Bm, Cm, z, gv, a.dt_out, a.cs_f, a.cs_b, E16, a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
-                F(w.nf), F(w.nb), F(w.pf), F(w.pb), status));
+            bool dbc_done = false;
+            if (dx_done) {                                           // the dx kernel has produced nf / nb
+                CUtensorMap mC, mEf, mEb, mSf, mSb;
+                const unsigned long long dC4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sC4[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+                const unsigned bC4[4] = {64, 1, 128, 1};
+                const unsigned long long rows = (unsigned long long)d.b * d.nc * d.H * d.P;
+                const char *e16 = static_cast<const char *>(E16);
+                if (tc::make_map4(&mC, a.p.x_dtype, a.C.ptr, dC4, sC4, bC4) &&
+                    tc::make_map2(&mEf, a.p.x_dtype, e16, d.N, rows, 64, d.P) &&
+                    tc::make_map2(&mEb, a.p.x_dtype, e16 + rows * d.N * 2, d.N, rows, 64, d.P) &&
+                    tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
+                    tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P)) {
+                    const size_t smem_p = tc::prev_tma_smem(d.P, d.N), smem_a = tc::dbc_tma_smem(d.P, std::min(d.N, 128));
+                    BISSD_ALLOW(tc::prev_terms_tma<T>, smem_p);
+                    BISSD_LAUNCH("tc_prev_terms_tma", tc::prev_terms_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_p, s>>>(
+                        d, mC, mSf, mSb, gv, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
+                    BISSD_ALLOW(tc::dbc_accum_tma<T>, smem_a);
+                    BISSD_LAUNCH("tc_dbc_accum_tma", tc::dbc_accum_tma<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_a, s>>>(
+                        d, mEf, mEb, mSf, mSb, x, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
+                    dbc_done = true;
+                    nsplit = 1;                                      // nf/nb/pf/pb now hold complete row sums
+                }
+            }
+            if (!dbc_done) {
+                BISSD_ALLOW(tc::dbc_states<T>, smem_n);
+                BISSD_LAUNCH("tc_dbc_states", tc::dbc_states<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_n, s>>>(
+                    dg, x, Bm, Cm, z, gv, a.dt_out, a.cs_f, a.cs_b, E16, a.states_f, a.states_b, F(w.dB_part), F(w.dC_part),
+                    F(w.nf), F(w.nb), F(w.pf), F(w.pb), status));
+            }
         }
     }
     if (!tcp) {

@@ -1,0 +1,269 @@
+// Backward, TMA-fed: the "states" parts of dB / dC as one long accumulation over heads and directions, and the
+// "prev" decay terms as their own small kernel (see simt::dbc_states for the formulae and reference line numbers).
+//
+//   dB_states[l,n] = sum_{h,dir} (x_h[l,:] Delta_h[l] e^{T-cs_dir[l]}) . E_{h,dir}[:,n]
+//   dC_states[l,n] = sum_{h,dir} (g_h[l,:] e^{cs_dir[l]})              . S_{h,dir}[:,n]
+// The row-scaled left operand is written by the threads (it has to pass through registers anyway), the right operand
+// ([headdim x dstate], dstate contiguous -> MN-major) comes by TMA into a three-deep ring, and all 2*R products land in
+// one TMEM accumulator that is read once.  The per-head row sums the reference takes from these products come from
+// elsewhere: nf / nb from the dx kernel's per-direction accumulators, pf / pb from prev_terms_tma below.
+#pragma once
+#include "tc_scan_tma.cuh"
+
+namespace bissd {
+namespace tc {
+
+struct DbcShared {
+    uint64_t full[3], free_bar[3], done_bar;
+    uint32_t tmem_base;
+};
+
+inline size_t dbc_tma_smem(int P, int nt) {
+    return 1024 + 3 * ((size_t)(P / 64) * 16384 + (size_t)(nt / 64) * P * 128) + 2 * 2 * 128 * 4;
+}
+
+// grid (b*nc*G*nsplit, Q/128, 2); blockIdx.z: 0 = dB (src = x, right operand = E16), 1 = dC (src = g, right = states).
+// part layout [b, nc*Q, G, N] fp32.
+template <class T>
+__global__ void __launch_bounds__(kThreads, 2)
+dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_constant__ CUtensorMap tmEb,
+              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb, View x, View g,
+              const float *dt_out, const float *cs_f, const float *cs_b, float *dB_part, float *dC_part, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ DbcShared sh;
+    const int P = d.P, N = d.N, Q = d.Q, R = d.R;
+    const int npb = P / 64;
+    const int nsplit = (N + 127) / 128;
+    const int nt = min(N, 128), nnb = nt / 64;
+    const int a_bytes = npb * 16384, b_bytes = nnb * P * 128, slot_bytes = a_bytes + b_bytes;
+    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    float *sc = reinterpret_cast<float *>(base_sm + 3 * slot_bytes);               // [2 bufs][2 dirs][128 rows]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % nsplit, bx = blockIdx.x / nsplit;
+    const int grp = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int which = blockIdx.z;
+    const int lim = min(Q, d.L - c * Q);
+    const int l0 = blockIdx.y * kTileM, n0 = split * 128;
+    const View &src = which ? g : x;
+    const uint32_t ncols = tmem_cols(nt);
+    if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
+    if (tid == 32) {
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.free_bar[i], 1);
+        }
+        mbar_init(&sh.done_bar, 1);
+        fence_mbar_init();
+    }
+    auto build_scale = [&](int hr) {                            // one (dir, row) per thread
+        const int h = grp * R + hr, dir = tid >> 7, r = tid & 127, l = l0 + r;
+        const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
+        float v = 0.f;
+        if (l < lim) {
+            const float cs = dir ? cs_b[base + l] : cs_f[base + l];
+            if (which) v = __expf(cs);
+            else v = dt_out[base + l] * __expf((dir ? cs_b[base] : cs_f[base + Q - 1]) - cs);
+        }
+        sc[((hr & 1) * 2 + dir) * 128 + r] = v;
+    };
+    const int total = 2 * R;
+    auto load_b = [&](int it) {                                 // thread 0: right operand of stage it = (head, dir)
+        const int hr = it >> 1, dir = it & 1, slot = it % 3;
+        const int tile = (b * d.nc + c) * d.H + grp * R + hr;
+        uint8_t *sb = base_sm + slot * slot_bytes + a_bytes;
+        const CUtensorMap *m = which ? (dir ? &tmSb : &tmSf) : (dir ? &tmEb : &tmEf);
+        mbar_expect_tx(&sh.full[slot], (uint32_t)b_bytes);
+        for (int j = 0; j < nnb; ++j) tma_load2(sb + j * P * 128, m, n0 + j * 64, tile * P, &sh.full[slot]);
+    };
+    uint4 ra[8];
+    auto fetch = [&](int it) {
+        const int hr = it >> 1, dir = it & 1, h = grp * R + hr;
+        const float *s = sc + ((hr & 1) * 2 + dir) * 128;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < 4 * npb) {
+                const int q = tid + (i & 3) * kThreads, j = i >> 2;
+                const int r = q >> 3, l = l0 + r, p = j * 64 + (q & 7) * 8;
+                ra[i] = (l < lim) ? scale8<T>(ld8v<T>(src, b, c * Q + l, h, p), s[r]) : zero8();
+            }
+        }
+    };
+    build_scale(0);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    bool ok = true;
+    if (tid == 0) {
+        load_b(0);
+        if (total > 1) load_b(1);
+    }
+    fetch(0);
+#pragma unroll 1
+    for (int it = 0; it < total; ++it) {
+        const int slot = it % 3;
+        uint8_t *sa = base_sm + slot * slot_bytes;
+        if (ok && it >= 3) ok = mbar_wait(&sh.free_bar[slot], ((it / 3) - 1) & 1);
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i < 4 * npb) {
+                    const int q = tid + (i & 3) * kThreads, j = i >> 2;
+                    const int r = q >> 3, cc = q & 7;
+                    *reinterpret_cast<uint4 *>(sa + j * 16384 + r * 128 + ((cc ^ (r & 7)) << 4)) = ra[i];
+                }
+            }
+            fence_async_smem();
+            if ((it & 1) == 0 && (it >> 1) + 1 < R) build_scale((it >> 1) + 1);
+            if (it + 1 < total) fetch(it + 1);
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0) {
+            ok = mbar_wait(&sh.full[slot], (it / 3) & 1);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t idesc = instr_desc(AbFmt<T>::v, false, true, nt);
+                const uint8_t *sb = sa + a_bytes;
+                for (int j = 0; j < npb; ++j)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(tmem, smem_desc(smem_u32(sa + j * 16384) + kk * 32, 16, 1024),
+                             smem_desc(smem_u32(sb) + (j * 64 + kk * 16) * 128, (uint32_t)P * 128, 1024), idesc,
+                             (it > 0 || j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sh.free_bar[slot]);
+                if (it + 2 < total) {                           // refill the slot stage it-1 used, once its MMAs are done
+                    if (it >= 1) ok = mbar_wait(&sh.free_bar[(it + 2) % 3], ((it - 1) / 3) & 1);
+                    if (ok) load_b(it + 2);
+                }
+            }
+        }
+    }
+    // a failure seen only by thread 0 in the last iteration is caught here
+    if (ok) {
+        if (tid == 0) umma_commit(&sh.done_bar);
+        ok = mbar_wait(&sh.done_bar, 0);
+    }
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
+    if (ok) {
+        const int l = l0 + (warp & 3) * 32 + lane;
+        float *part = (which ? dC_part : dB_part) + (((long long)b * d.nc * Q + c * Q + l) * d.G + grp) * N + n0;
+        for (int c0 = (warp >> 2) * 32; c0 < nt; c0 += 64) {
+            float v[32];
+            tmem_ld32(tmem_lane_base(tmem) + c0, v);
+            if (l < lim) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(part + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, ncols);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// "prev" decay terms:  pf[l] = e^{cs_f[l]} sum_p g[l,p] (C[l,:].S_f[p,:]),  pb[l] likewise with S_b / cs_b  - the row sums
+// the reference takes inside _chunk_scan_bwd_dc_kernel (src/ssd/bi/ssd_chunk_scan.py:598-623).  C and both entering
+// states arrive by TMA; nothing is staged by threads.   grid (b*nc*H, Q/128).
+inline size_t prev_tma_smem(int P, int N) { return 1024 + (size_t)(N / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128; }
+
+template <class T>
+__global__ void __launch_bounds__(kThreads, 2)
+prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmSf,
+               const __grid_constant__ CUtensorMap tmSb, View g, const float *cs_f, const float *cs_b, float *pf, float *pb,
+               int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ uint64_t bar_in, bar_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float rowred[2][kTileM];
+    const int P = d.P, N = d.N, Q = d.Q;
+    const int nsl = N / 64;
+    uint8_t *smC = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *smSf = smC + nsl * 16384, *smSb = smSf + nsl * P * 128;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int grp = h / d.R;
+    const int lim = min(Q, d.L - c * Q);
+    const int l0 = blockIdx.y * kTileM;
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
+    const uint32_t ncols = tmem_cols(2 * P);
+    if (warp == 0) tmem_alloc(&tmem_slot, ncols);
+    if (tid == 32) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_done, 1);
+        fence_mbar_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool ok = true;
+    if (tid == 0) {
+        const int tile = (b * d.nc + c) * d.H + h;
+        mbar_expect_tx(&bar_in, (uint32_t)(nsl * 16384 + 2 * nsl * P * 128));
+        for (int j = 0; j < nsl; ++j) {
+            tma_load4(smC + j * 16384, &tmC, j * 64, grp, c * Q + l0, b, &bar_in);
+            tma_load2(smSf + j * P * 128, &tmSf, j * 64, tile * P, &bar_in);
+            tma_load2(smSb + j * P * 128, &tmSb, j * 64, tile * P, &bar_in);
+        }
+        ok = mbar_wait(&bar_in, 0);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, P);
+            for (int dir = 0; dir < 2; ++dir)
+                for (int j = 0; j < nsl; ++j)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(tmem + dir * P, smem_desc(smem_u32(smC + j * 16384) + kk * 32, 16, 1024),
+                             smem_desc(smem_u32((dir ? smSb : smSf) + j * P * 128) + kk * 32, 16, 1024), idesc,
+                             (j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&bar_done);
+        }
+    }
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane, l = l0 + r;
+    if (ok) ok = mbar_wait(&bar_done, 0);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
+    float sf_ = 0.f, sb_ = 0.f;
+    if (ok) {
+        const uint32_t tl = tmem_lane_base(tmem);
+        for (int c0 = half * 32; c0 < P; c0 += 64) {
+            float af[32], ab[32];
+            tmem_ld32(tl + c0, af);
+            tmem_ld32(tl + P + c0, ab);
+            if (l < lim) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    float gv[8];
+                    unpack8<T>(ld8v<T>(g, b, c * Q + l, h, c0 + j), gv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        sf_ = fmaf(af[j + i], gv[i], sf_);
+                        sb_ = fmaf(ab[j + i], gv[i], sb_);
+                    }
+                }
+            }
+        }
+    }
+    if (half == 1) {
+        rowred[0][r] = sf_;
+        rowred[1][r] = sb_;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (ok && half == 0 && l < Q) {
+        const float ef = (l < lim) ? __expf(cs_f[base + l]) : 0.f, eb = (l < lim) ? __expf(cs_b[base + l]) : 0.f;
+        pf[base + l] = ef * (sf_ + (P > 32 ? rowred[0][r] : 0.f));
+        pb[base + l] = eb * (sb_ + (P > 32 ? rowred[1][r] : 0.f));
+    }
+    if (warp == 0) tmem_dealloc(tmem, ncols);
+}
+
+}  // namespace tc
+}  // namespace bissd
