@@ -89,8 +89,17 @@ def kernel_model(name, cfg):
         "bmm_bwd": (tg * 4 * Q * Q * N, CB + 2 * BC + 2 * 4 * b * L * H * N + 2 * BC),
         "cumsum_bwd": (0, 9 * HQ + 2 * 4 * b * L * H),
         "final_reduce": (0, 4 * b * nc * H * (2 + 4 * P)),
+        "gate_bwd": (0, 5 * X),
+        "prev_terms": (t * 4 * Q * P * N, X + BC + 2 * 2 * ST + 2 * HQ),
+        "dbc_accum": (t * 8 * Q * P * N, 2 * X + 2 * 2 * 2 * ST + 2 * 4 * b * L * G * N + 6 * HQ),
+        "dcb": (t * 2 * Q * Q * P, 2 * X + 3 * HQ + CB),
+        "dx": (t * (4 * Q * P * N + 2 * Q * Q * P), 4 * X + BC + 2 * 2 * ST + CB + 5 * HQ),
     }
-    return model.get(name, (0, 0))
+    # tensor-core kernels are reported as tc_<phase>[_tma]; they do the same algorithmic work as the phase they replace
+    key = name[3:] if name.startswith("tc_") else name
+    if key.endswith("_tma"):
+        key = key[:-4]
+    return model.get(key, model.get(key + "_kernel", (0, 0)))
 
 
 class ClockSampler:

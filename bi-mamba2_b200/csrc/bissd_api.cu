@@ -684,7 +684,7 @@ int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_by
         if (a->p.has_D && !a->dD) return BISSD_ERR_NULL;
         if (a->p.has_dt_bias && !a->ddt_bias) return BISSD_ERR_NULL;
     }
-    if (a->p.has_z && !a->z.ptr) return BISSD_ERR_NULL;
+    if (a->p.has_z && (!a->z.ptr || !a->dz || !a->out_x.ptr)) return BISSD_ERR_NULL;   // the gate runs in the LOCAL phase
     if (a->p.has_D && !a->D) return BISSD_ERR_NULL;
     if (a->p.has_dt_bias && !a->dt_bias) return BISSD_ERR_NULL;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < bwd_layout(d).total)
