@@ -102,6 +102,12 @@ def kernel_model(name, cfg):
     return model.get(key, model.get(key + "_kernel", (0, 0)))
 
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the heaviest kernels at the benchmark
+# shape, from ncu captures on a batch-2 case scaled by 4 (traffic is proportional to batch: every CTA reads its own
+# tiles); see profiles/ncu_intra_decay_grad_dx_tma_scan_tma_b2.md.
+NCU_TRAFFIC_BYTES = {"tc_intra_decay_grad": 122.6e6, "tc_dx_tma": 182.0e6, "tc_chunk_scan_tma": 200.8e6}
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -281,7 +287,8 @@ def run_ours(args):
         roof = dict(bound="tensor", achieved=kflops / per_launch_s / 1e12, peak=peaks["tflops"], unit="TFLOP/s")
     else:
         roof = dict(bound="hbm", achieved=kbytes / per_launch_s / 1e9, peak=peaks["hbm_gbs"], unit="GB/s")
-    roof.update(frac=roof["achieved"] / roof["peak"], traffic=None, kernel=tname, launches_per_step=tcount / tsteps,
+    roof.update(frac=roof["achieved"] / roof["peak"],
+                traffic=(NCU_TRAFFIC_BYTES.get(tname) if cfg["batch"] == 8 else None), kernel=tname, launches_per_step=tcount / tsteps,
                 us_per_launch=per_launch_s * 1e6, share_of_device_time=tms / total_ms, peak_source=peaks["source"])
     F, Bt = algorithmic_work(cfg)
     step_s = ms * 1e-3 / args.steps

@@ -16,6 +16,7 @@
 #include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
 #include "tc_selftest.cuh"
+#include "tc_state_tma.cuh"
 
 namespace bissd {
 
@@ -164,6 +165,16 @@ static bool no_tma() {   // BISSD_NO_TMA=1: keep the thread-staged tcgen05 kerne
     return v;
 }
 
+// rank-4 tensor map over a (batch, seq, head, inner) 16-bit tensor; box = [64 inner, 1 head, rows seq, 1 batch]
+static bool map_bshd(CUtensorMap *m, int dtype, const void *ptr, long long sb, long long sl, long long sh, int inner,
+                     int heads, int seqlen, int batch, unsigned rows) {
+    const unsigned long long dims[4] = {(unsigned long long)inner, (unsigned long long)heads, (unsigned long long)seqlen,
+                                        (unsigned long long)batch};
+    const unsigned long long str[3] = {(unsigned long long)sh * 2, (unsigned long long)sl * 2, (unsigned long long)sb * 2};
+    const unsigned box[4] = {64, 1, rows, 1};
+    return tc::make_map4(m, dtype, ptr, dims, str, box);
+}
+
 #define BISSD_ALLOW(kernel, bytes)                  \
     do {                                             \
         int rc_ = allow_smem(kernel, bytes);         \
@@ -193,7 +204,20 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
         if constexpr (TcKernels<T>::available) {
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
-                if (ntP <= 64) {
+                bool st_done = false;
+                if (!no_tma() && tc::state_tma_ok(d.P, d.N, d.Q)) {
+                    CUtensorMap mRow, mCol;
+                    if (map_bshd(&mRow, a.p.x_dtype, a.B.ptr, a.B.stride_batch, a.B.stride_seq, a.B.stride_head, d.N, d.G, d.L, d.b, d.Q) &&
+                        map_bshd(&mCol, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
+                        const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
+                        BISSD_ALLOW((tc::state_gemm_tma<T, 0>), smem_t);
+                        BISSD_LAUNCH("tc_chunk_state_tma", tc::state_gemm_tma<T, 0><<<dim3(bch, 2, d.N / 128), tc::kThreads, smem_t, s>>>(
+                            d, mRow, mCol, a.dt_out, a.cs_f, a.cs_b, loc, status));
+                        st_done = true;
+                    }
+                }
+                if (st_done) {
+                } else if (ntP <= 64) {
                     BISSD_ALLOW((tc::state_gemm<T, 0, 2>), smem);
                     BISSD_LAUNCH("tc_chunk_state", tc::state_gemm<T, 0, 2><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
                         d, Bm, x, z, a.dt_out, a.cs_f, a.cs_b, loc, status));
@@ -212,8 +236,13 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
     // the recurrence runs in both phases: from zero (or init_*) in LOCAL, again with init_* in FINISH
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.init_f || a.init_b);
     if (need_pass) {
-        BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, simt::TB), 2), simt::TB, 0, s>>>(
-            d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
+        if ((d.P * d.N) % 4 == 0) {
+            BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd4<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, 4 * simt::TB), 2), simt::TB, 0, s>>>(
+                d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
+        } else {
+            BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, simt::TB), 2), simt::TB, 0, s>>>(
+                d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
+        }
     }
     if (a.phases & BISSD_PHASE_FINISH) {
         if constexpr (TcKernels<T>::available) {
@@ -293,7 +322,20 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             }
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
-                if (ntP <= 64) {
+                bool st_done = false;
+                if (!no_tma() && tc::state_tma_ok(d.P, d.N, d.Q)) {
+                    CUtensorMap mRow, mCol;
+                    if (map_bshd(&mRow, a.p.x_dtype, a.C.ptr, a.C.stride_batch, a.C.stride_seq, a.C.stride_head, d.N, d.G, d.L, d.b, d.Q) &&
+                        map_bshd(&mCol, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, d.Q)) {
+                        const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
+                        BISSD_ALLOW((tc::state_gemm_tma<T, 1>), smem_t);
+                        BISSD_LAUNCH("tc_dstates_tma", tc::state_gemm_tma<T, 1><<<dim3(bch, 2, d.N / 128), tc::kThreads, smem_t, s>>>(
+                            d, mRow, mCol, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
+                        st_done = true;
+                    }
+                }
+                if (st_done) {
+                } else if (ntP <= 64) {
                     BISSD_ALLOW((tc::state_gemm<T, 1, 2>), smem);
                     BISSD_LAUNCH("tc_dstates", tc::state_gemm<T, 1, 2><<<dim3(bch, ceil_div(2 * d.N, tc::kTileM)), tc::kThreads, smem, s>>>(
                         dg, Cm, gv, z, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
@@ -310,9 +352,16 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         }
     }
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.dfinal_f || a.dfinal_b);
+    int pass_nblk = ((d.P * d.N) % 4 == 0) ? ceil_div(d.P * d.N, 4 * simt::TB) : w.nblk;   // dT partial slots per chunk
     if (need_pass) {
-        BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), simt::TB, 0, s>>>(
-            d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, tcp ? nullptr : F(w.E), tcp ? E16 : nullptr, F(w.dTpart), a.dinit_f, a.dinit_b));
+        if ((d.P * d.N) % 4 == 0) {
+            pass_nblk = ceil_div(d.P * d.N, 4 * simt::TB);
+            BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd4<T><<<dim3(d.b * d.H, pass_nblk, 2), simt::TB, 0, s>>>(
+                d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, tcp ? nullptr : F(w.E), tcp ? E16 : nullptr, F(w.dTpart), a.dinit_f, a.dinit_b));
+        } else {
+            BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), simt::TB, 0, s>>>(
+                d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, tcp ? nullptr : F(w.E), tcp ? E16 : nullptr, F(w.dTpart), a.dinit_f, a.dinit_b));
+        }
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
@@ -451,7 +500,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
-        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), w.nblk, nsplit, a.ddt,
+        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
     BISSD_LAUNCH("final_reduce", simt::final_reduce<<<d.H, simt::TB, 0, s>>>(
         d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,

@@ -945,15 +945,30 @@ __global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, 
     if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = red[0];
     __syncthreads();
     if (dD && dDpart) {
+        // rows of the partial buffer are split over TB / P thread groups, then the groups are added in a fixed order
+        const int rows = nbc * nlt;
+        const int ngrp = d.P <= TB ? TB / d.P : 1;
         float tot = 0.f;
-        for (int p = threadIdx.x; p < d.P; p += TB) {
+        for (int p0 = 0; p0 < d.P; p0 += TB) {
+            const int p = p0 + (threadIdx.x % (d.P <= TB ? d.P : TB)), grp = d.P <= TB ? threadIdx.x / d.P : 0;
             float s = 0.f;
-            for (int i = 0; i < nbc * 1; ++i)
-                for (int t = 0; t < nlt; ++t) s += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
-            if (d.D_hdim) dD[h * d.P + p] = s;
-            tot += s;
+            if (p < d.P && grp < ngrp)
+                for (int r = grp; r < rows; r += ngrp) {
+                    const int i = r / nlt, t = r - i * nlt;
+                    s += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
+                }
+            __syncthreads();
+            red[threadIdx.x] = s;
+            __syncthreads();
+            if (grp == 0 && p < d.P) {
+                float v = 0.f;
+                for (int q = 0; q < ngrp; ++q) v += red[q * d.P + (p - p0)];
+                if (d.D_hdim) dD[h * d.P + p] = v;
+                tot += v;
+            }
         }
         if (!d.D_hdim) {
+            __syncthreads();
             red[threadIdx.x] = tot;
             __syncthreads();
             for (int o = TB / 2; o > 0; o >>= 1) {
@@ -963,6 +978,107 @@ __global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, 
             if (threadIdx.x == 0) dD[h] = red[0];
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Four-elements-per-thread versions of the two state-passing kernels (need headdim*dstate % 4 == 0): 128-bit loads of
+// the fp32 chunk quantities, one packed store of the passed values, and the chunk loop unrolled so that several
+// chunks' loads are in flight.  Same arithmetic, same order, as state_passing_fwd / state_passing_bwd.
+template <class T> __device__ __forceinline__ void st4(void *p, long long i, float a, float b, float c, float e) {
+    T v[4] = {from_f<T>(a), from_f<T>(b), from_f<T>(c), from_f<T>(e)};
+    if (sizeof(T) == 4) *reinterpret_cast<float4 *>(static_cast<T *>(p) + i) = *reinterpret_cast<float4 *>(v);
+    else *reinterpret_cast<uint2 *>(static_cast<T *>(p) + i) = *reinterpret_cast<uint2 *>(v);
+}
+template <class T> __device__ __forceinline__ float4 ld4(const void *p, long long i) {
+    if (sizeof(T) == 4) return *reinterpret_cast<const float4 *>(static_cast<const T *>(p) + i);
+    const uint2 u = *reinterpret_cast<const uint2 *>(static_cast<const T *>(p) + i);
+    const T *v = reinterpret_cast<const T *>(&u);
+    return make_float4(to_f<T>(v[0]), to_f<T>(v[1]), to_f<T>(v[2]), to_f<T>(v[3]));
+}
+
+// grid (b*H, ceil(P*N/1024), 2)
+template <class T>
+__global__ void __launch_bounds__(TB) state_passing_fwd4(Dims d, const float *loc, const float *cs_f, const float *cs_b,
+                                                         const float *init_f, const float *init_b, void *states_f,
+                                                         void *states_b, float *final_f, float *final_b) {
+    const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
+    const int dir = blockIdx.z;
+    const int PN = d.P * d.N;
+    const int e = (blockIdx.y * TB + threadIdx.x) * 4;
+    if (e >= PN) return;
+    const long long per_dir = (long long)d.b * d.nc * d.H * PN;
+    const float *lp = loc + dir * per_dir;
+    const float *init = dir ? init_b : init_f;
+    void *states = dir ? states_b : states_f;
+    float *fin = dir ? final_b : final_f;
+    float4 run = init ? *reinterpret_cast<const float4 *>(init + (long long)(b * d.H + h) * PN + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long cstride = (long long)d.H * PN;
+    const long long off0 = ((long long)b * d.nc * d.H + h) * PN + e;
+    const long long cb0 = (long long)(b * d.H + h) * d.nc * d.Q;
+#pragma unroll 4
+    for (int i = 0; i < d.nc; ++i) {
+        const int c = dir ? d.nc - 1 - i : i;
+        const long long off = off0 + c * cstride;
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(lp + off));
+        const float dec = expf(dir ? cs_b[cb0 + (long long)c * d.Q] : cs_f[cb0 + (long long)c * d.Q + d.Q - 1]);
+        st4<T>(states, off, run.x, run.y, run.z, run.w);
+        run.x = dec * run.x + v.x;
+        run.y = dec * run.y + v.y;
+        run.z = dec * run.z + v.z;
+        run.w = dec * run.w + v.w;
+    }
+    if (fin) *reinterpret_cast<float4 *>(fin + (long long)(b * d.H + h) * PN + e) = run;
+}
+
+// grid (b*H, nblk4 = ceil(P*N/1024), 2); dTpart has nblk4 slots per (dir, b, h, c)
+template <class T>
+__global__ void __launch_bounds__(TB) state_passing_bwd4(Dims d, const float *gloc, const void *states_f,
+                                                         const void *states_b, const float *cs_f, const float *cs_b,
+                                                         const float *dfinal_f, const float *dfinal_b, float *E,
+                                                         void *E16, float *dTpart, float *dinit_f, float *dinit_b) {
+    __shared__ float red[TB / 32];
+    const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
+    const int dir = blockIdx.z;
+    const int PN = d.P * d.N;
+    const int nblk = gridDim.y;
+    const int e = (blockIdx.y * TB + threadIdx.x) * 4;
+    const bool on = e < PN;
+    const long long per_dir = (long long)d.b * d.nc * d.H * PN;
+    const float *gp = gloc + dir * per_dir;
+    const void *states = dir ? states_b : states_f;
+    const float *dfin = dir ? dfinal_b : dfinal_f;
+    float *dinit = dir ? dinit_b : dinit_f;
+    float4 run = (on && dfin) ? *reinterpret_cast<const float4 *>(dfin + (long long)(b * d.H + h) * PN + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long cstride = (long long)d.H * PN;
+    const long long off0 = ((long long)b * d.nc * d.H + h) * PN + e;
+    const long long cb0 = (long long)(b * d.H + h) * d.nc * d.Q;
+    for (int i = 0; i < d.nc; ++i) {
+        const int c = dir ? i : d.nc - 1 - i;
+        const long long off = off0 + c * cstride;
+        const float dec = expf(dir ? cs_b[cb0 + (long long)c * d.Q] : cs_f[cb0 + (long long)c * d.Q + d.Q - 1]);
+        float part = 0.f;
+        if (on) {
+            const float4 gv = __ldg(reinterpret_cast<const float4 *>(gp + off));
+            const float4 sv = ld4<T>(states, off);
+            if (E) *reinterpret_cast<float4 *>(E + dir * per_dir + off) = run;
+            if (E16) st4<T>(E16, dir * per_dir + off, run.x, run.y, run.z, run.w);
+            part = dec * (sv.x * run.x + sv.y * run.y + sv.z * run.z + sv.w * run.w);
+            run.x = dec * run.x + gv.x;
+            run.y = dec * run.y + gv.y;
+            run.z = dec * run.z + gv.z;
+            run.w = dec * run.w + gv.w;
+        }
+        part = warp_sum(part);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < TB / 32; ++w) s += red[w];
+            dTpart[((long long)dir * d.b * d.H * d.nc + (long long)(b * d.H + h) * d.nc + c) * nblk + blockIdx.y] = s;
+        }
+        __syncthreads();
+    }
+    if (on && dinit) *reinterpret_cast<float4 *>(dinit + (long long)(b * d.H + h) * PN + e) = run;
 }
 
 }  // namespace simt
