@@ -450,7 +450,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         if (tcp) {
             intra_tc = true;
             const int ntQ128 = std::min(ntQ, 128);
-            const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 3 * d.Q + tc::kTileM * 8);
+            const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 4 * d.Q + tc::kTileM * 8);
             bool dcb_done = false;
             if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mG, mX;

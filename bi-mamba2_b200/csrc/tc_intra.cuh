@@ -5,6 +5,7 @@
 //     times the bf16-rounded matrix).
 #pragma once
 #include "tc_kernels.cuh"
+#include "tc_tma.cuh"
 
 namespace bissd {
 namespace tc {
@@ -87,6 +88,42 @@ __global__ void __launch_bounds__(kThreads) dcb_kernel(Dims d, View x, View z, V
     pipe_destroy(p, 128);
 }
 
+// One 32-column strip of a row of the intra-chunk sweep.  DIR 0: left to right, W[s] counted for s < l, rm[j] = sum of
+// W left of column j (kept for j <= l).  DIR 1: right to left, W[s] for s > l, rm[j] = sum right of j (kept for j >= l).
+// tt: the strip's 32 table entries (tf or tb); rl: f2[l] or b2[l].
+template <int DIR>
+__device__ __forceinline__ void sweep_strip(const float (&v)[32], const float (&cbv)[32], float (&rm)[32], float &run,
+                                            const float *tt, float rl, int c0, int l, int Q) {
+    const bool whole = DIR ? (c0 > l) : (c0 + 31 < l);          // strip entirely inside this row's triangle
+#pragma unroll
+    for (int gq = 0; gq < 4; ++gq) {
+        const int j0 = DIR ? 24 - 8 * gq : 8 * gq;
+        float tv[8];
+        if (c0 + j0 < Q) {
+            const float4 t0 = *reinterpret_cast<const float4 *>(tt + j0), t1 = *reinterpret_cast<const float4 *>(tt + j0 + 4);
+            tv[0] = t0.x; tv[1] = t0.y; tv[2] = t0.z; tv[3] = t0.w; tv[4] = t1.x; tv[5] = t1.y; tv[6] = t1.z; tv[7] = t1.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tv[i] = 1e30f;
+        }
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) {
+            const int i = DIR ? 7 - ii : ii, j = j0 + i, s = c0 + j;
+            const float w = v[j] * cbv[j] * ex2_approx(rl - tv[i]);
+            if (whole) {
+                rm[j] = run;
+                run += w;
+            } else if (DIR == 0) {
+                rm[j] = (s <= l) ? run : 0.f;
+                if (s < l) run += w;
+            } else {
+                rm[j] = (s >= l) ? run : 0.f;
+                if (s > l) run += w;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Intra-chunk decay gradients for one (batch, chunk, head) and one tile of 128 rows l:
 //   W_f[l,s] = G2 CB Delta[s] e^{cs_f[l]-cs_f[s]} (s<l),  R_f[l,j] = sum_{s<j} W_f[l,s],  da_f[j] = sum_{l>=j} R_f[l,j]
@@ -97,7 +134,7 @@ __global__ void __launch_bounds__(kThreads) dcb_kernel(Dims d, View x, View z, V
 // (the two row tiles of a 256-chunk are added by the consumer); tile 0 zero-fills part 1 when there is only one tile.
 // grid (b*nc*H, ceil(Q/128)); n_tile = round16(Q); tables 3*Q floats + 128*8 exchange floats.
 template <class T>
-__global__ void __launch_bounds__(kThreads) intra_decay_grad(Dims d, View x, View z, View dout, const float *dt_out,
+__global__ void __launch_bounds__(kThreads, 2) intra_decay_grad(Dims d, View x, View z, View dout, const float *dt_out,
                                                              const float *cs_f, const float *cs_b, const float *CB,
                                                              float *da_part0, float *da_part1, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -105,15 +142,19 @@ __global__ void __launch_bounds__(kThreads) intra_decay_grad(Dims d, View x, Vie
     const int Q = d.Q;
     const int nt = round_up(Q, 16);
     Carve cv = carve(dyn, nt);
-    float *sf = cv.tab, *sb = cv.tab + Q, *sd = cv.tab + 2 * Q, *xch = cv.tab + 3 * Q;   // xch[128][8]
+    // log2-domain tables: f2 = cs_f log2e, b2 = cs_b log2e, tf = f2 - log2 Delta, tb = b2 - log2 Delta
+    float *sf = cv.tab, *sb = cv.tab + Q, *tf = cv.tab + 2 * Q, *tb = cv.tab + 3 * Q, *xch = cv.tab + 4 * Q;   // xch[128][8]
     const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
     const int g = h / d.R;
     const int lim = min(Q, d.L - c * Q);
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
     for (int i = threadIdx.x; i < Q; i += kThreads) {
-        sf[i] = cs_f[base + i];
-        sb[i] = cs_b[base + i];
-        sd[i] = dt_out[base + i];
+        const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
+        const float lg = __log2f(dt_out[base + i]);           // -inf on the zero-padded tail: those columns vanish
+        sf[i] = cf;
+        sb[i] = cb_;
+        tf[i] = cf - lg;
+        tb[i] = cb_ - lg;
     }
     Pipe p;
     const uint32_t ncols = tmem_cols(nt);
@@ -168,23 +209,8 @@ __global__ void __launch_bounds__(kThreads) intra_decay_grad(Dims d, View x, Vie
                             for (int i = 0; i < 8; ++i) cbv[j + i] = 0.f;
                         }
                     }
-                    if (!dirn) {
-                        const float fl = sf[l];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int s = c0 + j;
-                            rm[j] = (s <= l) ? run : 0.f;
-                            if (s < l && s < lim) run += v[j] * cbv[j] * sd[s] * __expf(fl - sf[s]);
-                        }
-                    } else {
-                        const float bl = sb[l];
-#pragma unroll
-                        for (int j = 31; j >= 0; --j) {
-                            const int s = c0 + j;
-                            rm[j] = (s >= l) ? run : 0.f;
-                            if (s > l && s < lim) run += v[j] * cbv[j] * sd[s] * __expf(bl - sb[s]);
-                        }
-                    }
+                    if (!dirn) sweep_strip<0>(v, cbv, rm, run, tf + c0, sf[l], c0, l, Q);
+                    else sweep_strip<1>(v, cbv, rm, run, tb + c0, sb[l], c0, l, Q);
                 }
             }
             // forward warps own the 8-column groups left of the diagonal group, reverse warps those right of it
