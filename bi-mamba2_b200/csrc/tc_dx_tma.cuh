@@ -101,13 +101,23 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
     }
     const float *cbt = CBt + ((long long)(b * d.nc + c) * d.G + grp) * Q * Q;
     uint4 ra[4];
+    float4 raw[8];                                              // CB values of the step after next, still in flight
+    auto load_raw = [&](int s0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int q = tid + i * kThreads;
+            const float *src = cbt + (long long)(l0 + (q >> 3)) * Q + s0 + (q & 7) * 8;
+            raw[2 * i] = __ldg(reinterpret_cast<const float4 *>(src));
+            raw[2 * i + 1] = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        }
+    };
     auto fetch = [&](int s0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int q = tid + i * kThreads;
             const int l = l0 + (q >> 3), sc = s0 + (q & 7) * 8;
-            float v[8];
-            ldg8f(cbt + (long long)l * Q + sc, v);
+            float v[8] = {raw[2 * i].x, raw[2 * i].y, raw[2 * i].z, raw[2 * i].w,
+                          raw[2 * i + 1].x, raw[2 * i + 1].y, raw[2 * i + 1].z, raw[2 * i + 1].w};
             const float fl = f2[l], bl = b2[l];
             if (sc > l) {
                 const float4 t0 = *reinterpret_cast<const float4 *>(f2 + sc), t1 = *reinterpret_cast<const float4 *>(f2 + sc + 4);
@@ -131,7 +141,9 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
             ra[i] = pack8<T>(v);
         }
     };
+    load_raw(0);
     fetch(0);
+    if (kStageK < Q) load_raw(kStageK);
     bool ok = true;
     if (tid == 0) {
         if (mbar_wait(&sh.bar_cs, 0)) {
@@ -163,6 +175,7 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
             }
             fence_async_smem();
             if (s0 + kStageK < Q) fetch(s0 + kStageK);
+            if (s0 + 2 * kStageK < Q) load_raw(s0 + 2 * kStageK);
         }
         ok = __syncthreads_and(ok) && !sh.fail;
         if (!ok) break;
@@ -201,21 +214,25 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
         }
         const uint32_t tl = tmem_lane_base(tmem);
         for (int c0 = half * 32; c0 < P; c0 += 64) {
-            float af[32], ab[32], ai[32];
-            tmem_ld32(tl + c0, af);
-            tmem_ld32(tl + P + c0, ab);
-            tmem_ld32(tl + 2 * P + c0, ai);
-            float cs8[32];
+            uint4 xr[4], gr[4];                                 // requested together, before anything is consumed
 #pragma unroll
-            for (int j = 0; j < 32; ++j) cs8[j] = 0.f;
-            if (l < lim) {
-                const int ls = c * Q + l;
+            for (int q = 0; q < 4; ++q) {
+                xr[q] = (l < lim) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
+                gr[q] = (l < lim) ? ld8v<T>(g, b, c * Q + l, h, c0 + q * 8) : zero8();
+            }
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    const int p0 = c0 + j;
-                    float xv[8], gv[8], o[8];
-                    unpack8<T>(ld8v<T>(x, b, ls, h, p0), xv);
-                    unpack8<T>(ld8v<T>(g, b, ls, h, p0), gv);
+            for (int hs = 0; hs < 2; ++hs) {                    // two 16-column pieces keep the register footprint down
+                const int cc = c0 + hs * 16;
+                float af[16], ab[16], ai[16];
+                tmem_ld16(tl + cc, af);
+                tmem_ld16(tl + P + cc, ab);
+                tmem_ld16(tl + 2 * P + cc, ai);
+#pragma unroll
+                for (int j = 0; j < 16; j += 8) {
+                    const int p0 = cc + j;
+                    float xv[8], gv[8], o[8], gx[8];
+                    unpack8<T>(xr[hs * 2 + (j >> 3)], xv);
+                    unpack8<T>(gr[hs * 2 + (j >> 3)], gv);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float a = fmaf(wf, af[j + i], fmaf(wb, ab[j + i], ai[j + i]));
@@ -224,18 +241,19 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
                         rs = fmaf(a, xv[i], rs);
                         rsf = fmaf(af[j + i], xv[i], rsf);
                         rsb = fmaf(ab[j + i], xv[i], rsb);
-                        cs8[j + i] = gv[i] * xv[i];
+                        gx[i] = gv[i] * xv[i];
                     }
-                    *reinterpret_cast<uint4 *>(static_cast<T *>(dx) + ((long long)(b * d.L + ls) * d.H + h) * P + p0) = pack8<T>(o);
-                }
-            }
-            if (d.has_D) {
+                    if (l < lim)
+                        *reinterpret_cast<uint4 *>(static_cast<T *>(dx) + ((long long)(b * d.L + c * Q + l) * d.H + h) * P + p0) = pack8<T>(o);
+                    if (d.has_D) {                              // column sums of g*x over this warp's 32 rows
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float s = cs8[j];
+                        for (int i = 0; i < 8; ++i) {
+                            float sgx = gx[i];
 #pragma unroll
-                    for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
-                    if (lane == 0) colred[quad][c0 + j] = s;
+                            for (int o2 = 16; o2 > 0; o2 >>= 1) sgx += __shfl_xor_sync(0xffffffffu, sgx, o2);
+                            if (lane == 0) colred[quad][p0 + i] = sgx;
+                        }
+                    }
                 }
             }
         }

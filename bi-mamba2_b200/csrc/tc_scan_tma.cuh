@@ -90,13 +90,23 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     }
     const float *cbt = CB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q;
     uint4 ra[4];
+    float4 raw[8];                                              // CB values of the step after next, still in flight
+    auto load_raw = [&](int s0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int q = tid + i * kThreads;
+            const float *src = cbt + (long long)(l0 + (q >> 3)) * Q + s0 + (q & 7) * 8;
+            raw[2 * i] = __ldg(reinterpret_cast<const float4 *>(src));
+            raw[2 * i + 1] = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        }
+    };
     auto fetch = [&](int s0) {                                  // this thread's four 8-column pieces of M[:, s0:s0+64]
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int q = tid + i * kThreads;
             const int l = l0 + (q >> 3), sc = s0 + (q & 7) * 8;
-            float v[8];
-            ldg8f(cbt + (long long)l * Q + sc, v);
+            float v[8] = {raw[2 * i].x, raw[2 * i].y, raw[2 * i].z, raw[2 * i].w,
+                          raw[2 * i + 1].x, raw[2 * i + 1].y, raw[2 * i + 1].z, raw[2 * i + 1].w};
             const float fl = f2[l], bl = b2[l];
             if (sc + 7 < l) {
                 const float4 t0 = *reinterpret_cast<const float4 *>(tf + sc), t1 = *reinterpret_cast<const float4 *>(tf + sc + 4);
@@ -120,7 +130,9 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
             ra[i] = pack8<T>(v);
         }
     };
+    load_raw(0);
     fetch(0);
+    if (kStageK < Q) load_raw(kStageK);
     bool ok = true;
     if (tid == 0) {                                             // the two state products, straight from the TMA tiles
         if (mbar_wait(&sh.bar_cs, 0)) {
@@ -152,6 +164,7 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
             }
             fence_async_smem();
             if (s0 + kStageK < Q) fetch(s0 + kStageK);
+            if (s0 + 2 * kStageK < Q) load_raw(s0 + 2 * kStageK);
         }
         ok = __syncthreads_and(ok) && !sh.fail;
         if (!ok) break;
@@ -183,6 +196,13 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
         const float ef = (l < lim) ? __expf(cs_f[base + l]) : 0.f, eb = (l < lim) ? __expf(cs_b[base + l]) : 0.f;
         const uint32_t tl = tmem_lane_base(tmem);
         for (int c0 = (warp >> 2) * 32; c0 < P; c0 += 64) {
+            // all global operands of this strip are requested before anything is consumed: one round trip, not eight
+            uint4 xr[4], zr[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                xr[q] = (l < lim && d.has_D) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
+                zr[q] = (l < lim && d.has_z) ? ld8v<T>(z, b, c * Q + l, h, c0 + q * 8) : zero8();
+            }
             float y[32], v[32];
             tmem_ld32(tl + 2 * P + c0, y);
             tmem_ld32(tl + c0, v);
@@ -200,7 +220,7 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
                     for (int i = 0; i < 8; ++i) o[i] = y[j + i];
                     if (d.has_D) {
                         float xv[8];
-                        unpack8<T>(ld8v<T>(x, b, c * Q + l, h, p0), xv);
+                        unpack8<T>(xr[j >> 3], xv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) o[i] = fmaf(d.D_hdim ? D[h * P + p0 + i] : D[h], xv[i], o[i]);
                     }
@@ -209,7 +229,7 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
                         const long long ox = b * out_x.sb + (long long)(c * Q + l) * out_x.sl + h * out_x.sh + p0;
                         *reinterpret_cast<uint4 *>(static_cast<T *>(out_x.ptr) + ox) = pack8<T>(o);
                         float zz[8];
-                        unpack8<T>(ld8v<T>(z, b, c * Q + l, h, p0), zz);
+                        unpack8<T>(zr[j >> 3], zz);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) o[i] *= __fdividef(zz[i], 1.f + __expf(-zz[i]));
                     }
