@@ -75,16 +75,26 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
         mbar_expect_tx(&sh.full[slot], (uint32_t)b_bytes);
         for (int j = 0; j < nnb; ++j) tma_load2(sb + j * P * 128, m, n0 + j * 64, tile * P, &sh.full[slot]);
     };
-    uint4 ra[8];
-    auto fetch = [&](int it) {
-        const int hr = it >> 1, dir = it & 1, h = grp * R + hr;
-        const float *s = sc + ((hr & 1) * 2 + dir) * 128;
+    uint4 ra[8], raw[8];
+    auto load_raw = [&](int it) {                               // unscaled rows of the left operand of stage `it`
+        const int h = grp * R + (it >> 1);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             if (i < 4 * npb) {
                 const int q = tid + (i & 3) * kThreads, j = i >> 2;
-                const int r = q >> 3, l = l0 + r, p = j * 64 + (q & 7) * 8;
-                ra[i] = (l < lim) ? scale8<T>(ld8v<T>(src, b, c * Q + l, h, p), s[r]) : zero8();
+                const int l = l0 + (q >> 3), p = j * 64 + (q & 7) * 8;
+                raw[i] = (l < lim) ? ld8v<T>(src, b, c * Q + l, h, p) : zero8();
+            }
+        }
+    };
+    auto fetch = [&](int it) {                                  // scale what load_raw(it) brought in
+        const int hr = it >> 1, dir = it & 1;
+        const float *s = sc + ((hr & 1) * 2 + dir) * 128;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < 4 * npb) {
+                const int q = tid + (i & 3) * kThreads;
+                ra[i] = scale8<T>(raw[i], s[q >> 3]);
             }
         }
     };
@@ -98,7 +108,9 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
         load_b(0);
         if (total > 1) load_b(1);
     }
+    load_raw(0);
     fetch(0);
+    if (total > 1) load_raw(1);
 #pragma unroll 1
     for (int it = 0; it < total; ++it) {
         const int slot = it % 3;
@@ -116,6 +128,7 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
             fence_async_smem();
             if ((it & 1) == 0 && (it >> 1) + 1 < R) build_scale((it >> 1) + 1);
             if (it + 1 < total) fetch(it + 1);
+            if (it + 2 < total) load_raw(it + 2);
         }
         ok = __syncthreads_and(ok);
         if (!ok) break;

@@ -88,16 +88,16 @@ __global__ void __launch_bounds__(kThreads) dcb_kernel(Dims d, View x, View z, V
     pipe_destroy(p, 128);
 }
 
-// One 32-column strip of a row of the intra-chunk sweep.  DIR 0: left to right, W[s] counted for s < l, rm[j] = sum of
+// One 16-column strip of a row of the intra-chunk sweep.  DIR 0: left to right, W[s] counted for s < l, rm[j] = sum of
 // W left of column j (kept for j <= l).  DIR 1: right to left, W[s] for s > l, rm[j] = sum right of j (kept for j >= l).
-// tt: the strip's 32 table entries (tf or tb); rl: f2[l] or b2[l].
+// tt: the strip's 16 table entries (tf or tb); rl: f2[l] or b2[l].
 template <int DIR>
-__device__ __forceinline__ void sweep_strip(const float (&v)[32], const float (&cbv)[32], float (&rm)[32], float &run,
+__device__ __forceinline__ void sweep_strip(const float (&v)[16], const float (&cbv)[16], float (&rm)[16], float &run,
                                             const float *tt, float rl, int c0, int l, int Q) {
-    const bool whole = DIR ? (c0 > l) : (c0 + 31 < l);          // strip entirely inside this row's triangle
+    const bool whole = DIR ? (c0 > l) : (c0 + 15 < l);          // strip entirely inside this row's triangle
 #pragma unroll
-    for (int gq = 0; gq < 4; ++gq) {
-        const int j0 = DIR ? 24 - 8 * gq : 8 * gq;
+    for (int gq = 0; gq < 2; ++gq) {
+        const int j0 = DIR ? 8 - 8 * gq : 8 * gq;
         float tv[8];
         if (c0 + j0 < Q) {
             const float4 t0 = *reinterpret_cast<const float4 *>(tt + j0), t1 = *reinterpret_cast<const float4 *>(tt + j0 + 4);
@@ -184,40 +184,44 @@ __global__ void __launch_bounds__(kThreads, 2) intra_decay_grad(Dims d, View x, 
         float diag[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) diag[i] = 0.f;
-        const int nchunk = nt / 32 + ((nt % 32) ? 1 : 0);
-        for (int t = 0; t < nchunk; ++t) {
-            const int c0 = (dirn ? nchunk - 1 - t : t) * 32;
-            // a chunk contributes only where it overlaps this warp's triangle (s < l forward, s > l reverse)
-            const bool live = dirn ? (c0 + 31 > wl_min) : (c0 < wl_max);
-            float rm[32];
+        // 16-column strips; the CB values of the next strip are requested before the current one is processed
+        const int nstrip = nt / 16;
+        auto strip_c0 = [&](int t) { return (dirn ? nstrip - 1 - t : t) * 16; };
+        auto strip_live = [&](int c0) { return dirn ? (c0 + 15 > wl_min) : (c0 < wl_max); };
+        float4 cbn[4];
+        auto load_cb = [&](int c0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) rm[j] = 0.f;
+            for (int q = 0; q < 4; ++q)
+                cbn[q] = (row_on && c0 + q * 4 < Q) ? __ldg(reinterpret_cast<const float4 *>(cbrow + c0 + q * 4))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        if (strip_live(strip_c0(0))) load_cb(strip_c0(0));
+        for (int t = 0; t < nstrip; ++t) {
+            const int c0 = strip_c0(t);
+            // a strip contributes only where it overlaps this warp's triangle (s < l forward, s > l reverse)
+            const bool live = strip_live(c0);
+            float rm[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) rm[j] = 0.f;
             if (live) {
-                float v[32];
-                tmem_ld32(tmem_lane_base(p.tmem) + c0, v);
+                float v[16], cbv[16];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    cbv[4 * q] = cbn[q].x; cbv[4 * q + 1] = cbn[q].y; cbv[4 * q + 2] = cbn[q].z; cbv[4 * q + 3] = cbn[q].w;
+                }
+                tmem_ld16(tmem_lane_base(p.tmem) + c0, v);
+                if (t + 1 < nstrip && strip_live(strip_c0(t + 1))) load_cb(strip_c0(t + 1));
                 if (row_on) {
-                    float cbv[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (c0 + j < Q) {
-                            float t8[8];
-                            ldg8f(cbrow + c0 + j, t8);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) cbv[j + i] = t8[i];
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) cbv[j + i] = 0.f;
-                        }
-                    }
                     if (!dirn) sweep_strip<0>(v, cbv, rm, run, tf + c0, sf[l], c0, l, Q);
                     else sweep_strip<1>(v, cbv, rm, run, tb + c0, sb[l], c0, l, Q);
                 }
+            } else if (t + 1 < nstrip && strip_live(strip_c0(t + 1))) {
+                load_cb(strip_c0(t + 1));
             }
             // forward warps own the 8-column groups left of the diagonal group, reverse warps those right of it
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
+            for (int j = 0; j < 16; j += 8) {
                 const int jc = (c0 + j) >> 3;
-                if (c0 + j >= nt) continue;
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = rm[j + i];
