@@ -121,3 +121,58 @@ def test_phased_calls_with_chained_boundaries_match_unsharded_operator(dtype, to
                 dD=leaves[5].grad, dz=leaves[6].grad, ddt_bias=leaves[7].grad)
     for k in got:
         assert max_rel_err(got[k], want[k]) < tol, k
+
+
+def _nccl_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from ssd.bi.sequence_parallel import bimamba_chunk_scan_combined_seq_parallel
+        from ssd.bi.ssd_combined import bimamba_chunk_scan_combined
+        b, L, H, P, G, N, Q = 1, 2048, 4, 64, 2, 128, 256
+        g = torch.Generator().manual_seed(5)
+        mk = lambda *s: torch.randn(*s, generator=g)
+        bf = torch.bfloat16
+        x, B, C, dout = (mk(b, L, H, P).to(bf).cuda(), mk(b, L, G, N).to(bf).cuda(), mk(b, L, G, N).to(bf).cuda(),
+                         mk(b, L, H, P).to(bf).cuda())
+        dt = (mk(b, L, H) - 5.0).cuda()
+        A = (-torch.exp(torch.rand(H, generator=g) * 2.0)).cuda()
+        D = mk(H, P).cuda()
+        full = [t.clone().requires_grad_(True) for t in (x, dt, A, B, C, D)]
+        ref = bimamba_chunk_scan_combined(*full[:5], Q, D=full[5], dt_softplus=True)
+        ref.backward(dout)
+        sl = slice(rank * L // world, (rank + 1) * L // world)
+        mine = [x[:, sl].clone().requires_grad_(True), dt[:, sl].clone().requires_grad_(True), A.clone().requires_grad_(True),
+                B[:, sl].clone().requires_grad_(True), C[:, sl].clone().requires_grad_(True), D.clone().requires_grad_(True)]
+        out = bimamba_chunk_scan_combined_seq_parallel(*mine[:5], Q, D=mine[5], dt_softplus=True)
+        out.backward(dout[:, sl])
+        dA, dD = mine[2].grad.clone(), mine[5].grad.clone()
+        dist.all_reduce(dA)
+        dist.all_reduce(dD)
+        torch.cuda.synchronize()
+        ret[rank] = dict(out=max_rel_err(out, ref[:, sl]), dx=max_rel_err(mine[0].grad, full[0].grad[:, sl]),
+                         ddt=max_rel_err(mine[1].grad, full[1].grad[:, sl]), dB=max_rel_err(mine[3].grad, full[3].grad[:, sl]),
+                         dC=max_rel_err(mine[4].grad, full[4].grad[:, sl]), dA=max_rel_err(dA, full[2].grad),
+                         dD=max_rel_err(dD, full[5].grad))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_sequence_parallel_over_nccl_matches_single_gpu():
+    """Real process group: one rank per GPU, boundary states exchanged with NCCL all-gather."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    for r in range(world):
+        assert all(v < 2e-2 for v in ret[r].values()), (r, dict(ret[r]))
