@@ -114,6 +114,13 @@ CASES = [
     ("fp16_large_state", (1, 256, 2, 128, 2, 256, 128), torch.float16, dict(has_z=True, softplus=False, has_bias=False,
                                                                            D_hdim=True)),
     ("bf16_dt_bf16", (1, 256, 2, 32, 1, 32, 64), torch.bfloat16, dict(dt_dtype=torch.bfloat16)),
+    # shapes that take the TMA-fed kernels (headdim, dstate multiples of 64; chunk 128 / 256)
+    ("tma_fp16_z", (1, 512, 4, 64, 2, 128, 256), torch.float16, dict(has_z=True)),
+    ("tma_bf16_ragged_tail", (2, 600, 4, 64, 1, 128, 256), torch.bfloat16, dict(has_z=True, D_hdim=True)),
+    ("tma_bf16_groups8_like_config3", (1, 1024, 16, 64, 8, 128, 256), torch.bfloat16, dict(D_hdim=True, has_bias=False)),
+    ("tma_bf16_dstate64_like_config4", (2, 512, 8, 64, 1, 64, 256), torch.bfloat16, dict(softplus=False, has_bias=False)),
+    ("tma_bf16_chunk128_headdim128", (1, 384, 2, 128, 1, 128, 128), torch.bfloat16, dict(has_z=True)),
+    ("tma_bf16_dstate256", (1, 256, 2, 64, 2, 256, 128), torch.bfloat16, dict()),
 ]
 
 
