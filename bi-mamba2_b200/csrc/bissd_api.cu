@@ -471,9 +471,23 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                 BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
                     dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
             }
-            BISSD_ALLOW(tc::intra_decay_grad<T>, smem_in);
-            BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
-                dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
+            bool intra_done = false;
+            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+                CUtensorMap mG, mX;
+                if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
+                    map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
+                    BISSD_ALLOW((tc::intra_decay_grad<T, true>), smem_in);
+                    BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T, true><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
+                        dg, mG, mX, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
+                    intra_done = true;
+                }
+            }
+            if (!intra_done) {
+                CUtensorMap none{};
+                BISSD_ALLOW((tc::intra_decay_grad<T, false>), smem_in);
+                BISSD_LAUNCH("tc_intra_decay_grad", tc::intra_decay_grad<T, false><<<dim3(bch, nlt_tc), tc::kThreads, smem_in, s>>>(
+                    dg, none, none, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b), status));
+            }
         }
     }
     if (!intra_tc) {

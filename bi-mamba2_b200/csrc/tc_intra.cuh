@@ -133,8 +133,10 @@ __device__ __forceinline__ void sweep_strip(const float (&v)[16], const float (&
 // over l by an MMA with a ones matrix.  Output: partial da over this row tile, out_part[row tile][b,H,nc,Q]
 // (the two row tiles of a 256-chunk are added by the consumer); tile 0 zero-fills part 1 when there is only one tile.
 // grid (b*nc*H, ceil(Q/128)); n_tile = round16(Q); tables 3*Q floats + 128*8 exchange floats.
-template <class T>
-__global__ void __launch_bounds__(kThreads, 2) intra_decay_grad(Dims d, View x, View z, View dout, const float *dt_out,
+template <class T, bool TMA>
+__global__ void __launch_bounds__(kThreads, 2) intra_decay_grad(Dims d, const __grid_constant__ CUtensorMap tmG,
+                                                             const __grid_constant__ CUtensorMap tmX, View x, View z,
+                                                             View dout, const float *dt_out,
                                                              const float *cs_f, const float *cs_b, const float *CB,
                                                              float *da_part0, float *da_part1, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -164,7 +166,33 @@ __global__ void __launch_bounds__(kThreads, 2) intra_decay_grad(Dims d, View x, 
         return (l0 + r < lim && k < d.P) ? gate8<T>(d, dout, z, b, c * Q + l0 + r, h, k) : zero8();
     };
     auto fb = [&](int r, int k) -> uint4 { return (r < lim && k < d.P) ? ld8v<T>(x, b, c * Q + r, h, k) : zero8(); };
-    bool ok = umma_gemm<T, false, false>(p, p.tmem, nt, d.P, 0u, fa, fb);
+    bool ok;
+    if (TMA) {
+        // g (128 rows) and x (Q rows) tiles by TMA into the engine's stage buffers, one 64-wide headdim slab per buffer
+        const int npb = d.P / 64;
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(&sh.free_bar[0], (uint32_t)(npb * (16384 + Q * 128)));
+            for (int j = 0; j < npb; ++j) {
+                tma_load4(p.a_stage[j], &tmG, j * 64, h, c * Q + l0, b, &sh.free_bar[0]);
+                tma_load4(p.b_stage[j], &tmX, j * 64, h, c * Q, b, &sh.free_bar[0]);
+            }
+            ok = mbar_wait(&sh.free_bar[0], 0);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, nt);
+                for (int j = 0; j < npb; ++j)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(p.tmem, smem_desc(smem_u32(p.a_stage[j]) + kk * 32, 16, 1024),
+                             smem_desc(smem_u32(p.b_stage[j]) + kk * 32, 16, 1024), idesc, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+        } else {
+            ok = true;
+        }
+        ok = __syncthreads_and(ok);
+    } else {
+        ok = umma_gemm<T, false, false>(p, p.tmem, nt, d.P, 0u, fa, fb);
+    }
     ok = ok && umma_drain(p);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int dirn = warp >> 2;
