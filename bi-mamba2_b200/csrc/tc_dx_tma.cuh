@@ -80,10 +80,6 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
         sh.fail = 0;
         fence_mbar_init();
     }
-    for (int i = tid; i < Q; i += kThreads) {
-        f2[i] = cs_f[base + i] * 1.4426950408889634f;
-        b2[i] = cs_b[base + i] * 1.4426950408889634f;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -100,6 +96,12 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
         for (int j = 0; j < npb; ++j) tma_load4(smG + j * Q * 128, &tmG, j * 64, h, c * Q, b, &sh.bar_x);
     }
     const float *cbt = CBt + ((long long)(b * d.nc + c) * d.G + grp) * Q * Q;
+    // the decay tables are built while the TMA loads are in flight
+    for (int i = tid; i < Q; i += kThreads) {
+        f2[i] = cs_f[base + i] * 1.4426950408889634f;
+        b2[i] = cs_b[base + i] * 1.4426950408889634f;
+    }
+    __syncthreads();
     uint4 ra[4];
     float4 raw[8];                                              // CB values of the step after next, still in flight
     auto load_raw = [&](int s0) {
@@ -195,6 +197,22 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
             }
         }
     }
+    // epilogue operands of the first strip are requested before waiting for the last MMAs
+    const int el = l0 + (warp & 3) * 32 + lane, ec0 = (warp >> 2) * 32;
+    uint4 xr[4], gr[4];
+    float e_dl = 0.f, e_cf = 0.f, e_cb = 0.f, e_tf = 0.f, e_tb = 0.f;
+    if (ok && el < lim) {
+        e_dl = dt_out[base + el];
+        e_cf = cs_f[base + el];
+        e_cb = cs_b[base + el];
+        e_tf = cs_f[base + Q - 1];
+        e_tb = cs_b[base];
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        xr[q] = (ok && el < lim && ec0 < P) ? ld8v<T>(x, b, c * Q + el, h, ec0 + q * 8) : zero8();
+        gr[q] = (ok && el < lim && ec0 < P) ? ld8v<T>(g, b, c * Q + el, h, ec0 + q * 8) : zero8();
+    }
     if (ok) {
         if (tid == 0) umma_commit(&sh.done_bar);
         ok = mbar_wait(&sh.done_bar, 0);
@@ -208,17 +226,18 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
     float wf = 0.f, wb = 0.f, dl = 0.f;
     if (ok) {
         if (l < lim) {
-            dl = dt_out[base + l];
-            wf = __expf(cs_f[base + Q - 1] - cs_f[base + l]);
-            wb = __expf(cs_b[base] - cs_b[base + l]);
+            dl = e_dl;
+            wf = __expf(e_tf - e_cf);
+            wb = __expf(e_tb - e_cb);
         }
         const uint32_t tl = tmem_lane_base(tmem);
         for (int c0 = half * 32; c0 < P; c0 += 64) {
-            uint4 xr[4], gr[4];                                 // requested together, before anything is consumed
+            if (c0 != ec0) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                xr[q] = (l < lim) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
-                gr[q] = (l < lim) ? ld8v<T>(g, b, c * Q + l, h, c0 + q * 8) : zero8();
+                for (int q = 0; q < 4; ++q) {
+                    xr[q] = (l < lim) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
+                    gr[q] = (l < lim) ? ld8v<T>(g, b, c * Q + l, h, c0 + q * 8) : zero8();
+                }
             }
 #pragma unroll
             for (int hs = 0; hs < 2; ++hs) {                    // two 16-column pieces keep the register footprint down

@@ -65,14 +65,6 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
         sh.fail = 0;
         fence_mbar_init();
     }
-    for (int i = tid; i < Q; i += kThreads) {
-        const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
-        const float lg = __log2f(dt_out[base + i]);           // -inf for the zero-padded tail: those columns vanish
-        f2[i] = cf;
-        b2[i] = cb_;
-        tf[i] = cf - lg;
-        tb[i] = cb_ - lg;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -89,6 +81,16 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
         for (int j = 0; j < npb; ++j) tma_load4(smX + j * Q * 128, &tmX, j * 64, h, c * Q, b, &sh.bar_x);
     }
     const float *cbt = CB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q;
+    // the decay tables are built while the TMA loads are in flight
+    for (int i = tid; i < Q; i += kThreads) {
+        const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
+        const float lg = __log2f(dt_out[base + i]);           // -inf for the zero-padded tail: those columns vanish
+        f2[i] = cf;
+        b2[i] = cb_;
+        tf[i] = cf - lg;
+        tb[i] = cb_ - lg;
+    }
+    __syncthreads();
     uint4 ra[4];
     float4 raw[8];                                              // CB values of the step after next, still in flight
     auto load_raw = [&](int s0) {
@@ -184,6 +186,19 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
             }
         }
     }
+    // epilogue operands of the first strip are requested before waiting for the last MMAs
+    const int el = l0 + (warp & 3) * 32 + lane, ec0 = (warp >> 2) * 32;
+    uint4 xr[4], zr[4];
+    float ecf = 0.f, ecb = 0.f;
+    if (ok && el < lim) {
+        ecf = cs_f[base + el];
+        ecb = cs_b[base + el];
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        xr[q] = (ok && el < lim && d.has_D && ec0 < P) ? ld8v<T>(x, b, c * Q + el, h, ec0 + q * 8) : zero8();
+        zr[q] = (ok && el < lim && d.has_z && ec0 < P) ? ld8v<T>(z, b, c * Q + el, h, ec0 + q * 8) : zero8();
+    }
     if (ok) {
         if (tid == 0) umma_commit(&sh.done_bar);
         ok = mbar_wait(&sh.done_bar, 0);
@@ -193,15 +208,16 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
     if (ok) {
         const int l = l0 + (warp & 3) * 32 + lane;
-        const float ef = (l < lim) ? __expf(cs_f[base + l]) : 0.f, eb = (l < lim) ? __expf(cs_b[base + l]) : 0.f;
+        const float ef = (l < lim) ? __expf(ecf) : 0.f, eb = (l < lim) ? __expf(ecb) : 0.f;
         const uint32_t tl = tmem_lane_base(tmem);
         for (int c0 = (warp >> 2) * 32; c0 < P; c0 += 64) {
             // all global operands of this strip are requested before anything is consumed: one round trip, not eight
-            uint4 xr[4], zr[4];
+            if (c0 != ec0) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                xr[q] = (l < lim && d.has_D) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
-                zr[q] = (l < lim && d.has_z) ? ld8v<T>(z, b, c * Q + l, h, c0 + q * 8) : zero8();
+                for (int q = 0; q < 4; ++q) {
+                    xr[q] = (l < lim && d.has_D) ? ld8v<T>(x, b, c * Q + l, h, c0 + q * 8) : zero8();
+                    zr[q] = (l < lim && d.has_z) ? ld8v<T>(z, b, c * Q + l, h, c0 + q * 8) : zero8();
+                }
             }
             float y[32], v[32];
             tmem_ld32(tl + 2 * P + c0, y);
