@@ -15,6 +15,7 @@
 #include "tc_dcb_tma.cuh"
 #include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
+#include "tc_scan_ws.cuh"
 #include "tc_selftest.cuh"
 #include "tc_state_tma.cuh"
 
@@ -89,7 +90,7 @@ static inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 // out); everything after it is fp32 scratch.
 constexpr size_t kWsHeader = 256;
 struct FwdWs {
-    size_t loc, cb, total;
+    size_t loc, cb, cb16, total;
 };
 struct BwdWs {
     size_t cb, cbt, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
@@ -102,6 +103,7 @@ static FwdWs fwd_layout(const Dims &d) {
     const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
     w.loc = o; o = align256(o + 2 * st * 4);
     w.cb = o; o = align256(o + (size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
+    w.cb16 = o; o = align256(o + (size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);      // C.B^T rounded to bf16 (TMA-fed scan)
     w.total = o;
     return w;
 }
@@ -158,6 +160,22 @@ static bool aligned16(const bissd_tensor &t) {
 static bool force_simt() {
     static const bool v = [] { const char *e = getenv("BISSD_FORCE_SIMT"); return e && e[0] == '1'; }();
     return v;
+}
+
+static bool no_ws() {    // BISSD_NO_WS=1: keep the one-tile-per-CTA TMA kernels where a persistent variant exists
+    static const bool v = [] { const char *e = getenv("BISSD_NO_WS"); return e && e[0] == '1'; }();
+    return v;
+}
+static int sm_count() {
+    static int n[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!n[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
+    }
+    return n[dev];
 }
 
 static bool no_tma() {   // BISSD_NO_TMA=1: keep the thread-staged tcgen05 kernels (for A/B comparisons)
@@ -249,9 +267,51 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
             if (tcp) {
                 const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_sc = tc::smem_bytes(ntP, 3 * d.Q);
                 BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
-                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, CB, nullptr, status));
+                const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
+                __nv_bfloat16 *CB16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cb16);
+                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
+                    d, Cm, Bm, ws_path ? nullptr : CB, nullptr, ws_path ? CB16 : nullptr, nullptr, status));
                 bool tma_done = false;
-                if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+                if (ws_path) {
+                    CUtensorMap mC, mCB, mSf, mSb, mX;
+                    const unsigned long long dC[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                    const unsigned long long sC[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+                    const unsigned bC[4] = {64, 1, 128, 1};
+                    const unsigned long long rows = (unsigned long long)d.b * d.nc * d.H * d.P;
+                    bool maps = tc::make_map4(&mC, a.p.x_dtype, a.C.ptr, dC, sC, bC) &&
+                                map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 64) &&
+                                tc::make_map2(&mCB, BISSD_BF16, CB16, d.Q, (unsigned long long)d.b * d.nc * d.G * d.Q, 64, 128) &&
+                                tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
+                                tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P);
+                    if (maps) {
+                        const size_t smem_t = tc::scan_ws_smem(d.P, d.N, d.Q);
+                        const int tiles = bch * (d.Q / tc::kTileM);
+                        const int grid = std::min(sm_count(), tiles);
+                        auto wide = [](const bissd_tensor &t) {   // 32-byte accesses allowed on every row piece
+                            return t.ptr && reinterpret_cast<uintptr_t>(t.ptr) % 32 == 0 && t.stride_batch % 16 == 0 &&
+                                   t.stride_seq % 16 == 0 && t.stride_head % 16 == 0;
+                        };
+                        const int wide_z = d.has_z && wide(a.z);
+                        const int wide_o = wide(a.out) && (!d.has_z || wide(a.out_x));
+#define BISSD_SCAN_WS(NSL, NS)                                                                                          \
+    do {                                                                                                                \
+        BISSD_ALLOW((tc::chunk_scan_ws<T, NSL, NS>), smem_t);                                                           \
+        BISSD_LAUNCH("tc_chunk_scan_ws", tc::chunk_scan_ws<T, NSL, NS><<<grid, tc::kWsThreads, smem_t, s>>>(            \
+            d, mC, mCB, mSf, mSb, mX, x, z, wide_z, a.D, a.dt_out, a.cs_f, a.cs_b, mview_of(a.out), mview_of(a.out_x), wide_o, \
+            status));                                                                                                   \
+    } while (0)
+                        if (d.N == 128 && d.Q == 256) BISSD_SCAN_WS(2, 4);
+                        else if (d.N == 64 && d.Q == 256) BISSD_SCAN_WS(1, 4);
+                        else if (d.N == 128 && d.Q == 128) BISSD_SCAN_WS(2, 2);
+                        else BISSD_SCAN_WS(1, 2);
+#undef BISSD_SCAN_WS
+                        tma_done = true;
+                    } else {                                     // maps refused: produce the fp32 tile after all
+                        BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
+                            d, Cm, Bm, CB, nullptr, nullptr, nullptr, status));
+                    }
+                }
+                if (!tma_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                     CUtensorMap mC, mSf, mSb, mX;
                     const unsigned long long dC[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
                     const unsigned long long sC[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
@@ -372,7 +432,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             part_heads = d.G;
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
-            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), F(w.cbt), status));
+            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, nullptr, status));
             bool dx_done = false;
             if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mB, mEf, mEb, mG;

@@ -61,9 +61,12 @@ template <class T> __device__ __forceinline__ uint4 pack8f(const float *p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// CB[b,c,g,l,s] = C[l].B[s]  (fp32).   grid (b*nc*G, ceil(Q/128)); n_tile = round16(Q); tables: none.
+// CB[b,c,g,l,s] = C[l].B[s].   grid (b*nc*G, ceil(Q/128)); n_tile = round16(Q); tables: none.
+// Outputs, each optional: CB (fp32), CBt (fp32, transposed), CB16 / CBt16 (the same two rounded to bf16, for the
+// kernels that take the tile by TMA and only use it as a factor of a 16-bit MMA operand).
 template <class T>
-__global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, float *CB, float *CBt, int *status) {
+__global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, float *CB, float *CBt, __nv_bfloat16 *CB16,
+                                                   __nv_bfloat16 *CBt16, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
     const int nt = round_up(d.Q, 16);
@@ -83,19 +86,37 @@ __global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, flo
     if (ok) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int l = l0 + (warp & 3) * 32 + lane;
-        float *out = CB + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q + (long long)l * d.Q;
+        const long long tile = ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q;
         for (int c0 = (warp >> 2) * 32; c0 < nt; c0 += 64) {
             float v[32];
             tmem_ld32(tmem_lane_base(p.tmem) + c0, v);
             if (l < d.Q) {
+                if (CB) {
+                    float *out = CB + tile + (long long)l * d.Q;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    if (c0 + j < d.Q) *reinterpret_cast<float4 *>(out + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    for (int j = 0; j < 32; j += 4)
+                        if (c0 + j < d.Q) *reinterpret_cast<float4 *>(out + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
                 if (CBt) {                                              // transposed copy: lanes write consecutive l
-                    float *ot = CBt + ((long long)(b * d.nc + c) * d.G + g) * d.Q * d.Q + l;
+                    float *ot = CBt + tile + l;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < d.Q) ot[(long long)(c0 + j) * d.Q] = v[j];
+                }
+                if (CB16) {
+                    __nv_bfloat16 *out = CB16 + tile + (long long)l * d.Q;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8)
+                        if (c0 + j < d.Q) {
+                            const float o[8] = {v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]};
+                            *reinterpret_cast<uint4 *>(out + c0 + j) = pack8<__nv_bfloat16>(o);
+                        }
+                }
+                if (CBt16) {
+                    __nv_bfloat16 *ot = CBt16 + tile + l;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < d.Q) ot[(long long)(c0 + j) * d.Q] = __float2bfloat16_rn(v[j]);
                 }
             }
         }

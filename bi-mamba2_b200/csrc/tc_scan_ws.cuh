@@ -1,0 +1,535 @@
+// Forward chunk scan, persistent warp-specialised variant (see simt::chunk_scan for the formula).
+//
+// One CTA per SM walks a contiguous range of (batch, chunk, row tile, head) tiles.  Consecutive tiles of one group
+// share the C rows [128 x N] and the 16-bit C.B^T rows [128 x Q]; both stay resident in shared memory while the heads
+// of the group stream through:
+//
+//   warp 0 (one lane)   issues every tcgen05.mma
+//   warp 1 (one lane)   issues every TMA load
+//   warps 2-5           epilogue: TMEM -> registers -> out_x / out in 32-byte pieces (row factors, gate)
+//   warps 6-13          build the masked-decay tile M 64 columns at a time into a ring of stages
+//
+// Accumulators are double-buffered in TMEM (2 x 3P columns), so the epilogue of tile i overlaps the MMAs of tile i+1
+// and the M build of tile i+1/i+2.  The entering states of tile i+1 are requested as soon as the state products of
+// tile i have completed; x of tile i+1 arrives in 64-row pieces, each requested once the MMAs that read the same
+// piece of tile i have completed.
+//
+// M[l,s] = CB[l,s] w[l,s] with w = Delta[s] (L_f + L_b)[l,s].  In blocks of 32 rows x 64 columns that lie entirely
+// below (above) the diagonal, w factorises around a reference index between s and l - both exponents stay <= 0 -
+// into a row factor and a column factor, so only the blocks the diagonal crosses pay one ex2 per element.  A per-head
+// scalar D is folded into the diagonal of M.
+//
+// Every blocking point is an mbarrier wait with an attempt limit; a wait that runs out raises a CTA-wide flag that
+// every other wait polls, the status word is set and all roles leave their loops.
+//
+// Shapes: headdim 64, dstate 64 or 128, chunk 128 or 256, 16-bit inputs.
+#pragma once
+#include "tc_kernels.cuh"
+#include "tc_tma.cuh"
+
+namespace bissd {
+namespace tc {
+
+constexpr int kWsBuilderWarps = 8, kWsEpiWarps = 4;
+constexpr int kWsFirstEpi = 2, kWsFirstBuilder = kWsFirstEpi + kWsEpiWarps;
+constexpr int kWsThreads = 32 * (kWsFirstBuilder + kWsBuilderWarps);
+constexpr int kWsMStages = 3;
+
+struct WsShared {
+    uint64_t grp_full, grp_done, st_full, st_done, tab_bar, fin_bar;
+    uint64_t x_full[4], x_free[4];
+    uint64_t m_full[kWsMStages], m_free[kWsMStages];
+    uint64_t acc_full[2], acc_free[2];
+    uint32_t tmem_base;
+    int fail;
+};
+
+inline size_t scan_ws_smem(int P, int N, int Q) {
+    return 1024 + (size_t)(N / 64) * 16384 + (size_t)(Q / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 + (size_t)Q * 128 +
+           (size_t)kWsMStages * kAStageBytes + 2 * 4 * (size_t)Q * 4;
+}
+inline bool scan_ws_ok(int P, int N, int Q) {
+    if (P != 64 || (N != 64 && N != 128) || (Q != 128 && Q != 256)) return false;
+    return scan_ws_smem(P, N, Q) <= 227 * 1024;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait that also gives up when another role has already failed
+__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
+    if (mbar_test(bar, parity)) return true;
+    for (uint32_t i = 0; i < kWaitAttempts; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 7) == 7 && *fail) return false;
+    }
+    *fail = 1;
+    return false;
+}
+// the same for a whole warp: every lane polls, the outcome is made uniform so that .aligned instructions stay legal
+__device__ __forceinline__ bool ws_wait_warp(uint64_t *bar, uint32_t parity, volatile int *fail) {
+    return __all_sync(0xffffffffu, ws_wait(bar, parity, fail));
+}
+
+// Walks (batch, chunk, row tile, head) tiles in the order head fastest; grp numbers the (batch, chunk, row tile,
+// group) sets whose tiles share C and C.B^T.
+struct WsIter {
+    int b, c, rt, h, hr, g, grp;
+    __device__ __forceinline__ void init(const Dims &d, int nrt, int t) {
+        h = t % d.H;
+        int r = t / d.H;
+        rt = r % nrt;
+        r /= nrt;
+        c = r % d.nc;
+        b = r / d.nc;
+        g = h / d.R;
+        hr = h - g * d.R;
+        grp = ((b * d.nc + c) * nrt + rt) * d.G + g;
+    }
+    __device__ __forceinline__ void next(const Dims &d, int nrt) {
+        ++h;
+        if (++hr == d.R) {
+            hr = 0;
+            ++g;
+            ++grp;
+        }
+        if (h == d.H) {
+            h = 0;
+            g = 0;
+            if (++rt == nrt) {
+                rt = 0;
+                if (++c == d.nc) {
+                    c = 0;
+                    ++b;
+                }
+            }
+        }
+    }
+};
+
+__device__ __forceinline__ float tanh_approx(float v) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+// 16 consecutive 16-bit elements (32-byte aligned) from global memory in one access
+__device__ __forceinline__ void ldg16(const void *p, uint4 &lo, uint4 &hi) {
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
+}
+
+// 16 consecutive 16-bit elements to global memory: one 32-byte store when the address allows it
+__device__ __forceinline__ void stg16(void *p, const uint4 &lo, const uint4 &hi, bool wide) {
+    if (wide) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                     "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                     : "memory");
+    } else {
+        reinterpret_cast<uint4 *>(p)[0] = lo;
+        reinterpret_cast<uint4 *>(p)[1] = hi;
+    }
+}
+// 16 fp32 columns of this thread's TMEM lane without the completion wait (see tmem_ld_wait)
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Position in the ring of M stages and the parity of each stage's next "free" phase.
+struct WsRing {
+    uint32_t mb = 0, par = 0, used = 0;
+};
+
+// All stages of one tile whose rows start at l0.  Deliberately a compact runtime loop (the code of all four roles has
+// to stay resident in the instruction caches): per stage wait for the ring slot, then for each of the four 32-row
+// blocks pick - uniformly over the CTA - the factorised form below / above the diagonal or the per-element form.
+template <class T>
+__device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM, const float *tabp, int ns, int l0, int bt,
+                                              int lane, float dfold, WsRing &ring, uint64_t *m_full, uint64_t *m_free,
+                                              volatile int *fail) {
+    const int cc = bt & 7, r0 = bt >> 3, Q = ns * 64;
+    const float *f2 = tabp, *b2 = f2 + Q, *tf = b2 + Q, *tb = tf + Q;
+    const uint32_t swz = (uint32_t)((cc ^ (r0 & 7)) << 4);      // r & 7 is the same for this thread's four rows
+#pragma unroll 1
+    for (int s = 0; s < ns; ++s) {
+        const int s0 = s * 64, sc = s0 + cc * 8;
+        if (ring.used >= kWsMStages &&
+            !ws_wait_warp(&m_free[ring.mb], ((ring.par >> ring.mb) & 1) ^ 1, fail))
+            return false;
+        const uint8_t *slab = smCB + s * 16384;
+        uint8_t *stage = smM + ring.mb * kAStageBytes;
+        float tfv[8], tbv[8], col[8];
+        {
+            const float4 a = *reinterpret_cast<const float4 *>(tf + sc), b = *reinterpret_cast<const float4 *>(tf + sc + 4);
+            tfv[0] = a.x; tfv[1] = a.y; tfv[2] = a.z; tfv[3] = a.w; tfv[4] = b.x; tfv[5] = b.y; tfv[6] = b.z; tfv[7] = b.w;
+            const float4 c = *reinterpret_cast<const float4 *>(tb + sc), e = *reinterpret_cast<const float4 *>(tb + sc + 4);
+            tbv[0] = c.x; tbv[1] = c.y; tbv[2] = c.z; tbv[3] = c.w; tbv[4] = e.x; tbv[5] = e.y; tbv[6] = e.z; tbv[7] = e.w;
+        }
+        // a stage has blocks below the diagonal or above it, never both (rows span 128, columns 64)
+        const bool below = l0 + 127 > s0 + 63 && !(l0 < s0);
+        const float ref = below ? f2[s0 + 63] : b2[s0];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) col[j] = ex2_approx(ref - (below ? tfv[j] : tbv[j]));
+#pragma unroll 1
+        for (int q = 0; q < 4; ++q) {
+            const int r = r0 + 32 * q, l = l0 + r, lo = l0 + 32 * q;
+            const uint4 raw = *reinterpret_cast<const uint4 *>(slab + r * 128 + swz);
+            float v[8];
+            unpack8<__nv_bfloat16>(raw, v);
+            const float fl = f2[l], bl = b2[l];
+            if (lo > s0 + 63 || lo + 31 < s0) {                  // the whole block on one side of the diagonal
+                const float rf = ex2_approx((below ? fl : bl) - ref);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= rf * col[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int sj = sc + j;
+                    const float w = ex2_approx(sj <= l ? fl - tfv[j] : bl - tbv[j]);
+                    v[j] = (sj == l) ? fmaf(v[j], 2.f * w, dfold) : v[j] * w;
+                }
+            }
+            *reinterpret_cast<uint4 *>(stage + r * 128 + swz) = pack8<T>(v);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&m_full[ring.mb]);
+        ring.par ^= 1u << ring.mb;
+        ring.mb = (ring.mb + 1 == kWsMStages) ? 0 : ring.mb + 1;
+        ++ring.used;
+    }
+    return true;
+}
+
+// NSL = dstate / 64, NS = chunk / 64
+template <class T, int NSL, int NS>
+__global__ void __launch_bounds__(kWsThreads, 1)
+chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCB,
+              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
+              const __grid_constant__ CUtensorMap tmX, View x, View z, int wide_z, const float *D, const float *dt_out,
+              const float *cs_f, const float *cs_b, MutView out, MutView out_x, int wide_o, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ WsShared sh;
+    constexpr int P = 64, Q = NS * 64, nrt = Q / kTileM;
+    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *smC = base_sm;                                   // NSL slabs [128 x 64], K-major
+    uint8_t *smCB = smC + NSL * 16384;                        // NS slabs [128 x 64] bf16, K-major
+    uint8_t *smS = smCB + NS * 16384;                         // S_f then S_b: NSL slabs [P x 64] each
+    uint8_t *smX = smS + 2 * NSL * P * 128;                   // [Q x 64], MN-major, in NS pieces of 64 rows
+    uint8_t *smM = smX + Q * 128;                             // kWsMStages stages [128 x 64]
+    float *tab = reinterpret_cast<float *>(smM + kWsMStages * kAStageBytes);   // 2 x (f2, b2, tf, tb)[Q]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int *fail = &sh.fail;
+
+    const int total = d.b * d.nc * nrt * d.H;
+    const int t0 = (int)((long long)total * blockIdx.x / gridDim.x);
+    const int t1 = (int)((long long)total * (blockIdx.x + 1) / gridDim.x);
+    const int nt = t1 - t0;
+    constexpr uint32_t ncols = 512;
+    if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
+    if (tid == 32) {
+        mbar_init(&sh.grp_full, 1);
+        mbar_init(&sh.grp_done, 1);
+        mbar_init(&sh.st_full, 1);
+        mbar_init(&sh.st_done, 1);
+        mbar_init(&sh.tab_bar, kWsBuilderWarps);
+        mbar_init(&sh.fin_bar, 1);
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&sh.x_full[i], 1);
+            mbar_init(&sh.x_free[i], 1);
+        }
+        for (int i = 0; i < kWsMStages; ++i) {
+            mbar_init(&sh.m_full[i], kWsBuilderWarps);
+            mbar_init(&sh.m_free[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.acc_full[i], 1);
+            mbar_init(&sh.acc_free[i], kWsEpiWarps);
+        }
+        sh.fail = 0;
+        fence_mbar_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0) {
+        // --------------------------------------------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            const uint64_t dC = smem_desc(smem_u32(smC), 16, 1024), dS = smem_desc(smem_u32(smS), 16, 1024);
+            const uint64_t dM = smem_desc(smem_u32(smM), 16, 1024), dX = smem_desc(smem_u32(smX), (uint32_t)Q * 128, 1024);
+            constexpr uint32_t idesc_st = instr_desc(AbFmt<T>::v, false, false, P);
+            constexpr uint32_t idesc_m = instr_desc(AbFmt<T>::v, false, true, P);
+            WsIter it;
+            it.init(d, nrt, t0);
+            bool ok = true;
+            int cur_grp = -1;
+            uint32_t ngrp = 0, mb = 0, m_par = 0;
+            for (int i = 0; i < nt && ok; ++i) {
+                const int buf = i & 1;
+                const uint32_t acc = tmem + buf * 3 * P;
+                if (it.grp != cur_grp) {
+                    ok = ws_wait(&sh.grp_full, ngrp & 1, fail);
+                    ++ngrp;
+                    cur_grp = it.grp;
+                }
+                if (ok && i >= 2) ok = ws_wait(&sh.acc_free[buf], ((i >> 1) - 1) & 1, fail);
+                ok = ok && ws_wait(&sh.st_full, i & 1, fail);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int dir = 0; dir < 2; ++dir)
+#pragma unroll
+                    for (int j = 0; j < NSL; ++j)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma(acc + dir * P, dC + ((j * 16384 + kk * 32) >> 4),
+                                 dS + (((dir * NSL + j) * P * 128 + kk * 32) >> 4), idesc_st, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sh.st_done);
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    ok = ok && ws_wait(&sh.m_full[mb], (m_par >> mb) & 1, fail) && ws_wait(&sh.x_full[s], i & 1, fail);
+                    if (ok) {
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma(acc + 2 * P, dM + ((mb * kAStageBytes + kk * 32) >> 4),
+                                 dX + (((s * 64 + kk * 16) * 128) >> 4), idesc_m, (s > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&sh.m_free[mb]);
+                        umma_commit(&sh.x_free[s]);
+                        m_par ^= 1u << mb;
+                        mb = (mb + 1 == kWsMStages) ? 0 : mb + 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&sh.acc_full[buf]);
+                it.next(d, nrt);
+                if (i + 1 < nt && it.grp != cur_grp) umma_commit(&sh.grp_done);   // C and C.B^T may be replaced
+            }
+            if (!ok) {
+                atomicExch(status, kErrMmaTimeout);
+                umma_commit(&sh.fin_bar);                       // leave no MMA in flight
+                mbar_wait(&sh.fin_bar, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------------------------------------- TMA loads
+        if (lane == 0) {
+            WsIter it;
+            it.init(d, nrt, t0);
+            bool ok = true;
+            int cur_grp = -1;
+            int ngrp = 0, loads_st = 0, loads_x[4] = {0, 0, 0, 0};
+            for (int j = 0; j < nt && ok; ++j) {
+                if (it.grp != cur_grp) {
+                    if (ngrp > 0) ok = ws_wait(&sh.grp_done, (ngrp - 1) & 1, fail);
+                    if (!ok) break;
+                    mbar_expect_tx(&sh.grp_full, (uint32_t)((NSL + NS) * 16384));
+#pragma unroll
+                    for (int k = 0; k < NSL; ++k)
+                        tma_load4(smC + k * 16384, &tmC, k * 64, it.g, it.c * Q + it.rt * kTileM, it.b, &sh.grp_full);
+                    const int row = ((it.b * d.nc + it.c) * d.G + it.g) * Q + it.rt * kTileM;
+#pragma unroll
+                    for (int k = 0; k < NS; ++k) tma_load2(smCB + k * 16384, &tmCB, k * 64, row, &sh.grp_full);
+                    cur_grp = it.grp;
+                    ++ngrp;
+                }
+                if (j > 0) ok = ws_wait(&sh.st_done, (j - 1) & 1, fail);
+                if (!ok) break;
+                const int tile = (it.b * d.nc + it.c) * d.H + it.h;
+                mbar_expect_tx(&sh.st_full, (uint32_t)(2 * NSL * P * 128));
+#pragma unroll
+                for (int k = 0; k < NSL; ++k) {
+                    tma_load2(smS + k * P * 128, &tmSf, k * 64, tile * P, &sh.st_full);
+                    tma_load2(smS + (NSL + k) * P * 128, &tmSb, k * 64, tile * P, &sh.st_full);
+                }
+                ++loads_st;
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    if (j > 0) ok = ok && ws_wait(&sh.x_free[s], (j - 1) & 1, fail);
+                    if (ok) {
+                        mbar_expect_tx(&sh.x_full[s], 8192u);
+                        tma_load4(smX + s * 8192, &tmX, 0, it.h, it.c * Q + s * 64, it.b, &sh.x_full[s]);
+                        ++loads_x[s];
+                    }
+                }
+                it.next(d, nrt);
+            }
+            if (!ok) {                                          // leave no load in flight
+                atomicExch(status, kErrMmaTimeout);
+                if (loads_st) mbar_wait(&sh.st_full, (loads_st - 1) & 1);
+                for (int s = 0; s < NS; ++s)
+                    if (loads_x[s]) mbar_wait(&sh.x_full[s], (loads_x[s] - 1) & 1);
+                if (ngrp) mbar_wait(&sh.grp_full, (ngrp - 1) & 1);
+            }
+        }
+    } else if (warp < kWsFirstBuilder) {
+        // ---------------------------------------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;
+        const uint32_t tl = tmem + ((uint32_t)(quarter * 32) << 16);
+        WsIter it;
+        it.init(d, nrt, t0);
+        bool ok = true;
+        uint4 zr[8];
+        auto load_z = [&](const WsIter &w) {
+            const int l = w.rt * kTileM + quarter * 32 + lane;
+            const bool live = d.has_z && l < min(Q, d.L - w.c * Q);
+            const T *zp = static_cast<const T *>(z.ptr) + w.b * z.sb + (long long)(w.c * Q + l) * z.sl + w.h * z.sh;
+            if (!live) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) zr[q] = zero8();
+            } else if (wide_z) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ldg16(zp + q * 16, zr[2 * q], zr[2 * q + 1]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) zr[q] = __ldg(reinterpret_cast<const uint4 *>(zp + q * 8));
+            }
+        };
+        if (nt > 0) load_z(it);
+        for (int i = 0; i < nt && ok; ++i) {
+            const int buf = i & 1;
+            const int lim = min(Q, d.L - it.c * Q);
+            const int l = it.rt * kTileM + quarter * 32 + lane;
+            const long long base = ((long long)(it.b * d.H + it.h) * d.nc + it.c) * Q;
+            const bool live = l < lim;
+            float ecf = 0.f, ecb = 0.f;
+            if (live) {
+                ecf = cs_f[base + l];
+                ecb = cs_b[base + l];
+            }
+            const int hh = it.h, bb = it.b, row = it.c * Q + l;
+            T *po = static_cast<T *>(out.ptr) + bb * out.sb + (long long)row * out.sl + hh * out.sh;
+            T *px = static_cast<T *>(out_x.ptr) + bb * out_x.sb + (long long)row * out_x.sl + hh * out_x.sh;
+            ok = ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail);
+            if (!ok) break;
+            tc_fence_after();
+            const float ef = live ? __expf(ecf) : 0.f, eb = live ? __expf(ecb) : 0.f;
+            const uint32_t acc = tl + buf * 3 * P;
+#pragma unroll
+            for (int c0 = 0; c0 < P; c0 += 16) {
+                uint32_t ry[16], rf[16], rb[16];
+                tmem_ld16_nowait(acc + 2 * P + c0, ry);
+                tmem_ld16_nowait(acc + c0, rf);
+                tmem_ld16_nowait(acc + P + c0, rb);
+                tmem_ld_wait();
+                if (c0 + 16 >= P) {                              // the accumulator is free once the last read has landed
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.acc_free[buf]);
+                }
+                float y[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    y[j] = fmaf(eb, __uint_as_float(rb[j]), fmaf(ef, __uint_as_float(rf[j]), __uint_as_float(ry[j])));
+                if (d.has_D && d.D_hdim && live) {               // per-element D: not folded into M
+#pragma unroll
+                    for (int j = 0; j < 16; j += 8) {
+                        float xv[8];
+                        unpack8<T>(ld8v<T>(x, bb, row, hh, c0 + j), xv);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) y[j + k] = fmaf(D[hh * P + c0 + j + k], xv[k], y[j + k]);
+                    }
+                }
+                float o0[8], o1[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    o0[k] = y[k];
+                    o1[k] = y[8 + k];
+                }
+                if (d.has_z) {
+                    if (live) stg16(px + c0, pack8<T>(o0), pack8<T>(o1), wide_o);
+                    float z0[8], z1[8];
+                    unpack8<T>(zr[c0 >> 3], z0);
+                    unpack8<T>(zr[(c0 >> 3) + 1], z1);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        o0[k] *= 0.5f * z0[k] * (1.f + tanh_approx(0.5f * z0[k]));
+                        o1[k] *= 0.5f * z1[k] * (1.f + tanh_approx(0.5f * z1[k]));
+                    }
+                }
+                if (live) stg16(po + c0, pack8<T>(o0), pack8<T>(o1), wide_o);
+            }
+            it.next(d, nrt);
+            if (i + 1 < nt) load_z(it);                          // a whole tile ahead of its use
+        }
+    } else {
+        // ------------------------------------------------------------------------------------------ M builders
+        const int bt = tid - 32 * kWsFirstBuilder;               // 0 .. 255
+        WsIter it;
+        it.init(d, nrt, t0);
+        bool ok = true;
+        int cur_grp = -1;
+        uint32_t ngrp = 0;
+        WsRing ring;
+        float pcf = 0.f, pcb = 0.f, pdt = 1.f, pD = 0.f;        // next tile's table inputs for entry bt, and its D
+        const bool fold = d.has_D && !d.D_hdim;
+        auto fetch_tab = [&](const WsIter &w) {
+            if (bt < Q) {
+                const long long base = ((long long)(w.b * d.H + w.h) * d.nc + w.c) * Q;
+                pcf = cs_f[base + bt];
+                pcb = cs_b[base + bt];
+                pdt = dt_out[base + bt];
+            }
+            if (fold) pD = D[w.h];
+        };
+        auto write_tab = [&](int which) {
+            if (bt < Q) {
+                float *t = tab + which * 4 * Q;
+                const float cf = pcf * 1.4426950408889634f, cb_ = pcb * 1.4426950408889634f;
+                const float lg = __log2f(pdt);                   // -inf for the zero-padded tail: those columns vanish
+                t[bt] = cf;
+                t[Q + bt] = cb_;
+                t[2 * Q + bt] = cf - lg;
+                t[3 * Q + bt] = cb_ - lg;
+            }
+        };
+        if (nt > 0) {
+            fetch_tab(it);
+            write_tab(0);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tab_bar);
+            ok = ws_wait_warp(&sh.tab_bar, 0, fail);
+        }
+        for (int i = 0; i < nt && ok; ++i) {
+            const float dfold = pD;
+            const int rt = it.rt;
+            const int grp = it.grp;
+            it.next(d, nrt);
+            if (i + 1 < nt) fetch_tab(it);
+            if (grp != cur_grp) {
+                ok = ws_wait_warp(&sh.grp_full, ngrp & 1, fail);
+                ++ngrp;
+                cur_grp = grp;
+                if (!ok) break;
+            }
+            const float *tb_ = tab + (i & 1) * 4 * Q;
+            ok = ws_build_tile<T>(smCB, smM, tb_, NS, rt * kTileM, bt, lane, dfold, ring, sh.m_full, sh.m_free, fail);
+            if (!ok) break;
+            if (i + 1 < nt) {
+                write_tab((i + 1) & 1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.tab_bar);
+                ok = ws_wait_warp(&sh.tab_bar, (i + 1) & 1, fail);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (sh.fail && tid == 0) atomicExch(status, kErrMmaTimeout);
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem, ncols);
+    }
+}
+
+}  // namespace tc
+}  // namespace bissd
