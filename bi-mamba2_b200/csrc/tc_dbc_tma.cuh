@@ -36,7 +36,7 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
     const int nsplit = (N + 127) / 128;
     const int nt = min(N, 128), nnb = nt / 64;
     const int a_bytes = npb * 16384, b_bytes = nnb * P * 128, slot_bytes = a_bytes + b_bytes;
-    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *base_sm = smem_align1024(dyn);
     float *sc = reinterpret_cast<float *>(base_sm + 3 * slot_bytes);               // [2 bufs][2 dirs][128 rows]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x % nsplit, bx = blockIdx.x / nsplit;
@@ -195,7 +195,7 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     __shared__ float rowred[2][kTileM];
     const int P = d.P, N = d.N, Q = d.Q;
     const int nsl = N / 64;
-    uint8_t *smC = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *smC = smem_align1024(dyn);
     uint8_t *smSf = smC + nsl * 16384, *smSb = smSf + nsl * P * 128;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);

@@ -27,7 +27,7 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
     const int P = d.P, Q = d.Q, R = d.R;
     const int npb = P / 64;
     const int stage_bytes = 2 * npb * 16384;
-    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *base_sm = smem_align1024(dyn);
     float *tabs = reinterpret_cast<float *>(base_sm + 3 * stage_bytes);          // [2][4][Q]: f2, b2, tf, tb
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);

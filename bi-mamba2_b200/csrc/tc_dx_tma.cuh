@@ -56,7 +56,7 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
     __shared__ float colred[4][128];
     const int P = d.P, N = d.N, Q = d.Q;
     const int nsl = N / 64, npb = P / 64;
-    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smB = base_sm;
     uint8_t *smEf = smB + nsl * 16384;
     uint8_t *smEb = smEf + nsl * P * 128;

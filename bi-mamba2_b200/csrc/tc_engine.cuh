@@ -28,6 +28,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// First 1024-byte boundary inside the dynamic shared memory.  Plain pointer arithmetic on the array (no round trip
+// through an integer) keeps the shared address space visible to the compiler, so accesses through the result are
+// shared-memory instructions rather than generic ones.
+__device__ __forceinline__ uint8_t *smem_align1024(uint8_t *dyn) {
+    return dyn + ((1024u - (smem_u32(dyn) & 1023u)) & 1023u);
+}
+
 // ---- mbarrier ----------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -27,7 +27,7 @@ struct Carve {
 };
 __device__ __forceinline__ Carve carve(uint8_t *dyn, int n_tile) {
     Carve c;
-    c.stage = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    c.stage = smem_align1024(dyn);
     c.tab = reinterpret_cast<float *>(c.stage + 2 * kAStageBytes + 2 * b_stage_bytes(n_tile));
     return c;
 }

@@ -41,7 +41,7 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     __shared__ ScanShared sh;
     const int P = d.P, N = d.N, Q = d.Q;
     const int nsl = N / 64, npb = P / 64;
-    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smC = base_sm;                                   // nsl slabs [128 x 64]
     uint8_t *smSf = smC + nsl * 16384;                        // nsl slabs [P x 64]
     uint8_t *smSb = smSf + nsl * P * 128;

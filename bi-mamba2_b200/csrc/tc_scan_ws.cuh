@@ -6,8 +6,9 @@
 //
 //   warp 0 (one lane)   issues every tcgen05.mma
 //   warp 1 (one lane)   issues every TMA load
-//   warps 2-5           epilogue: TMEM -> registers -> out_x / out in 32-byte pieces (row factors, gate)
-//   warps 6-13          build the masked-decay tile M 64 columns at a time into a ring of stages
+//   warps 2-9           epilogue: TMEM -> registers -> out_x / out in 32-byte pieces (row factors, gate);
+//                       warps w and w+4 share 32 rows and take 32 columns each
+//   warps 10-17         build the masked-decay tile M 64 columns at a time into a ring of stages
 //
 // Accumulators are double-buffered in TMEM (2 x 3P columns), so the epilogue of tile i overlaps the MMAs of tile i+1
 // and the M build of tile i+1/i+2.  The entering states of tile i+1 are requested as soon as the state products of
@@ -30,7 +31,7 @@
 namespace bissd {
 namespace tc {
 
-constexpr int kWsBuilderWarps = 8, kWsEpiWarps = 4;
+constexpr int kWsBuilderWarps = 8, kWsEpiWarps = 8;
 constexpr int kWsFirstEpi = 2, kWsFirstBuilder = kWsFirstEpi + kWsEpiWarps;
 constexpr int kWsThreads = 32 * (kWsFirstBuilder + kWsBuilderWarps);
 constexpr int kWsMStages = 3;
@@ -147,6 +148,33 @@ struct WsRing {
     uint32_t mb = 0, par = 0, used = 0;
 };
 
+// raw (8 bf16) * rf * col[j], as the operand type T.  bf16: the product is formed in packed bf16 arithmetic (one more
+// rounding than the fp32 route, a third of the instructions); f16: through fp32.
+template <class T>
+__device__ __forceinline__ uint4 ws_scale8(const uint4 &raw, float rf, const float (&col)[8]);
+template <>
+__device__ __forceinline__ uint4 ws_scale8<__nv_bfloat16>(const uint4 &raw, float rf, const float (&col)[8]) {
+    uint4 o;
+    const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 w = __floats2bfloat162_rn(rf * col[2 * k], rf * col[2 * k + 1]);
+        const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&in[k]), w);
+        out[k] = *reinterpret_cast<const uint32_t *>(&v);
+    }
+    o.x = out[0]; o.y = out[1]; o.z = out[2]; o.w = out[3];
+    return o;
+}
+template <>
+__device__ __forceinline__ uint4 ws_scale8<__half>(const uint4 &raw, float rf, const float (&col)[8]) {
+    float v[8];
+    unpack8<__nv_bfloat16>(raw, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= rf * col[j];
+    return pack8<__half>(v);
+}
+
 // All stages of one tile whose rows start at l0.  Deliberately a compact runtime loop (the code of all four roles has
 // to stay resident in the instruction caches): per stage wait for the ring slot, then for each of the four 32-row
 // blocks pick - uniformly over the CTA - the factorised form below / above the diagonal or the per-element form.
@@ -177,26 +205,37 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
         const float ref = below ? f2[s0 + 63] : b2[s0];
 #pragma unroll
         for (int j = 0; j < 8; ++j) col[j] = ex2_approx(ref - (below ? tfv[j] : tbv[j]));
+        // rows in two halves of 64 (two 32-row blocks of the same kind each), the two blocks interleaved
 #pragma unroll 1
-        for (int q = 0; q < 4; ++q) {
-            const int r = r0 + 32 * q, l = l0 + r, lo = l0 + 32 * q;
-            const uint4 raw = *reinterpret_cast<const uint4 *>(slab + r * 128 + swz);
-            float v[8];
-            unpack8<__nv_bfloat16>(raw, v);
-            const float fl = f2[l], bl = b2[l];
-            if (lo > s0 + 63 || lo + 31 < s0) {                  // the whole block on one side of the diagonal
-                const float rf = ex2_approx((below ? fl : bl) - ref);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] *= rf * col[j];
+        for (int qp = 0; qp < 2; ++qp) {
+            const int lo = l0 + 64 * qp;
+            const int ra = r0 + 64 * qp, rb = ra + 32, la = l0 + ra, lb = l0 + rb;
+            const uint4 rawa = *reinterpret_cast<const uint4 *>(slab + ra * 128 + swz);
+            const uint4 rawb = *reinterpret_cast<const uint4 *>(slab + rb * 128 + swz);
+            uint4 oa, ob;
+            if (lo > s0 + 63 || lo + 63 < s0) {                  // both blocks on one side of the diagonal
+                const float rfa = ex2_approx((below ? f2[la] : b2[la]) - ref);
+                const float rfb = ex2_approx((below ? f2[lb] : b2[lb]) - ref);
+                oa = ws_scale8<T>(rawa, rfa, col);
+                ob = ws_scale8<T>(rawb, rfb, col);
             } else {
+                float va[8], vb[8];
+                unpack8<__nv_bfloat16>(rawa, va);
+                unpack8<__nv_bfloat16>(rawb, vb);
+                const float fa = f2[la], ba = b2[la], fb = f2[lb], bb = b2[lb];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int sj = sc + j;
-                    const float w = ex2_approx(sj <= l ? fl - tfv[j] : bl - tbv[j]);
-                    v[j] = (sj == l) ? fmaf(v[j], 2.f * w, dfold) : v[j] * w;
+                    const float wa = ex2_approx(sj <= la ? fa - tfv[j] : ba - tbv[j]);
+                    const float wb = ex2_approx(sj <= lb ? fb - tfv[j] : bb - tbv[j]);
+                    va[j] = (sj == la) ? fmaf(va[j], 2.f * wa, dfold) : va[j] * wa;
+                    vb[j] = (sj == lb) ? fmaf(vb[j], 2.f * wb, dfold) : vb[j] * wb;
                 }
+                oa = pack8<T>(va);
+                ob = pack8<T>(vb);
             }
-            *reinterpret_cast<uint4 *>(stage + r * 128 + swz) = pack8<T>(v);
+            *reinterpret_cast<uint4 *>(stage + ra * 128 + swz) = oa;
+            *reinterpret_cast<uint4 *>(stage + rb * 128 + swz) = ob;
         }
         fence_async_smem();
         __syncwarp();
@@ -218,10 +257,10 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
     extern __shared__ uint8_t dyn[];
     __shared__ WsShared sh;
     constexpr int P = 64, Q = NS * 64, nrt = Q / kTileM;
-    uint8_t *base_sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smC = base_sm;                                   // NSL slabs [128 x 64], K-major
     uint8_t *smCB = smC + NSL * 16384;                        // NS slabs [128 x 64] bf16, K-major
-    uint8_t *smS = smCB + NS * 16384;                         // S_f then S_b: NSL slabs [P x 64] each
+    uint8_t *smS = smCB + NS * 16384;                         // per K slab: S_f [P x 64] then S_b [P x 64]
     uint8_t *smX = smS + 2 * NSL * P * 128;                   // [Q x 64], MN-major, in NS pieces of 64 rows
     uint8_t *smM = smX + Q * 128;                             // kWsMStages stages [128 x 64]
     float *tab = reinterpret_cast<float *>(smM + kWsMStages * kAStageBytes);   // 2 x (f2, b2, tf, tb)[Q]
@@ -266,7 +305,7 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
         if (lane == 0) {
             const uint64_t dC = smem_desc(smem_u32(smC), 16, 1024), dS = smem_desc(smem_u32(smS), 16, 1024);
             const uint64_t dM = smem_desc(smem_u32(smM), 16, 1024), dX = smem_desc(smem_u32(smX), (uint32_t)Q * 128, 1024);
-            constexpr uint32_t idesc_st = instr_desc(AbFmt<T>::v, false, false, P);
+            constexpr uint32_t idesc_st = instr_desc(AbFmt<T>::v, false, false, 2 * P);
             constexpr uint32_t idesc_m = instr_desc(AbFmt<T>::v, false, true, P);
             WsIter it;
             it.init(d, nrt, t0);
@@ -285,14 +324,13 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
                 ok = ok && ws_wait(&sh.st_full, i & 1, fail);
                 if (!ok) break;
                 tc_fence_after();
+                // both directions in one N = 2P product: B rows 0..P-1 are S_f, rows P..2P-1 are S_b
 #pragma unroll
-                for (int dir = 0; dir < 2; ++dir)
+                for (int j = 0; j < NSL; ++j)
 #pragma unroll
-                    for (int j = 0; j < NSL; ++j)
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma(acc + dir * P, dC + ((j * 16384 + kk * 32) >> 4),
-                                 dS + (((dir * NSL + j) * P * 128 + kk * 32) >> 4), idesc_st, (j > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(acc, dC + ((j * 16384 + kk * 32) >> 4), dS + ((j * 2 * P * 128 + kk * 32) >> 4), idesc_st,
+                             (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&sh.st_done);
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
@@ -348,8 +386,8 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
                 mbar_expect_tx(&sh.st_full, (uint32_t)(2 * NSL * P * 128));
 #pragma unroll
                 for (int k = 0; k < NSL; ++k) {
-                    tma_load2(smS + k * P * 128, &tmSf, k * 64, tile * P, &sh.st_full);
-                    tma_load2(smS + (NSL + k) * P * 128, &tmSb, k * 64, tile * P, &sh.st_full);
+                    tma_load2(smS + (2 * k) * P * 128, &tmSf, k * 64, tile * P, &sh.st_full);
+                    tma_load2(smS + (2 * k + 1) * P * 128, &tmSb, k * 64, tile * P, &sh.st_full);
                 }
                 ++loads_st;
 #pragma unroll
@@ -373,25 +411,25 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
         }
     } else if (warp < kWsFirstBuilder) {
         // ---------------------------------------------------------------------------------------------- epilogue
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, ch = ((warp - kWsFirstEpi) >> 2) * 32;   // rows 32*quarter.., columns ch..ch+31
         const uint32_t tl = tmem + ((uint32_t)(quarter * 32) << 16);
         WsIter it;
         it.init(d, nrt, t0);
         bool ok = true;
-        uint4 zr[8];
+        uint4 zr[4];
         auto load_z = [&](const WsIter &w) {
             const int l = w.rt * kTileM + quarter * 32 + lane;
             const bool live = d.has_z && l < min(Q, d.L - w.c * Q);
-            const T *zp = static_cast<const T *>(z.ptr) + w.b * z.sb + (long long)(w.c * Q + l) * z.sl + w.h * z.sh;
+            const T *zp = static_cast<const T *>(z.ptr) + w.b * z.sb + (long long)(w.c * Q + l) * z.sl + w.h * z.sh + ch;
             if (!live) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) zr[q] = zero8();
+                for (int q = 0; q < 4; ++q) zr[q] = zero8();
             } else if (wide_z) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) ldg16(zp + q * 16, zr[2 * q], zr[2 * q + 1]);
+                for (int q = 0; q < 2; ++q) ldg16(zp + q * 16, zr[2 * q], zr[2 * q + 1]);
             } else {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) zr[q] = __ldg(reinterpret_cast<const uint4 *>(zp + q * 8));
+                for (int q = 0; q < 4; ++q) zr[q] = __ldg(reinterpret_cast<const uint4 *>(zp + q * 8));
             }
         };
         if (nt > 0) load_z(it);
@@ -407,21 +445,21 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
                 ecb = cs_b[base + l];
             }
             const int hh = it.h, bb = it.b, row = it.c * Q + l;
-            T *po = static_cast<T *>(out.ptr) + bb * out.sb + (long long)row * out.sl + hh * out.sh;
-            T *px = static_cast<T *>(out_x.ptr) + bb * out_x.sb + (long long)row * out_x.sl + hh * out_x.sh;
+            T *po = static_cast<T *>(out.ptr) + bb * out.sb + (long long)row * out.sl + hh * out.sh + ch;
+            T *px = static_cast<T *>(out_x.ptr) + bb * out_x.sb + (long long)row * out_x.sl + hh * out_x.sh + ch;
             ok = ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail);
             if (!ok) break;
             tc_fence_after();
             const float ef = live ? __expf(ecf) : 0.f, eb = live ? __expf(ecb) : 0.f;
-            const uint32_t acc = tl + buf * 3 * P;
+            const uint32_t acc = tl + buf * 3 * P + ch;
 #pragma unroll
-            for (int c0 = 0; c0 < P; c0 += 16) {
+            for (int c0 = 0; c0 < 32; c0 += 16) {
                 uint32_t ry[16], rf[16], rb[16];
                 tmem_ld16_nowait(acc + 2 * P + c0, ry);
                 tmem_ld16_nowait(acc + c0, rf);
                 tmem_ld16_nowait(acc + P + c0, rb);
                 tmem_ld_wait();
-                if (c0 + 16 >= P) {                              // the accumulator is free once the last read has landed
+                if (c0 + 16 >= 32) {                             // the accumulator is free once the last read has landed
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh.acc_free[buf]);
@@ -434,9 +472,9 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 16; j += 8) {
                         float xv[8];
-                        unpack8<T>(ld8v<T>(x, bb, row, hh, c0 + j), xv);
+                        unpack8<T>(ld8v<T>(x, bb, row, hh, ch + c0 + j), xv);
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) y[j + k] = fmaf(D[hh * P + c0 + j + k], xv[k], y[j + k]);
+                        for (int k = 0; k < 8; ++k) y[j + k] = fmaf(D[hh * P + ch + c0 + j + k], xv[k], y[j + k]);
                     }
                 }
                 float o0[8], o1[8];

@@ -11,7 +11,7 @@ template <class T, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads) selftest_gemm(const T *A, const T *B, float *C, int N, int K, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
-    uint8_t *stage = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *stage = smem_align1024(dyn);
     Pipe p;
     pipe_init(p, &sh, stage, 256 * 128, 256, status);
     auto fa = [&](int r, int k) -> uint4 {

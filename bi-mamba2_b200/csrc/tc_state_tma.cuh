@@ -27,7 +27,7 @@ state_gemm_tma(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
     __shared__ uint32_t tmem_slot;
     const int P = d.P, N = d.N, Q = d.Q;
     const int npb = P / 64;
-    uint8_t *smA = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    uint8_t *smA = smem_align1024(dyn);
     uint8_t *smX = smA + 2 * Q * 128;
     float *w = reinterpret_cast<float *>(smX + npb * Q * 128);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
