@@ -131,7 +131,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dCB = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
-    w.dDpart = take((size_t)d.b * d.nc * d.H * w.nlt * d.P * 4);
+    w.dDpart = take((size_t)d.b * d.nc * d.H * std::max(w.nlt, 8) * d.P * 4);   // up to 8 partial rows per (b,c,h)
     w.dApart = take((size_t)d.b * d.nc * d.H * 4);
     w.dbiaspart = take((size_t)d.b * d.nc * d.H * 4);
     w.total = o;
@@ -293,12 +293,15 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                         };
                         const int wide_z = d.has_z && wide(a.z);
                         const int wide_o = wide(a.out) && (!d.has_z || wide(a.out_x));
+                        tc::WsArgs wa{};
+                        wa.x = x; wa.z = z; wa.D = a.D; wa.dt_out = a.dt_out; wa.cs_f = a.cs_f; wa.cs_b = a.cs_b;
+                        wa.out = mview_of(a.out); wa.out_x = mview_of(a.out_x);
+                        wa.wide_z = wide_z; wa.wide_o = wide_o;
 #define BISSD_SCAN_WS(NSL, NS)                                                                                          \
     do {                                                                                                                \
-        BISSD_ALLOW((tc::chunk_scan_ws<T, NSL, NS>), smem_t);                                                           \
-        BISSD_LAUNCH("tc_chunk_scan_ws", tc::chunk_scan_ws<T, NSL, NS><<<grid, tc::kWsThreads, smem_t, s>>>(            \
-            d, mC, mCB, mSf, mSb, mX, x, z, wide_z, a.D, a.dt_out, a.cs_f, a.cs_b, mview_of(a.out), mview_of(a.out_x), wide_o, \
-            status));                                                                                                   \
+        BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 0>), smem_t);                                                            \
+        BISSD_LAUNCH("tc_chunk_scan_ws", tc::ws_kernel<T, NSL, NS, 0><<<grid, tc::kWsThreads, smem_t, s>>>(             \
+            d, mC, mCB, mSf, mSb, mX, wa, status));                                                                     \
     } while (0)
                         if (d.N == 128 && d.Q == 256) BISSD_SCAN_WS(2, 4);
                         else if (d.N == 64 && d.Q == 256) BISSD_SCAN_WS(1, 4);
@@ -425,6 +428,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
+    int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
             nlt = nlt_tc;
@@ -432,9 +436,56 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             part_heads = d.G;
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
-            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, nullptr, status));
+            const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
+            __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt);      // shares the fp32 copy's region
+            BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
+                d, Cm, Bm, F(w.cb), ws_path ? nullptr : F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, status));
             bool dx_done = false;
-            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+            if (ws_path) {
+                CUtensorMap mB, mCBt, mEf, mEb, mG;
+                const unsigned long long dB4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
+                const unsigned bB4[4] = {64, 1, 128, 1};
+                const unsigned long long rows = (unsigned long long)d.b * d.nc * d.H * d.P;
+                const char *e16 = static_cast<const char *>(E16);
+                const bool maps = tc::make_map4(&mB, a.p.x_dtype, a.B.ptr, dB4, sB4, bB4) &&
+                                  map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 64) &&
+                                  tc::make_map2(&mCBt, BISSD_BF16, CBt16, d.Q, (unsigned long long)d.b * d.nc * d.G * d.Q, 64, 128) &&
+                                  tc::make_map2(&mEf, a.p.x_dtype, e16, d.N, rows, 64, d.P) &&
+                                  tc::make_map2(&mEb, a.p.x_dtype, e16 + rows * d.N * 2, d.N, rows, 64, d.P);
+                if (maps) {
+                    auto wide = [](const void *ptr, long long sb, long long sl, long long sh) {
+                        return ptr && reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && sb % 16 == 0 && sl % 16 == 0 && sh % 16 == 0;
+                    };
+                    tc::WsArgs wa{};
+                    wa.x = x; wa.z = gv; wa.D = a.D; wa.dt_out = a.dt_out; wa.cs_f = a.cs_f; wa.cs_b = a.cs_b;
+                    wa.out = MutView{a.dx, (long long)d.L * d.H * d.P, (long long)d.H * d.P, (long long)d.P};
+                    wa.out_x = wa.out;
+                    wa.ddt_out = F(w.ddt_out); wa.nf = F(w.nf); wa.nb = F(w.nb); wa.dDpart = F(w.dDpart);
+                    wa.wide_x = wide(x.ptr, x.sb, x.sl, x.sh);
+                    wa.wide_z = wide(gv.ptr, gv.sb, gv.sl, gv.sh);
+                    wa.wide_o = wide(a.dx, 16, 16, 16) && (d.H * d.P) % 16 == 0;
+                    const size_t smem_t = tc::scan_ws_smem(d.P, d.N, d.Q);
+                    const int grid = std::min(sm_count(), bch * nlt_tc);
+#define BISSD_DX_WS(NSL, NS)                                                                                            \
+    do {                                                                                                                \
+        BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 1>), smem_t);                                                            \
+        BISSD_LAUNCH("tc_dx_ws", tc::ws_kernel<T, NSL, NS, 1><<<grid, tc::kWsThreads, smem_t, s>>>(                     \
+            d, mB, mCBt, mEf, mEb, mG, wa, status));                                                                    \
+    } while (0)
+                    if (d.N == 128 && d.Q == 256) BISSD_DX_WS(2, 4);
+                    else if (d.N == 64 && d.Q == 256) BISSD_DX_WS(1, 4);
+                    else if (d.N == 128 && d.Q == 128) BISSD_DX_WS(2, 2);
+                    else BISSD_DX_WS(1, 2);
+#undef BISSD_DX_WS
+                    dx_done = true;
+                    dd_slots = nlt_tc * 4;
+                } else {                                         // maps refused: produce the fp32 transposed tile after all
+                    BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
+                        d, Cm, Bm, nullptr, F(w.cbt), nullptr, nullptr, status));
+                }
+            }
+            if (!dx_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mB, mEf, mEb, mG;
                 const unsigned long long dB4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
                 const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
@@ -576,8 +627,8 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
         F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
-    BISSD_LAUNCH("final_reduce", simt::final_reduce<<<d.H, simt::TB, 0, s>>>(
-        d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,
+    BISSD_LAUNCH("final_reduce", simt::final_reduce<1024><<<d.H, 1024, 0, s>>>(
+        d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,
         d.has_D ? a.dD : nullptr));
     return BISSD_OK;
 }

@@ -917,20 +917,21 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Fixed-order reduction of the per-block partials into dA (H), ddt_bias (H) and dD (H or H*P).  grid (H).
-__global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, const float *dbiaspart,
+// Fixed-order reduction of the per-block partials into dA (H), ddt_bias (H) and dD (H or H*P).  grid (H), NT threads.
+template <int NT>
+__global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, const float *dbiaspart,
                                                    const float *dDpart, int nlt, float *dA, float *ddt_bias, float *dD) {
-    __shared__ float red[TB];
+    __shared__ float red[NT];
     const int h = blockIdx.x;
     const int nbc = d.b * d.nc;
     float sa = 0.f, sbias = 0.f;
-    for (int i = threadIdx.x; i < nbc; i += TB) {
+    for (int i = threadIdx.x; i < nbc; i += NT) {
         sa += dApart[(long long)i * d.H + h];
         sbias += dbiaspart[(long long)i * d.H + h];
     }
     red[threadIdx.x] = sa;
     __syncthreads();
-    for (int o = TB / 2; o > 0; o >>= 1) {
+    for (int o = NT / 2; o > 0; o >>= 1) {
         if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
@@ -938,25 +939,37 @@ __global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, 
     __syncthreads();
     red[threadIdx.x] = sbias;
     __syncthreads();
-    for (int o = TB / 2; o > 0; o >>= 1) {
+    for (int o = NT / 2; o > 0; o >>= 1) {
         if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
     if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = red[0];
     __syncthreads();
     if (dD && dDpart) {
-        // rows of the partial buffer are split over TB / P thread groups, then the groups are added in a fixed order
+        // rows of the partial buffer are split over NT / P thread groups, then the groups are added in a fixed order
         const int rows = nbc * nlt;
-        const int ngrp = d.P <= TB ? TB / d.P : 1;
+        const int ngrp = d.P <= NT ? NT / d.P : 1;
         float tot = 0.f;
-        for (int p0 = 0; p0 < d.P; p0 += TB) {
-            const int p = p0 + (threadIdx.x % (d.P <= TB ? d.P : TB)), grp = d.P <= TB ? threadIdx.x / d.P : 0;
+        for (int p0 = 0; p0 < d.P; p0 += NT) {
+            const int p = p0 + (threadIdx.x % (d.P <= NT ? d.P : NT)), grp = d.P <= NT ? threadIdx.x / d.P : 0;
             float s = 0.f;
-            if (p < d.P && grp < ngrp)
-                for (int r = grp; r < rows; r += ngrp) {
-                    const int i = r / nlt, t = r - i * nlt;
-                    s += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
+            if (p < d.P && grp < ngrp) {
+                // four independent partial sums keep several loads in flight; they are combined in a fixed order
+                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+                int r = grp;
+                for (; r + 3 * ngrp < rows; r += 4 * ngrp) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int rr = r + u * ngrp, i = rr / nlt, t = rr - i * nlt;
+                        s4[u] += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
+                    }
                 }
+                for (; r < rows; r += ngrp) {
+                    const int i = r / nlt, t = r - i * nlt;
+                    s4[0] += dDpart[(((long long)i * d.H + h) * nlt + t) * d.P + p];
+                }
+                s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            }
             __syncthreads();
             red[threadIdx.x] = s;
             __syncthreads();
@@ -971,7 +984,7 @@ __global__ void __launch_bounds__(TB) final_reduce(Dims d, const float *dApart, 
             __syncthreads();
             red[threadIdx.x] = tot;
             __syncthreads();
-            for (int o = TB / 2; o > 0; o >>= 1) {
+            for (int o = NT / 2; o > 0; o >>= 1) {
                 if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
                 __syncthreads();
             }

@@ -1,4 +1,9 @@
-// Forward chunk scan, persistent warp-specialised variant (see simt::chunk_scan for the formula).
+// Persistent warp-specialised kernels for the two "masked-decay tile times activations" passes:
+//   MODE 0  forward chunk scan (see simt::chunk_scan for the formula): operands C, C.B^T, entering states, x
+//   MODE 1  backward dx / ddt_out / "next" terms / dD (see simt::dx_kernel): operands B, (C.B^T)^T, passed state
+//           gradients, g = gated output gradient
+// Both have the shape  acc[l,:] = rf[l] (A.S_f^T)[l,:] + rb[l] (A.S_b^T)[l,:] + sum_s M[l,s] X[s,:]  and differ in
+// the decay tables behind M and in the epilogue.  The description below uses the forward names.
 //
 // One CTA per SM walks a contiguous range of (batch, chunk, row tile, head) tiles.  Consecutive tiles of one group
 // share the C rows [128 x N] and the 16-bit C.B^T rows [128 x Q]; both stay resident in shared memory while the heads
@@ -38,6 +43,7 @@ constexpr int kWsMStages = 3;
 
 struct WsShared {
     uint64_t grp_full, grp_done, st_full, st_done, tab_bar, fin_bar;
+    uint64_t red_bar[4];                                        // MODE 1: row sums of the upper column half are in place
     uint64_t x_full[4], x_free[4];
     uint64_t m_full[kWsMStages], m_free[kWsMStages];
     uint64_t acc_full[2], acc_free[2];
@@ -140,6 +146,12 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[1
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -247,15 +259,162 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
     return true;
 }
 
+// Everything the epilogues and the table builders read or write through plain pointers.
+struct WsArgs {
+    View x;                  // MODE 0: x for a per-element D; MODE 1: x
+    View z;                  // MODE 0: z (gate); MODE 1: g, the gated output gradient
+    const float *D, *dt_out, *cs_f, *cs_b;
+    MutView out, out_x;      // MODE 0: out, out_x; MODE 1: out = dx
+    float *ddt_out, *nf, *nb, *dDpart;   // MODE 1
+    int wide_z, wide_x, wide_o;          // 32-byte accesses allowed on z / x / the outputs
+};
+
+// One step of the transpose-reduce over a warp: every lane holds N values (one per column); lanes whose bit N/2 is
+// clear keep the lower half of the columns and receive the partner's lower half, the others the upper half.  After
+// the steps N = 8, 4, 2 lane j holds in v[0] the sum over the 8 lanes that agree with it above bit 2, for column j & 7.
+template <int N>
+__device__ __forceinline__ void ws_fold(float (&v)[32], int lane) {
+    constexpr int H2 = N / 2;
+    const bool up = (lane & H2) != 0;
+#pragma unroll
+    for (int k = 0; k < H2; ++k) {
+        const float send = up ? v[k] : v[k + H2];
+        const float keep = up ? v[k + H2] : v[k];
+        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, H2);
+    }
+}
+
+// MODE 1 epilogue (one warp: rows 32*quarter.., columns ch..ch+31 of every tile of this CTA):
+//   a = wf (B.E_f^T) + wb (B.E_b^T) + Mt.g;  dx = a Delta + D g;  ddt_out = sum_p a x;  nf / nb = Delta wf|wb sum_p
+//   (B.E^T) x;  dD partial = column sums of g x.  Row sums are completed across the two column halves through shared
+//   memory (three tiles deep: the upper-half warp can run at most two tiles ahead of its partner).
+template <class T, int NS>
+__device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, WsShared &sh, float (*rowred)[3][kTileM],
+                                               uint32_t tl, int quarter, int ch, int lane, WsIter it, int nt, int nrt,
+                                               volatile int *fail) {
+    constexpr int P = 64, Q = NS * 64;
+    const View x = a.x, g = a.z;
+    const int half = ch >> 5, r = quarter * 32 + lane;
+    uint4 xr[4], gr[4];
+    auto load16 = [&](const T *p, bool wide, uint4 &lo, uint4 &hi) {
+        if (wide) {
+            ldg16(p, lo, hi);
+        } else {
+            lo = __ldg(reinterpret_cast<const uint4 *>(p));
+            hi = __ldg(reinterpret_cast<const uint4 *>(p) + 1);
+        }
+    };
+    auto load_rows = [&](const WsIter &w) {
+        const int l = w.rt * kTileM + r;
+        const bool live = l < min(Q, d.L - w.c * Q);
+        const T *xp = static_cast<const T *>(x.ptr) + w.b * x.sb + (long long)(w.c * Q + l) * x.sl + w.h * x.sh + ch;
+        const T *gp = static_cast<const T *>(g.ptr) + w.b * g.sb + (long long)(w.c * Q + l) * g.sl + w.h * g.sh + ch;
+        if (!live) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xr[q] = gr[q] = zero8();
+        } else {
+            load16(xp, a.wide_x, xr[0], xr[1]);
+            load16(xp + 16, a.wide_x, xr[2], xr[3]);
+            load16(gp, a.wide_z, gr[0], gr[1]);
+            load16(gp + 16, a.wide_z, gr[2], gr[3]);
+        }
+    };
+    if (nt > 0) load_rows(it);
+    for (int i = 0; i < nt; ++i) {
+        const int buf = i & 1, slot = i % 3;
+        const int lim = min(Q, d.L - it.c * Q);
+        const int l = it.rt * kTileM + r;
+        const long long base = ((long long)(it.b * d.H + it.h) * d.nc + it.c) * Q;
+        const bool live = l < lim;
+        float dl = 0.f, e1 = 0.f, e2 = 0.f;
+        if (live) {
+            dl = a.dt_out[base + l];
+            e1 = a.cs_f[base + Q - 1] - a.cs_f[base + l];
+            e2 = a.cs_b[base] - a.cs_b[base + l];
+        }
+        const float Dh = (d.has_D && !d.D_hdim) ? a.D[it.h] : 0.f;
+        T *pdx = static_cast<T *>(a.out.ptr) + it.b * a.out.sb + (long long)(it.c * Q + l) * a.out.sl + it.h * a.out.sh + ch;
+        if (!ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail)) break;
+        tc_fence_after();
+        const float wf = live ? __expf(e1) : 0.f, wb = live ? __expf(e2) : 0.f;
+        const uint32_t acc = tl + buf * 3 * P + ch;
+        float rs = 0.f, rsf = 0.f, rsb = 0.f;
+        const long long dslot = ((long long)(it.b * d.nc + it.c) * d.H + it.h) * (nrt * 4) + it.rt * 4 + quarter;
+        uint4 held = zero8();
+#pragma unroll
+        for (int c0 = 0; c0 < 32; c0 += 8) {
+            uint32_t rf[8], rb[8], ri[8];
+            tmem_ld8_nowait(acc + c0, rf);
+            tmem_ld8_nowait(acc + P + c0, rb);
+            tmem_ld8_nowait(acc + 2 * P + c0, ri);
+            tmem_ld_wait();
+            if (c0 + 8 >= 32) {                                  // the accumulator is free once the last read has landed
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.acc_free[buf]);
+            }
+            float xv[8], gv[8], o[8], gx[32];
+            unpack8<T>(xr[c0 >> 3], xv);
+            unpack8<T>(gr[c0 >> 3], gv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float af = __uint_as_float(rf[j]), ab = __uint_as_float(rb[j]);
+                const float av = fmaf(wf, af, fmaf(wb, ab, __uint_as_float(ri[j])));
+                o[j] = av * dl;
+                if (d.has_D) o[j] = fmaf(d.D_hdim ? a.D[it.h * P + ch + c0 + j] : Dh, gv[j], o[j]);
+                rs = fmaf(av, xv[j], rs);
+                rsf = fmaf(af, xv[j], rsf);
+                rsb = fmaf(ab, xv[j], rsb);
+                gx[j] = gv[j] * xv[j];
+            }
+            if (c0 & 8) {
+                if (live) stg16(pdx + c0 - 8, held, pack8<T>(o), a.wide_o);
+            } else {
+                held = pack8<T>(o);
+            }
+            if (d.has_D) {                                       // column sums of g x over this warp's 32 rows
+                ws_fold<8>(gx, lane);
+                ws_fold<4>(gx, lane);
+                ws_fold<2>(gx, lane);
+                float v = gx[0];                                 // sum over the 8 lanes that share lane bits 3 and 4
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (lane < 8) a.dDpart[dslot * P + ch + c0 + lane] = v;
+            }
+        }
+        if (half == 1) {
+            rowred[slot][0][r] = rs;
+            rowred[slot][1][r] = rsf;
+            rowred[slot][2][r] = rsb;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.red_bar[quarter]);
+        } else {
+            if (!ws_wait_warp(&sh.red_bar[quarter], i & 1, fail)) break;
+            rs += rowred[slot][0][r];
+            rsf += rowred[slot][1][r];
+            rsb += rowred[slot][2][r];
+            a.ddt_out[base + l] = rs;
+            a.nf[base + l] = dl * wf * rsf;
+            a.nb[base + l] = dl * wb * rsb;
+        }
+        it.next(d, nrt);
+        if (i + 1 < nt) load_rows(it);                           // a whole tile ahead of their use
+    }
+}
+
 // NSL = dstate / 64, NS = chunk / 64
-template <class T, int NSL, int NS>
+template <class T, int NSL, int NS, int MODE>
 __global__ void __launch_bounds__(kWsThreads, 1)
-chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCB,
-              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
-              const __grid_constant__ CUtensorMap tmX, View x, View z, int wide_z, const float *D, const float *dt_out,
-              const float *cs_f, const float *cs_b, MutView out, MutView out_x, int wide_o, int *status) {
+ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCB,
+          const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
+          const __grid_constant__ CUtensorMap tmX, const WsArgs a, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ WsShared sh;
+    __shared__ float rowred[MODE == 1 ? 3 : 1][3][kTileM];       // MODE 1: three tiles deep, (rs, rsf, rsb) per row
+    const View x = a.x, z = a.z;
+    const float *D = a.D, *dt_out = a.dt_out, *cs_f = a.cs_f, *cs_b = a.cs_b;
+    const MutView out = a.out, out_x = a.out_x;
+    const int wide_z = a.wide_z, wide_o = a.wide_o;
     constexpr int P = 64, Q = NS * 64, nrt = Q / kTileM;
     uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smC = base_sm;                                   // NSL slabs [128 x 64], K-major
@@ -281,6 +440,7 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
         mbar_init(&sh.tab_bar, kWsBuilderWarps);
         mbar_init(&sh.fin_bar, 1);
         for (int i = 0; i < 4; ++i) {
+            mbar_init(&sh.red_bar[i], 1);
             mbar_init(&sh.x_full[i], 1);
             mbar_init(&sh.x_free[i], 1);
         }
@@ -416,6 +576,9 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
         WsIter it;
         it.init(d, nrt, t0);
         bool ok = true;
+        if constexpr (MODE == 1) {
+            ws_epilogue_dx<T, NS>(d, a, sh, rowred, tl, quarter, ch, lane, it, nt, nrt, fail);
+        } else {
         uint4 zr[4];
         auto load_z = [&](const WsIter &w) {
             const int l = w.rt * kTileM + quarter * 32 + lane;
@@ -499,6 +662,7 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
             it.next(d, nrt);
             if (i + 1 < nt) load_z(it);                          // a whole tile ahead of its use
         }
+        }
     } else {
         // ------------------------------------------------------------------------------------------ M builders
         const int bt = tid - 32 * kWsFirstBuilder;               // 0 .. 255
@@ -509,7 +673,7 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
         uint32_t ngrp = 0;
         WsRing ring;
         float pcf = 0.f, pcb = 0.f, pdt = 1.f, pD = 0.f;        // next tile's table inputs for entry bt, and its D
-        const bool fold = d.has_D && !d.D_hdim;
+        const bool fold = MODE == 0 && d.has_D && !d.D_hdim;
         auto fetch_tab = [&](const WsIter &w) {
             if (bt < Q) {
                 const long long base = ((long long)(w.b * d.H + w.h) * d.nc + w.c) * Q;
@@ -523,11 +687,20 @@ chunk_scan_ws(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_cons
             if (bt < Q) {
                 float *t = tab + which * 4 * Q;
                 const float cf = pcf * 1.4426950408889634f, cb_ = pcb * 1.4426950408889634f;
-                const float lg = __log2f(pdt);                   // -inf for the zero-padded tail: those columns vanish
-                t[bt] = cf;
-                t[Q + bt] = cb_;
-                t[2 * Q + bt] = cf - lg;
-                t[3 * Q + bt] = cb_ - lg;
+                if constexpr (MODE == 0) {
+                    const float lg = __log2f(pdt);               // -inf for the zero-padded tail: those columns vanish
+                    t[bt] = cf;
+                    t[Q + bt] = cb_;
+                    t[2 * Q + bt] = cf - lg;
+                    t[3 * Q + bt] = cb_ - lg;
+                } else {
+                    // transposed tile: below the diagonal 2^(b2[s] - b2[l]), above it 2^(f2[s] - f2[l]); with the
+                    // tables negated and swapped the builder's forward formulas produce exactly these
+                    t[bt] = -cb_;
+                    t[Q + bt] = -cf;
+                    t[2 * Q + bt] = -cb_;
+                    t[3 * Q + bt] = -cf;
+                }
             }
         };
         if (nt > 0) {
