@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "simt_kernels.cuh"
 #include "tc_intra.cuh"
+#include "tc_intra_sums.cuh"
 #include "tc_kernels.cuh"
 #include "tc_dbc_tma.cuh"
 #include "tc_dcb_tma.cuh"
@@ -93,7 +94,7 @@ struct FwdWs {
     size_t loc, cb, cb16, total;
 };
 struct BwdWs {
-    size_t cb, cbt, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    size_t cb, cbt, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
     int nblk, nlt, nsplit;
 };
 
@@ -128,6 +129,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
     w.pf = take(hq * 4 * w.nsplit); w.pb = take(hq * 4 * w.nsplit);
     w.da_f = take(hq * 4); w.da_b = take(hq * 4);
+    w.u4 = take(4 * hq * 4);                                         // u_f / u_b of the two row tiles (tc::intra_sums)
     w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dCB = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
@@ -176,6 +178,11 @@ static int sm_count() {
         n[dev] = v;
     }
     return n[dev];
+}
+
+static bool no_sums() {  // BISSD_NO_SUMS=1: keep the prefix-sweep form of the intra-chunk decay gradient
+    static const bool v = [] { const char *e = getenv("BISSD_NO_SUMS"); return e && e[0] == '1'; }();
+    return v;
 }
 
 static bool no_tma() {   // BISSD_NO_TMA=1: keep the thread-staged tcgen05 kernels (for A/B comparisons)
@@ -428,6 +435,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
+    bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
@@ -583,7 +591,19 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
             }
             bool intra_done = false;
-            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q) && !no_sums()) {
+                CUtensorMap mG, mX;
+                if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
+                    map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
+                    const size_t smem_s = tc::intra_sums_smem(d.Q);
+                    BISSD_ALLOW(tc::intra_sums<T>, smem_s);
+                    BISSD_LAUNCH("tc_intra_sums", tc::intra_sums<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_s, s>>>(
+                        dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
+                    intra_done = true;
+                    use_u4 = true;
+                }
+            }
+            if (!intra_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mG, mX;
                 if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
                     map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
@@ -625,7 +645,8 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
-        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), F(w.da_f), F(w.da_b), F(w.dTpart), pass_nblk, nsplit, a.ddt,
+        F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), use_u4 ? nullptr : F(w.da_f), use_u4 ? nullptr : F(w.da_b),
+        use_u4 ? F(w.u4) : nullptr, F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
     BISSD_LAUNCH("final_reduce", simt::final_reduce<1024><<<d.H, 1024, 0, s>>>(
         d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,

@@ -837,13 +837,16 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
 //   ddt = (ddA A + ddt_out), zero where the clamp is active, times sigmoid(pre) when softplus (pre <= 20)
 // Takes over the host glue at src/ssd/bi/ssd_combined.py:456-466 and _chunk_cumsum_bwd_kernel
 // (src/ssd/bi/ssd_chunk_state.py:106-170).  dA / ddt_bias partials per (b,c,h) are reduced by final_reduce.
+// The intra-chunk decay gradients come either as da_f / da_b (already dominance sums) or, when u4 is given, as the
+// per-index differences u_f / u_b = column sums - row sums (four arrays: row tile 0 f, b, row tile 1 f, b), which are
+// added to the terms that are prefix-summed (u_f) and suffix-summed (u_b) exclusively; da_f / da_b are then null.
 // dynamic smem: 8 * Q floats.
 __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
                                                  long long dsh, const float *A, const float *dt_bias,
                                                  const float *dt_out, const float *ddt_out, const float *nf,
                                                  const float *nb, const float *pf, const float *pb, const float *da_f,
-                                                 const float *da_b, const float *dTpart, int nblk, int nsplit,
-                                                 void *ddt, float *dApart, float *dbiaspart) {
+                                                 const float *da_b, const float *u4, const float *dTpart, int nblk,
+                                                 int nsplit, void *ddt, float *dApart, float *dbiaspart) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
@@ -859,53 +862,83 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
         dTf += dTpart[tix * nblk + k];
         dTb += dTpart[((long long)d.b * d.H * d.nc + tix) * nblk + k];
     }
-    // ascending pass: exclusive cumsum of nf, inclusive cumsum of pb (+dT_b at index 0)
-    float c1 = 0.f, c2 = 0.f;
-    for (int l0 = 0; l0 < d.Q; l0 += 32) {
-        const int l = l0 + lane;
-        float v1 = 0.f, v2 = 0.f;
-        if (l < d.Q) {
-            for (int k = 0; k < nsplit; ++k) {
-                v1 += nf[k * split_stride + base + l];
-                v2 += pb[k * split_stride + base + l];
+    // Every global operand of a pass is requested before the first scan step (chunk <= 256: at most 8 tiles of 32), so
+    // the loads of all tiles are in flight together instead of one round trip per tile.
+    constexpr int MAXT = 8;
+    const int ntile = ceil_div(d.Q, 32);
+    // ascending pass: exclusive cumsum of nf (+ u_f), inclusive cumsum of pb (+dT_b at index 0)
+    {
+        float a1[MAXT], a2[MAXT], ex[MAXT];
+#pragma unroll
+        for (int t = 0; t < MAXT; ++t) {
+            a1[t] = a2[t] = ex[t] = 0.f;
+            const int l = t * 32 + lane;
+            if (t < ntile && l < d.Q) {
+                for (int k = 0; k < nsplit; ++k) {
+                    a1[t] += nf[k * split_stride + base + l];
+                    a2[t] += pb[k * split_stride + base + l];
+                }
+                if (u4) a1[t] += u4[base + l] + u4[2 * split_stride + base + l];      // u_f of the two row tiles
+                if (da_f) ex[t] = da_f[base + l] + da_b[base + l];
+                if (l == 0) a2[t] += dTb;
             }
-            if (l == 0) v2 += dTb;
         }
-        const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
-        c1 = __shfl_sync(0xffffffffu, i1, 31);
-        c2 = __shfl_sync(0xffffffffu, i2, 31);
-        if (l < d.Q) acc[l] = (i1 - v1) + i2 + da_f[base + l] + da_b[base + l];
+        float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int t = 0; t < MAXT; ++t) {
+            if (t < ntile) {
+                const int l = t * 32 + lane;
+                const float i1 = warp_incl_scan(a1[t], lane) + c1, i2 = warp_incl_scan(a2[t], lane) + c2;
+                c1 = __shfl_sync(0xffffffffu, i1, 31);
+                c2 = __shfl_sync(0xffffffffu, i2, 31);
+                if (l < d.Q) acc[l] = (i1 - a1[t]) + i2 + ex[t];
+            }
+        }
     }
     __syncwarp();
-    // descending pass: exclusive reverse cumsum of nb, inclusive reverse cumsum of pf (+dT_f at index Q-1)
-    c1 = 0.f;
-    c2 = 0.f;
+    // descending pass: exclusive reverse cumsum of nb (+ u_b), inclusive reverse cumsum of pf (+dT_f at index Q-1)
     float sumA = 0.f, sumB = 0.f;
     const float Ah = A[h];
     const float bias = d.has_bias ? dt_bias[h] : 0.f;
-    for (int t = ceil_div(d.Q, 32) - 1; t >= 0; --t) {
-        const int l = t * 32 + (31 - lane);
-        float v1 = 0.f, v2 = 0.f;
-        if (l < d.Q) {
-            for (int k = 0; k < nsplit; ++k) {
-                v1 += nb[k * split_stride + base + l];
-                v2 += pf[k * split_stride + base + l];
+    {
+        float a1[MAXT], a2[MAXT], dto[MAXT], pre[MAXT], dlo[MAXT];
+#pragma unroll
+        for (int t = 0; t < MAXT; ++t) {
+            a1[t] = a2[t] = dto[t] = pre[t] = dlo[t] = 0.f;
+            const int l = t * 32 + (31 - lane);
+            if (t < ntile && l < d.Q) {
+                for (int k = 0; k < nsplit; ++k) {
+                    a1[t] += nb[k * split_stride + base + l];
+                    a2[t] += pf[k * split_stride + base + l];
+                }
+                if (u4) a1[t] += u4[split_stride + base + l] + u4[3 * split_stride + base + l];   // u_b of the two row tiles
+                if (l == d.Q - 1) a2[t] += dTf;
+                if (l < lim) {
+                    dto[t] = ddt_out[base + l];
+                    dlo[t] = dt_out[base + l];
+                    pre[t] = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
+                }
             }
-            if (l == d.Q - 1) v2 += dTf;
         }
-        const float i1 = warp_incl_scan(v1, lane) + c1, i2 = warp_incl_scan(v2, lane) + c2;
-        c1 = __shfl_sync(0xffffffffu, i1, 31);
-        c2 = __shfl_sync(0xffffffffu, i2, 31);
-        if (l < lim) {
-            const float ddA = acc[l] + (i1 - v1) + i2;
-            float g = ddA * Ah + ddt_out[base + l];
-            const float pre = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
-            const float val = d.softplus ? softplus_ref(pre) : pre;
-            if (val < d.dt_min || val > d.dt_max) g = 0.f;
-            if (d.softplus && pre <= 20.f) g *= sigmoidf_(pre);
-            st_any(ddt, dt_dtype, ((long long)b * d.L + c * d.Q + l) * d.H + h, g);
-            sumA += ddA * dt_out[base + l];
-            sumB += g;
+        float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int t = MAXT - 1; t >= 0; --t) {
+            if (t < ntile) {
+                const int l = t * 32 + (31 - lane);
+                const float i1 = warp_incl_scan(a1[t], lane) + c1, i2 = warp_incl_scan(a2[t], lane) + c2;
+                c1 = __shfl_sync(0xffffffffu, i1, 31);
+                c2 = __shfl_sync(0xffffffffu, i2, 31);
+                if (l < lim) {
+                    const float ddA = acc[l] + (i1 - a1[t]) + i2;
+                    float g = ddA * Ah + dto[t];
+                    const float val = d.softplus ? softplus_ref(pre[t]) : pre[t];
+                    if (val < d.dt_min || val > d.dt_max) g = 0.f;
+                    if (d.softplus && pre[t] <= 20.f) g *= sigmoidf_(pre[t]);
+                    st_any(ddt, dt_dtype, ((long long)b * d.L + c * d.Q + l) * d.H + h, g);
+                    sumA += ddA * dlo[t];
+                    sumB += g;
+                }
+            }
         }
     }
     sumA = warp_sum(sumA);
