@@ -45,16 +45,6 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
     const int g = h / d.R;
     const int lim = min(Q, d.L - c * Q);
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
-    for (int i = threadIdx.x; i < Q; i += kThreads) {
-        const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
-        const float lg = __log2f(dt_out[base + i]);               // -inf on the zero-padded tail: those columns vanish
-        sf[i] = cf;
-        sb[i] = cb_;
-        tf[i] = cf - lg;
-        tb[i] = cb_ - lg;
-        colF[i] = ex2_approx(cs_f[base + (i | 15)] * 1.4426950408889634f - (cf - lg));
-        colB[i] = ex2_approx(cs_b[base + (i & ~15)] * 1.4426950408889634f - (cb_ - lg));
-    }
     Pipe p;
     const uint32_t ncols = tmem_cols(nt);
     pipe_init(p, &sh, cv.stage, b_stage_bytes(nt), ncols, status);
@@ -62,7 +52,8 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     bool ok = true;
     {
-        // g (128 rows) and x (Q rows) by TMA into the stage buffers, one 64-wide headdim slab per buffer
+        // g (128 rows) and x (Q rows) by TMA into the stage buffers, one 64-wide headdim slab per buffer; the decay
+        // tables are built while the tiles are in flight
         const int npb = d.P / 64;
         if (tid == 0) {
             mbar_expect_tx(&sh.free_bar[0], (uint32_t)(npb * (16384 + Q * 128)));
@@ -70,6 +61,18 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
                 tma_load4(p.a_stage[j], &tmG, j * 64, h, c * Q + l0, b, &sh.free_bar[0]);
                 tma_load4(p.b_stage[j], &tmX, j * 64, h, c * Q, b, &sh.free_bar[0]);
             }
+        }
+        for (int i = threadIdx.x; i < Q; i += kThreads) {
+            const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
+            const float lg = __log2f(dt_out[base + i]);               // -inf on the zero-padded tail: those columns vanish
+            sf[i] = cf;
+            sb[i] = cb_;
+            tf[i] = cf - lg;
+            tb[i] = cb_ - lg;
+            colF[i] = ex2_approx(cs_f[base + (i | 15)] * 1.4426950408889634f - (cf - lg));
+            colB[i] = ex2_approx(cs_b[base + (i & ~15)] * 1.4426950408889634f - (cb_ - lg));
+        }
+        if (tid == 0) {
             ok = mbar_wait(&sh.free_bar[0], 0);
             if (ok) {
                 tc_fence_after();
@@ -117,16 +120,24 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
             for (int q = 0; q < 4; ++q)
                 cbn[q] = row_on ? __ldg(reinterpret_cast<const float4 *>(cbrow + c0 + q * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
         };
+        // the accumulator columns and the CB values of strip k+1 are requested before strip k is worked on
+        uint32_t rn[16];
+        tmem_ld16_nowait(tmem_lane_base(p.tmem) + cbeg, rn);
         load_cb(cbeg);
 #pragma unroll 1
         for (int c0 = cbeg; c0 < cend; c0 += 16) {
             float v[16], cbv[16], w[16];
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(rn[j]);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 cbv[4 * q] = cbn[q].x; cbv[4 * q + 1] = cbn[q].y; cbv[4 * q + 2] = cbn[q].z; cbv[4 * q + 3] = cbn[q].w;
             }
-            tmem_ld16(tmem_lane_base(p.tmem) + c0, v);
-            if (c0 + 16 < cend) load_cb(c0 + 16);
+            if (c0 + 16 < cend) {
+                tmem_ld16_nowait(tmem_lane_base(p.tmem) + c0 + 16, rn);
+                load_cb(c0 + 16);
+            }
             // The row sums are taken over the values as rounded to bf16 for the column-sum MMA: only then do row and
             // column sums telescope exactly and the rounding errors stay local instead of accumulating along the scan.
             const int side = (c0 + 15 < wl_min) ? 0 : (c0 > wl_max) ? 1 : 2;   // left of every diagonal / right / mixed
@@ -149,22 +160,21 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
                     w[j] = (!row_on || s == l) ? 0.f : v[j] * cbv[j] * e;
                 }
             }
-            const float o0[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
-            const float o1[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
-            const uint4 q0 = pack8<__nv_bfloat16>(o0), q1 = pack8<__nv_bfloat16>(o1);
+            const uint4 q0 = make_uint4(pack2<__nv_bfloat16>(w[0], w[1]), pack2<__nv_bfloat16>(w[2], w[3]),
+                                        pack2<__nv_bfloat16>(w[4], w[5]), pack2<__nv_bfloat16>(w[6], w[7]));
+            const uint4 q1 = make_uint4(pack2<__nv_bfloat16>(w[8], w[9]), pack2<__nv_bfloat16>(w[10], w[11]),
+                                        pack2<__nv_bfloat16>(w[12], w[13]), pack2<__nv_bfloat16>(w[14], w[15]));
             store8(c0 >> 3, q0);
             store8((c0 >> 3) + 1, q1);
             float rq[16];
-            {
-                float t0[8], t1[8];
-                unpack8<__nv_bfloat16>(q0, t0);
-                unpack8<__nv_bfloat16>(q1, t1);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    rq[j] = t0[j];
-                    rq[8 + j] = t1[j];
-                }
-            }
+            unpack2<__nv_bfloat16>(q0.x, rq[0], rq[1]);
+            unpack2<__nv_bfloat16>(q0.y, rq[2], rq[3]);
+            unpack2<__nv_bfloat16>(q0.z, rq[4], rq[5]);
+            unpack2<__nv_bfloat16>(q0.w, rq[6], rq[7]);
+            unpack2<__nv_bfloat16>(q1.x, rq[8], rq[9]);
+            unpack2<__nv_bfloat16>(q1.y, rq[10], rq[11]);
+            unpack2<__nv_bfloat16>(q1.z, rq[12], rq[13]);
+            unpack2<__nv_bfloat16>(q1.w, rq[14], rq[15]);
             if (side == 0) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) rf += rq[j];

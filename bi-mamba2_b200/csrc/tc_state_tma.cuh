@@ -12,6 +12,20 @@
 namespace bissd {
 namespace tc {
 
+// 8 packed 16-bit values times one factor.  bf16: packed multiply with the factor rounded to bf16 first (a quarter of
+// the instructions of the fp32 route); f16: through fp32, where small factors do not underflow.
+template <class T> __device__ __forceinline__ uint4 scale8_packed(uint4 u, float s) { return scale8<T>(u, s); }
+template <> __device__ __forceinline__ uint4 scale8_packed<__nv_bfloat16>(uint4 u, float s) {
+    const __nv_bfloat162 f = __float2bfloat162_rn(s);
+    uint32_t in[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&in[k]), f);
+        in[k] = *reinterpret_cast<const uint32_t *>(&v);
+    }
+    return make_uint4(in[0], in[1], in[2], in[3]);
+}
+
 inline bool state_tma_ok(int P, int N, int Q) {
     return P % 64 == 0 && P <= 128 && N % 128 == 0 && N <= 256 && (Q == 128 || Q == 256);
 }
@@ -38,11 +52,17 @@ state_gemm_tma(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
     const uint32_t ncols = tmem_cols(P);
     if (warp == 0) tmem_alloc(&tmem_slot, ncols);
-    if (tid == 32) {
+    if (tid == 0) {
+        // the thread that initialises the barriers also issues the loads: they are in flight while the row factors are
+        // computed, and everybody else meets the barriers only after the CTA-wide sync below
         mbar_init(&bar_a, 1);
         mbar_init(&bar_x, 1);
         mbar_init(&bar_done, 1);
         fence_mbar_init();
+        mbar_expect_tx(&bar_x, (uint32_t)(npb * Q * 128));
+        for (int j = 0; j < npb; ++j) tma_load4(smX + j * Q * 128, &tmCol, j * 64, h, c * Q, b, &bar_x);
+        mbar_expect_tx(&bar_a, (uint32_t)(2 * Q * 128));
+        for (int j = 0; j < 2; ++j) tma_load4(smA + j * Q * 128, &tmRow, n0 + j * 64, grp, c * Q, b, &bar_a);
     }
     {
         const float T0 = dir ? cs_b[base] : cs_f[base + Q - 1];
@@ -57,19 +77,13 @@ state_gemm_tma(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    if (tid == 0) {
-        mbar_expect_tx(&bar_x, (uint32_t)(npb * Q * 128));
-        for (int j = 0; j < npb; ++j) tma_load4(smX + j * Q * 128, &tmCol, j * 64, h, c * Q, b, &bar_x);
-        mbar_expect_tx(&bar_a, (uint32_t)(2 * Q * 128));
-        for (int j = 0; j < 2; ++j) tma_load4(smA + j * Q * 128, &tmRow, n0 + j * 64, grp, c * Q, b, &bar_a);
-    }
     bool ok = mbar_wait(&bar_x, 0);
     if (ok) {                                                   // scale row l of the x / g tile by w[l], in place
         const int chunks = npb * Q * 8;
         for (int q = tid; q < chunks; q += kThreads) {
             uint4 *ptr = reinterpret_cast<uint4 *>(smX) + q;
             const int l = (q >> 3) % Q;
-            *ptr = scale8<T>(*ptr, w[l]);
+            *ptr = scale8_packed<T>(*ptr, w[l]);
         }
         fence_async_smem();
     }

@@ -154,5 +154,5 @@ def manual_backward(x, dt, A, B, C, chunk_size, dout, D=None, z=None, dt_bias=No
     if dt_bias is not None:
         res["ddt_bias"] = ddt.sum(dim=(0, 1))
     res.update(E_f=E_f, E_b=E_b, dT_f=dT_f, dT_b=dT_b, Gf=Gf, Gb=Gb, ddt_out=ddt_out, nf=nf, nb=nb, pf=pf, pb=pb,
-               da_f=da_f, da_b=da_b, dCB=dCB, ddA=ddA, dB_states=dB_states, dC_states=dC_states)
+               da_f=da_f, da_b=da_b, Wf=Wf, Wb=Wb, dCB=dCB, ddA=ddA, dB_states=dB_states, dC_states=dC_states)
     return res

@@ -76,3 +76,22 @@ def test_sequence_split_composes():
     left = dense_reference(x[:, :h], dt[:, :h], A, B[:, :h], C[:, :h], initial_states_b=b_right)
     right = dense_reference(x[:, h:], dt[:, h:], A, B[:, h:], C[:, h:], initial_states_f=f_left)
     assert max_rel_err(torch.cat([left, right], 1), full) < 1e-12
+
+
+def test_decay_gradient_telescopes_into_row_and_column_sums():
+    """The identity behind the row/column-sum form of the intra-chunk decay gradient (csrc/tc_intra_sums.cuh):
+    da_f[j] = sum_{k<j} (colsum W_f[k] - rowsum W_f[k]),  da_b[j] = sum_{k>j} (colsum W_b[k] - rowsum W_b[k])."""
+    from oracle.bissd_manual_backward import manual_backward
+    g = torch.Generator().manual_seed(11)
+    b, L, H, P, G, N, Q = 2, 96, 4, 8, 2, 8, 32
+    mk = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    x, B, C, dout = mk(b, L, H, P), mk(b, L, G, N), mk(b, L, G, N), mk(b, L, H, P)
+    dt = torch.rand(b, L, H, generator=g, dtype=torch.float64) * 0.3
+    A = -torch.rand(H, generator=g, dtype=torch.float64) - 0.2
+    r = manual_backward(x, dt, A, B, C, Q, dout)
+    uf = r["Wf"].sum(-2) - r["Wf"].sum(-1)                               # column sums - row sums, (b,H,nc,Q)
+    ub = r["Wb"].sum(-2) - r["Wb"].sum(-1)
+    da_f = torch.cumsum(uf, -1) - uf                                      # exclusive prefix sum
+    da_b = torch.flip(torch.cumsum(torch.flip(ub, [-1]), -1), [-1]) - ub  # exclusive suffix sum
+    assert max_rel_err(da_f, r["da_f"]) < 1e-10
+    assert max_rel_err(da_b, r["da_b"]) < 1e-10
