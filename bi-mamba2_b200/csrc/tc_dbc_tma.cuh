@@ -205,17 +205,10 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
     const uint32_t ncols = tmem_cols(2 * P);
     if (warp == 0) tmem_alloc(&tmem_slot, ncols);
-    if (tid == 32) {
+    if (tid == 0) {                                             // barriers and loads by the same thread, before the sync
         mbar_init(&bar_in, 1);
         mbar_init(&bar_done, 1);
         fence_mbar_init();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_slot;
-    bool ok = true;
-    if (tid == 0) {
         const int tile = (b * d.nc + c) * d.H + h;
         mbar_expect_tx(&bar_in, (uint32_t)(nsl * 16384 + 2 * nsl * P * 128));
         for (int j = 0; j < nsl; ++j) {
@@ -223,6 +216,24 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
             tma_load2(smSf + j * P * 128, &tmSf, j * 64, tile * P, &bar_in);
             tma_load2(smSb + j * P * 128, &tmSb, j * 64, tile * P, &bar_in);
         }
+    }
+    // this thread's g row piece and row factors are requested while the tiles are in flight
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane, l = l0 + r;
+    uint4 gq[4];
+    float ecf = 0.f, ecb = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) gq[j] = (l < lim && half * 32 < P) ? ld8v<T>(g, b, c * Q + l, h, half * 32 + j * 8) : zero8();
+    if (l < lim) {
+        ecf = cs_f[base + l];
+        ecb = cs_b[base + l];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool ok = true;
+    if (tid == 0) {
         ok = mbar_wait(&bar_in, 0);
         if (ok) {
             tc_fence_after();
@@ -237,8 +248,6 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
             umma_commit(&bar_done);
         }
     }
-    const int quad = warp & 3, half = warp >> 2;
-    const int r = quad * 32 + lane, l = l0 + r;
     if (ok) ok = mbar_wait(&bar_done, 0);
     ok = __syncthreads_and(ok);
     tc_fence_after();
@@ -254,7 +263,7 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     float gv[8];
-                    unpack8<T>(ld8v<T>(g, b, c * Q + l, h, c0 + j), gv);
+                    unpack8<T>(c0 == half * 32 ? gq[j >> 3] : ld8v<T>(g, b, c * Q + l, h, c0 + j), gv);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         sf_ = fmaf(af[j + i], gv[i], sf_);
@@ -271,7 +280,7 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     tc_fence_before();
     __syncthreads();
     if (ok && half == 0 && l < Q) {
-        const float ef = (l < lim) ? __expf(cs_f[base + l]) : 0.f, eb = (l < lim) ? __expf(cs_b[base + l]) : 0.f;
+        const float ef = (l < lim) ? __expf(ecf) : 0.f, eb = (l < lim) ? __expf(ecb) : 0.f;
         pf[base + l] = ef * (sf_ + (P > 32 ? rowred[0][r] : 0.f));
         pb[base + l] = eb * (sb_ + (P > 32 ? rowred[1][r] : 0.f));
     }
