@@ -95,10 +95,12 @@ def kernel_model(name, cfg):
         "dcb": (t * 2 * Q * Q * P, 2 * X + 3 * HQ + CB),
         "dx": (t * (4 * Q * P * N + 2 * Q * Q * P), 4 * X + BC + 2 * 2 * ST + CB + 5 * HQ),
     }
-    # tensor-core kernels are reported as tc_<phase>[_tma]; they do the same algorithmic work as the phase they replace
+    model["intra_sums"] = model["intra_decay_grad"]
+    # tensor-core kernels are reported as tc_<phase>[_tma|_ws]; they do the same algorithmic work as the phase they replace
     key = name[3:] if name.startswith("tc_") else name
-    if key.endswith("_tma"):
-        key = key[:-4]
+    for suffix in ("_tma", "_ws"):
+        if key.endswith(suffix):
+            key = key[:-len(suffix)]
     return model.get(key, model.get(key + "_kernel", (0, 0)))
 
 

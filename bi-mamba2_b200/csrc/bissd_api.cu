@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "norm_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_intra_sums.cuh"
 #include "tc_kernels.cuh"
@@ -666,6 +667,68 @@ static int check_device() {
 
 using namespace bissd;
 
+// ---- gated RMSNorm ---------------------------------------------------------------------------------------------
+static int norm_check(const bissd_norm_args *a, norm::NormDims *d, bool backward) {
+    if (!a || !a->x || !a->weight || !a->rstd) return BISSD_ERR_NULL;
+    if (!backward && !a->out) return BISSD_ERR_NULL;
+    if (backward && (!a->dout || !a->dx || !a->dweight || (a->z && !a->dz))) return BISSD_ERR_NULL;
+    if (a->rows <= 0 || a->hidden <= 0 || a->hidden % 256 != 0 || a->hidden > 4096) return BISSD_ERR_SHAPE;
+    const int group = a->group_size > 0 ? a->group_size : a->hidden;
+    if (group % 256 != 0 || a->hidden % group != 0) return BISSD_ERR_SHAPE;
+    if (a->x_dtype < BISSD_F32 || a->x_dtype > BISSD_F16) return BISSD_ERR_DTYPE;
+    if (a->w_dtype != BISSD_F32 && a->w_dtype != a->x_dtype) return BISSD_ERR_DTYPE;
+    auto al = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (!al(a->x) || !al(a->z) || !al(a->weight) || !al(a->out) || !al(a->dout) || !al(a->dx) || !al(a->dz))
+        return BISSD_ERR_ALIGN;
+    if (a->stride_x % 8 || a->stride_z % 8 || a->stride_out % 8) return BISSD_ERR_ALIGN;
+    d->rows = a->rows; d->hidden = a->hidden; d->group = group; d->ngroups = a->hidden / group;
+    d->sx = a->stride_x; d->sz = a->stride_z; d->so = a->stride_out;
+    d->has_z = a->z != nullptr; d->norm_before_gate = a->norm_before_gate; d->eps = a->eps;
+    return BISSD_OK;
+}
+static int norm_grid(const norm::NormDims &d) {
+    const long long want = (d.rows + norm::kWarps - 1) / norm::kWarps;
+    return (int)std::min<long long>(want, (long long)sm_count() * 8);
+}
+
+template <class T, class W>
+static int norm_forward_impl(const bissd_norm_args *a, const norm::NormDims &d, cudaStream_t s) {
+    const int grid = norm_grid(d);
+    if (d.hidden <= 2048) {
+        BISSD_LAUNCH("rmsnorm_gated_fwd", norm::rmsnorm_gated_fwd<T, W, 8><<<grid, norm::kThreads, 0, s>>>(
+            d, a->x, a->z, a->weight, a->out, a->rstd));
+    } else {
+        BISSD_LAUNCH("rmsnorm_gated_fwd", norm::rmsnorm_gated_fwd<T, W, 16><<<grid, norm::kThreads, 0, s>>>(
+            d, a->x, a->z, a->weight, a->out, a->rstd));
+    }
+    return BISSD_OK;
+}
+template <class T, class W>
+static int norm_backward_impl(const bissd_norm_args *a, const norm::NormDims &d, float *part, cudaStream_t s) {
+    const int grid = norm_grid(d);
+    const size_t smem = (size_t)d.hidden * sizeof(float);
+    if (d.hidden <= 2048) {
+        BISSD_LAUNCH("rmsnorm_gated_bwd", norm::rmsnorm_gated_bwd<T, W, 8><<<grid, norm::kThreads, smem, s>>>(
+            d, a->x, a->z, a->weight, a->dout, a->rstd, a->dx, a->dz, part));
+    } else {
+        BISSD_LAUNCH("rmsnorm_gated_bwd", norm::rmsnorm_gated_bwd<T, W, 16><<<grid, norm::kThreads, smem, s>>>(
+            d, a->x, a->z, a->weight, a->dout, a->rstd, a->dx, a->dz, part));
+    }
+    BISSD_LAUNCH("norm_bwd_reduce", norm::norm_bwd_reduce<W><<<(d.hidden + 255) / 256, norm::kThreads, 0, s>>>(
+        part, grid, d.hidden, a->dweight));
+    return BISSD_OK;
+}
+#define BISSD_NORM_DISPATCH(fn, ...)                                                                \
+    do {                                                                                            \
+        const bool wf = a->w_dtype == BISSD_F32;                                                    \
+        switch (a->x_dtype) {                                                                       \
+            case BISSD_F32: return fn<float, float>(__VA_ARGS__);                                   \
+            case BISSD_BF16: return wf ? fn<__nv_bfloat16, float>(__VA_ARGS__) : fn<__nv_bfloat16, __nv_bfloat16>(__VA_ARGS__); \
+            default: return wf ? fn<__half, float>(__VA_ARGS__) : fn<__half, __half>(__VA_ARGS__); \
+        }                                                                                           \
+    } while (0)
+
+
 extern "C" {
 
 int bissd_abi_version(void) { return BISSD_ABI_VERSION; }
@@ -774,6 +837,40 @@ int bissd_selftest_gemm(int dtype, int a_mn_major, int b_mn_major, int n, int k,
 #undef BISSD_SELFTEST_T
 #undef BISSD_SELFTEST
     return BISSD_OK;
+}
+
+int bissd_rmsnorm_gated_workspace_bytes(const bissd_norm_args *a, size_t *bwd_bytes) {
+    norm::NormDims d;
+    if (!bwd_bytes) return BISSD_ERR_NULL;
+    if (!a || a->rows <= 0 || a->hidden <= 0) return BISSD_ERR_SHAPE;
+    d.rows = a->rows;
+    *bwd_bytes = (size_t)norm_grid(d) * a->hidden * sizeof(float);
+    return BISSD_OK;
+}
+
+int bissd_rmsnorm_gated_forward(const bissd_norm_args *a, void *stream) {
+    norm::NormDims d;
+    int rc = norm_check(a, &d, false);
+    if (rc != BISSD_OK) return rc;
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    BISSD_NORM_DISPATCH(norm_forward_impl, a, d, s);
+}
+
+int bissd_rmsnorm_gated_backward(const bissd_norm_args *a, void *workspace, size_t workspace_bytes, void *stream) {
+    norm::NormDims d;
+    int rc = norm_check(a, &d, true);
+    if (rc != BISSD_OK) return rc;
+    if (!workspace) return BISSD_ERR_NULL;
+    size_t need = 0;
+    bissd_rmsnorm_gated_workspace_bytes(a, &need);
+    if (workspace_bytes < need) return BISSD_ERR_WORKSPACE;
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float *part = static_cast<float *>(workspace);
+    BISSD_NORM_DISPATCH(norm_backward_impl, a, d, part, s);
 }
 
 const char *bissd_kernel_path(const bissd_problem *p) {

@@ -46,9 +46,18 @@ class BwdArgs(C.Structure):
                 ("phases", C.c_int32)]
 
 
+class NormArgs(C.Structure):
+    _fields_ = [("rows", C.c_int64), ("hidden", C.c_int32), ("group_size", C.c_int32), ("x_dtype", C.c_int32),
+                ("w_dtype", C.c_int32), ("norm_before_gate", C.c_int32), ("eps", C.c_float),
+                ("stride_x", C.c_int64), ("stride_z", C.c_int64), ("stride_out", C.c_int64),
+                ("x", C.c_void_p), ("z", C.c_void_p), ("weight", C.c_void_p), ("out", C.c_void_p), ("rstd", C.c_void_p),
+                ("dout", C.c_void_p), ("dx", C.c_void_p), ("dz", C.c_void_p), ("dweight", C.c_void_p)]
+
+
 EXPORTS = ("bissd_abi_version", "bissd_strerror", "bissd_last_cuda_error", "bissd_workspace_bytes", "bissd_forward",
            "bissd_backward", "bissd_kernel_path", "bissd_launch_count", "bissd_trace_enable", "bissd_trace_read", "bissd_selftest_gemm", "bissd_read_status",
-           "bissd_forward_static_scratch")
+           "bissd_forward_static_scratch", "bissd_rmsnorm_gated_workspace_bytes", "bissd_rmsnorm_gated_forward",
+           "bissd_rmsnorm_gated_backward")
 
 STATIC_SCRATCH_BYTES = 16 << 20      # BISSD_STATIC_SCRATCH_BYTES
 ERR_TOO_LARGE = -9
@@ -89,6 +98,12 @@ def load():
                                      C.POINTER(C.c_int)]
     lib.bissd_forward_static_scratch.restype = C.c_int
     lib.bissd_forward_static_scratch.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+    lib.bissd_rmsnorm_gated_workspace_bytes.restype = C.c_int
+    lib.bissd_rmsnorm_gated_workspace_bytes.argtypes = [C.POINTER(NormArgs), C.POINTER(C.c_size_t)]
+    lib.bissd_rmsnorm_gated_forward.restype = C.c_int
+    lib.bissd_rmsnorm_gated_forward.argtypes = [C.POINTER(NormArgs), C.c_void_p]
+    lib.bissd_rmsnorm_gated_backward.restype = C.c_int
+    lib.bissd_rmsnorm_gated_backward.argtypes = [C.POINTER(NormArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.bissd_read_status.restype = C.c_int
     lib.bissd_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]
     lib.bissd_selftest_gemm.restype = C.c_int

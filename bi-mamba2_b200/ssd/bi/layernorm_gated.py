@@ -2,14 +2,102 @@
 
 Same class name, constructor and forward signature as the reference's `ssd.bi.layernorm_gated.RMSNorm`
 (src/ssd/bi/layernorm_gated.py:415-437); the arithmetic follows its `rms_norm_ref` (:18-41): statistics in fp32,
-result cast back to the input dtype.  This layer sits outside the scan operator and is expressed with PyTorch
-tensor ops (autograd provides its backward).
+result cast back to the input dtype.
+
+On a CUDA device the work is done by libbissd's `bissd_rmsnorm_gated_forward/_backward` (csrc/norm_kernels.cuh) when
+the shape is in the kernels' range (hidden a multiple of 256, at most 4096; groups multiples of 256; no bias) -
+`rmsnorm_fn`; everything else, and CPU tensors, go through the same formula written with PyTorch tensor ops
+(`rmsnorm_ref_fn`), which is also what the tests hold the kernels to.
 """
+import ctypes
+
 import torch
 import torch.nn.functional as F
 
+from ssd import _cabi
+
+_DT = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+
+
+def _kernel_ok(x, weight, bias, z, group_size):
+    hidden = x.shape[-1]
+    group = hidden if group_size is None else group_size
+    return (x.is_cuda and bias is None and x.dtype in _DT and weight.dtype in (torch.float32, x.dtype) and
+            hidden % 256 == 0 and hidden <= 4096 and group % 256 == 0 and hidden % group == 0 and
+            (z is None or (z.shape == x.shape and z.dtype == x.dtype)) and x.numel() > 0)
+
+
+def _rows(t, hidden):
+    t = t.reshape(-1, hidden)
+    if t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, out=None, dout=None, dx=None, dz=None, dw=None):
+    ptr = lambda t: None if t is None else t.data_ptr()
+    a = _cabi.NormArgs()
+    a.rows, a.hidden = x2.shape
+    a.group_size = 0 if group_size is None else int(group_size)
+    a.x_dtype, a.w_dtype = _DT[x2.dtype], _DT[weight.dtype]
+    a.norm_before_gate, a.eps = int(bool(norm_before_gate)), float(eps)
+    a.stride_x = x2.stride(0)
+    a.stride_z = z2.stride(0) if z2 is not None else 0
+    a.stride_out = (out if out is not None else dout).stride(0)
+    a.x, a.z, a.weight, a.out, a.rstd = ptr(x2), ptr(z2), ptr(weight), ptr(out), ptr(rstd)
+    a.dout, a.dx, a.dz, a.dweight = ptr(dout), ptr(dx), ptr(dz), ptr(dw)
+    return a
+
+
+class _RMSNormGatedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, z, eps, group_size, norm_before_gate):
+        lib = _cabi.load()
+        hidden = x.shape[-1]
+        x2 = _rows(x, hidden)
+        z2 = _rows(z, hidden) if z is not None else None
+        weight = weight.contiguous()
+        group = hidden if group_size is None else group_size
+        out = torch.empty((x2.shape[0], hidden), dtype=x.dtype, device=x.device)
+        rstd = torch.empty((x2.shape[0], hidden // group), dtype=torch.float32, device=x.device)
+        a = _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, out=out)
+        with torch.cuda.device(x.device):
+            _cabi.check(lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+        ctx.save_for_backward(x2, weight, z2, rstd)
+        ctx.cfg = (eps, group_size, norm_before_gate, x.shape)
+        return out.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _cabi.load()
+        x2, weight, z2, rstd = ctx.saved_tensors
+        eps, group_size, norm_before_gate, shape = ctx.cfg
+        hidden = x2.shape[1]
+        d2 = _rows(dout, hidden)
+        dx = torch.empty((x2.shape[0], hidden), dtype=x2.dtype, device=x2.device)
+        dz = torch.empty_like(dx) if z2 is not None else None
+        dw = torch.empty_like(weight)
+        # dx / dz are written with x's / z's row strides
+        xs = x2 if x2.stride(0) == hidden else x2.contiguous()
+        zs = z2 if z2 is None or z2.stride(0) == hidden else z2.contiguous()
+        a = _norm_args(xs, zs, weight, rstd, eps, group_size, norm_before_gate, dout=d2, dx=dx, dz=dz, dw=dw)
+        need = ctypes.c_size_t()
+        _cabi.check(lib.bissd_rmsnorm_gated_workspace_bytes(ctypes.byref(a), ctypes.byref(need)))
+        ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=x2.device)
+        with torch.cuda.device(x2.device):
+            _cabi.check(lib.bissd_rmsnorm_gated_backward(ctypes.byref(a), ws.data_ptr(), need.value,
+                                                         torch.cuda.current_stream().cuda_stream))
+        return dx.reshape(shape), dw, (dz.reshape(shape) if dz is not None else None), None, None, None
+
 
 def rmsnorm_fn(x, weight, bias=None, z=None, eps=1e-6, group_size=None, norm_before_gate=True):
+    """Same signature as the reference's rmsnorm_fn (src/ssd/bi/layernorm_gated.py:391-393)."""
+    if _kernel_ok(x, weight, bias, z, group_size):
+        return _RMSNormGatedFn.apply(x, weight, z, eps, group_size, norm_before_gate)
+    return rmsnorm_ref_fn(x, weight, bias, z=z, eps=eps, group_size=group_size, norm_before_gate=norm_before_gate)
+
+
+def rmsnorm_ref_fn(x, weight, bias=None, z=None, eps=1e-6, group_size=None, norm_before_gate=True):
     dtype = x.dtype
     xf = x.float()
     zf = z.float() if z is not None else None

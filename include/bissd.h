@@ -154,6 +154,34 @@ int bissd_forward_static_scratch(const bissd_fwd_args *args, void *stream);
 /* Backward pass. */
 int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- gated RMSNorm (the layer that follows the scan in BiMamba2) -------------------------------------------------
+ * Takes over rmsnorm_fn / _layer_norm_fwd / _layer_norm_bwd of src/ssd/bi/layernorm_gated.py:108-152, :271-340, used by
+ * ssd.modules.BiMamba2 at src/ssd/modules.py:114,184:
+ *     norm_before_gate:  out = x rstd w silu(z)        otherwise:  out = (x silu(z)) rstd w
+ *     rstd[row, group] = rsqrt(mean over the group of the normalised quantity squared + eps)
+ * x, z, out, dout, dx, dz: `rows` rows of `hidden` contiguous channels (row strides in elements, multiples of 8;
+ * 16-byte aligned pointers); weight, dweight: `hidden` values of dtype w_dtype (fp32 or x's dtype); rstd: fp32
+ * (rows, hidden / group_size).  hidden must be a multiple of 256 and at most 4096; group_size 0 (= hidden) or a
+ * multiple of 256 dividing hidden.  No bias (the reference's RMSNorm registers none).  z may be NULL (no gate). */
+typedef struct bissd_norm_args {
+    int64_t rows;
+    int32_t hidden, group_size;
+    int32_t x_dtype, w_dtype;            /* bissd_dtype */
+    int32_t norm_before_gate;
+    float eps;
+    int64_t stride_x, stride_z, stride_out;   /* x and dx; z and dz; out and dout */
+    const void *x, *z, *weight;
+    void *out;                           /* forward result */
+    float *rstd;                         /* written by the forward, read by the backward */
+    const void *dout;                    /* backward only, as are the next three */
+    void *dx, *dz, *dweight;
+} bissd_norm_args;
+
+/* Scratch the backward needs (per-CTA partial rows of the weight gradient). */
+int bissd_rmsnorm_gated_workspace_bytes(const bissd_norm_args *args, size_t *bwd_bytes);
+int bissd_rmsnorm_gated_forward(const bissd_norm_args *args, void *stream);
+int bissd_rmsnorm_gated_backward(const bissd_norm_args *args, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
 const char *bissd_kernel_path(const bissd_problem *p);
 

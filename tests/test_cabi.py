@@ -50,9 +50,10 @@ def test_struct_layout_matches_c_header():
 #include <stddef.h>
 #include "bissd.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(bissd_problem), sizeof(bissd_tensor), sizeof(bissd_fwd_args),
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(bissd_problem), sizeof(bissd_tensor), sizeof(bissd_fwd_args),
          sizeof(bissd_bwd_args), offsetof(bissd_fwd_args, dt_out), offsetof(bissd_fwd_args, phases),
-         offsetof(bissd_bwd_args, dx), offsetof(bissd_bwd_args, phases));
+         offsetof(bissd_bwd_args, dx), offsetof(bissd_bwd_args, phases), sizeof(bissd_norm_args),
+         offsetof(bissd_norm_args, stride_x), offsetof(bissd_norm_args, dweight));
   return 0; }
 '''
     with tempfile.TemporaryDirectory() as td:
@@ -62,7 +63,8 @@ int main(void) {
         got = [int(v) for v in subprocess.check_output([exe]).split()]
     want = [ctypes.sizeof(_cabi.Problem), ctypes.sizeof(_cabi.Tensor), ctypes.sizeof(_cabi.FwdArgs),
             ctypes.sizeof(_cabi.BwdArgs), _cabi.FwdArgs.dt_out.offset, _cabi.FwdArgs.phases.offset,
-            _cabi.BwdArgs.dx.offset, _cabi.BwdArgs.phases.offset]
+            _cabi.BwdArgs.dx.offset, _cabi.BwdArgs.phases.offset, ctypes.sizeof(_cabi.NormArgs),
+            _cabi.NormArgs.stride_x.offset, _cabi.NormArgs.dweight.offset]
     assert got == want
 
 
@@ -103,3 +105,19 @@ def test_operator_refuses_cpu_tensors(lib):
     with pytest.raises(RuntimeError, match="CUDA"):
         bimamba_chunk_scan_combined(x, torch.rand(1, 64, 2), -torch.ones(2), torch.randn(1, 64, 1, 8),
                                     torch.randn(1, 64, 1, 8), 32)
+
+
+def test_norm_entry_points_validate_before_any_launch(lib):
+    a = _cabi.NormArgs(rows=4, hidden=200, group_size=0, x_dtype=0, w_dtype=0, norm_before_gate=1, eps=1e-5,
+                       stride_x=200, stride_z=200, stride_out=200, x=256, weight=256, out=256, rstd=256)
+    assert lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), None) == -2          # hidden not a multiple of 256
+    a.hidden, a.stride_x, a.stride_out = 512, 512, 512
+    a.group_size = 384
+    assert lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), None) == -2          # group does not divide hidden
+    a.group_size, a.x = 0, None
+    assert lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), None) == -1
+    a.x, a.w_dtype = 256, 2
+    assert lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), None) == -3          # weight dtype neither fp32 nor x's
+    need = ctypes.c_size_t()
+    a.w_dtype = 0
+    assert lib.bissd_rmsnorm_gated_workspace_bytes(ctypes.byref(a), ctypes.byref(need)) == 0 and need.value >= 512 * 4
