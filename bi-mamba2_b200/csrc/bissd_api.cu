@@ -543,8 +543,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     BISSD_LAUNCH("tc_prev_terms_tma", tc::prev_terms_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_p, s>>>(
                         d, mC, mSf, mSb, gv, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
                     BISSD_ALLOW(tc::dbc_accum_tma<T>, smem_a);
+                    CUtensorMap mX128, mG128;
+                    if (!map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128) ||
+                        !map_bshd(&mG128, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128))
+                        return BISSD_ERR_ALIGN;
                     BISSD_LAUNCH("tc_dbc_accum_tma", tc::dbc_accum_tma<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_a, s>>>(
-                        d, mEf, mEb, mSf, mSb, x, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
+                        d, mEf, mEb, mSf, mSb, mX128, mG128, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
                     dbc_done = true;
                     nsplit = 1;                                      // nf/nb/pf/pb now hold complete row sums
                 }

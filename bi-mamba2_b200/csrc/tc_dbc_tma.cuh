@@ -3,12 +3,13 @@
 //
 //   dB_states[l,n] = sum_{h,dir} (x_h[l,:] Delta_h[l] e^{T-cs_dir[l]}) . E_{h,dir}[:,n]
 //   dC_states[l,n] = sum_{h,dir} (g_h[l,:] e^{cs_dir[l]})              . S_{h,dir}[:,n]
-// The row-scaled left operand is written by the threads (it has to pass through registers anyway), the right operand
-// ([headdim x dstate], dstate contiguous -> MN-major) comes by TMA into a three-deep ring, and all 2*R products land in
-// one TMEM accumulator that is read once.  The per-head row sums the reference takes from these products come from
+// Both operands come by TMA into a three-deep ring - the left one ([128 rows x headdim], K-major) is row-scaled in
+// place by the threads, the right one ([headdim x dstate], dstate contiguous -> MN-major) is used as it lands - and
+// all 2*R products go into one TMEM accumulator that is read once.  The per-head row sums the reference takes from these products come from
 // elsewhere: nf / nb from the dx kernel's per-direction accumulators, pf / pb from prev_terms_tma below.
 #pragma once
 #include "tc_scan_tma.cuh"
+#include "tc_state_tma.cuh"
 
 namespace bissd {
 namespace tc {
@@ -22,13 +23,17 @@ inline size_t dbc_tma_smem(int P, int nt) {
     return 1024 + 3 * ((size_t)(P / 64) * 16384 + (size_t)(nt / 64) * P * 128) + 2 * 2 * 128 * 4;
 }
 
-// grid (b*nc*G*nsplit, Q/128, 2); blockIdx.z: 0 = dB (src = x, right operand = E16), 1 = dC (src = g, right = states).
-// part layout [b, nc*Q, G, N] fp32.
+// grid (b*nc*G*nsplit, Q/128, 2); blockIdx.z: 0 = dB (left = x, right operand = E16), 1 = dC (left = g, right = states).
+// part layout [b, nc*Q, G, N] fp32.  tmL: x or g, box [64 x 128 rows].
+// Both operands of every (head, direction) stage arrive by TMA into a three-deep ring; the threads only scale the
+// 128 rows of the left tile in place (packed multiply for bf16) before thread 0 issues the stage's MMAs.  The row
+// factors of head h+1 are loaded while head h is being worked on.
 template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_constant__ CUtensorMap tmEb,
-              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb, View x, View g,
-              const float *dt_out, const float *cs_f, const float *cs_b, float *dB_part, float *dC_part, int *status) {
+              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
+              const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG, const float *dt_out,
+              const float *cs_f, const float *cs_b, float *dB_part, float *dC_part, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ DbcShared sh;
     const int P = d.P, N = d.N, Q = d.Q, R = d.R;
@@ -44,111 +49,90 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
     const int which = blockIdx.z;
     const int lim = min(Q, d.L - c * Q);
     const int l0 = blockIdx.y * kTileM, n0 = split * 128;
-    const View &src = which ? g : x;
+    const int total = 2 * R;
     const uint32_t ncols = tmem_cols(nt);
+    auto load_stage = [&](int it) {                             // thread 0: both operands of stage it = (head, dir)
+        const int hr = it >> 1, dir = it & 1, slot = it % 3;
+        const int h = grp * R + hr;
+        const int tile = (b * d.nc + c) * d.H + h;
+        uint8_t *sa = base_sm + slot * slot_bytes, *sb = sa + a_bytes;
+        const CUtensorMap *m = which ? (dir ? &tmSb : &tmSf) : (dir ? &tmEb : &tmEf);
+        mbar_expect_tx(&sh.full[slot], (uint32_t)slot_bytes);
+        for (int j = 0; j < npb; ++j) tma_load4(sa + j * 16384, which ? &tmG : &tmX, j * 64, h, c * Q + l0, b, &sh.full[slot]);
+        for (int j = 0; j < nnb; ++j) tma_load2(sb + j * P * 128, m, n0 + j * 64, tile * P, &sh.full[slot]);
+    };
     if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
-    if (tid == 32) {
+    if (tid == 0) {                                             // barriers and the first loads by the same thread
         for (int i = 0; i < 3; ++i) {
             mbar_init(&sh.full[i], 1);
             mbar_init(&sh.free_bar[i], 1);
         }
         mbar_init(&sh.done_bar, 1);
         fence_mbar_init();
+        load_stage(0);
+        if (total > 1) load_stage(1);
+        if (total > 2) load_stage(2);
     }
-    auto build_scale = [&](int hr) {                            // one (dir, row) per thread
-        const int h = grp * R + hr, dir = tid >> 7, r = tid & 127, l = l0 + r;
+    // one (dir, row) per thread: the inputs of the row factor of head hr, then the factor itself
+    const int sdir = tid >> 7, srow = tid & 127, sl = l0 + srow;
+    float pcs = 0.f, pT = 0.f, pdt = 0.f;
+    auto fetch_scale = [&](int hr) {
+        const int h = grp * R + hr;
         const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
+        if (sl < lim) {
+            pcs = sdir ? cs_b[base + sl] : cs_f[base + sl];
+            if (!which) {
+                pT = sdir ? cs_b[base] : cs_f[base + Q - 1];
+                pdt = dt_out[base + sl];
+            }
+        }
+    };
+    auto write_scale = [&](int hr) {
         float v = 0.f;
-        if (l < lim) {
-            const float cs = dir ? cs_b[base + l] : cs_f[base + l];
-            if (which) v = __expf(cs);
-            else v = dt_out[base + l] * __expf((dir ? cs_b[base] : cs_f[base + Q - 1]) - cs);
-        }
-        sc[((hr & 1) * 2 + dir) * 128 + r] = v;
+        if (sl < lim) v = which ? __expf(pcs) : pdt * __expf(pT - pcs);
+        sc[((hr & 1) * 2 + sdir) * 128 + srow] = v;
     };
-    const int total = 2 * R;
-    auto load_b = [&](int it) {                                 // thread 0: right operand of stage it = (head, dir)
-        const int hr = it >> 1, dir = it & 1, slot = it % 3;
-        const int tile = (b * d.nc + c) * d.H + grp * R + hr;
-        uint8_t *sb = base_sm + slot * slot_bytes + a_bytes;
-        const CUtensorMap *m = which ? (dir ? &tmSb : &tmSf) : (dir ? &tmEb : &tmEf);
-        mbar_expect_tx(&sh.full[slot], (uint32_t)b_bytes);
-        for (int j = 0; j < nnb; ++j) tma_load2(sb + j * P * 128, m, n0 + j * 64, tile * P, &sh.full[slot]);
-    };
-    uint4 ra[8], raw[8];
-    auto load_raw = [&](int it) {                               // unscaled rows of the left operand of stage `it`
-        const int h = grp * R + (it >> 1);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < 4 * npb) {
-                const int q = tid + (i & 3) * kThreads, j = i >> 2;
-                const int l = l0 + (q >> 3), p = j * 64 + (q & 7) * 8;
-                raw[i] = (l < lim) ? ld8v<T>(src, b, c * Q + l, h, p) : zero8();
-            }
-        }
-    };
-    auto fetch = [&](int it) {                                  // scale what load_raw(it) brought in
-        const int hr = it >> 1, dir = it & 1;
-        const float *s = sc + ((hr & 1) * 2 + dir) * 128;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < 4 * npb) {
-                const int q = tid + (i & 3) * kThreads;
-                ra[i] = scale8<T>(raw[i], s[q >> 3]);
-            }
-        }
-    };
-    build_scale(0);
+    fetch_scale(0);
+    write_scale(0);
+    if (R > 1) fetch_scale(1);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     bool ok = true;
-    if (tid == 0) {
-        load_b(0);
-        if (total > 1) load_b(1);
-    }
-    load_raw(0);
-    fetch(0);
-    if (total > 1) load_raw(1);
 #pragma unroll 1
     for (int it = 0; it < total; ++it) {
-        const int slot = it % 3;
+        const int slot = it % 3, hr = it >> 1, dir = it & 1;
         uint8_t *sa = base_sm + slot * slot_bytes;
-        if (ok && it >= 3) ok = mbar_wait(&sh.free_bar[slot], ((it / 3) - 1) & 1);
-        if (ok) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i < 4 * npb) {
-                    const int q = tid + (i & 3) * kThreads, j = i >> 2;
-                    const int r = q >> 3, cc = q & 7;
-                    *reinterpret_cast<uint4 *>(sa + j * 16384 + r * 128 + ((cc ^ (r & 7)) << 4)) = ra[i];
-                }
+        ok = mbar_wait(&sh.full[slot], (it / 3) & 1);
+        if (ok) {                                               // scale row r of the left tile by its factor, in place
+            const float *sf_ = sc + ((hr & 1) * 2 + dir) * 128;
+            for (int q = tid; q < npb * 1024; q += kThreads) {
+                uint4 *ptr = reinterpret_cast<uint4 *>(sa) + q;
+                *ptr = scale8_packed<T>(*ptr, sf_[(q >> 3) & 127]);
             }
             fence_async_smem();
-            if ((it & 1) == 0 && (it >> 1) + 1 < R) build_scale((it >> 1) + 1);
-            if (it + 1 < total) fetch(it + 1);
-            if (it + 2 < total) load_raw(it + 2);
+            if (dir == 1 && hr + 1 < R) {                       // next head's factors; then the loads for the one after
+                write_scale(hr + 1);
+                if (hr + 2 < R) fetch_scale(hr + 2);
+            }
         }
         ok = __syncthreads_and(ok);
         if (!ok) break;
         if (tid == 0) {
-            ok = mbar_wait(&sh.full[slot], (it / 3) & 1);
-            if (ok) {
-                tc_fence_after();
-                const uint32_t idesc = instr_desc(AbFmt<T>::v, false, true, nt);
-                const uint8_t *sb = sa + a_bytes;
-                for (int j = 0; j < npb; ++j)
+            tc_fence_after();
+            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, true, nt);
+            const uint8_t *sb = sa + a_bytes;
+            for (int j = 0; j < npb; ++j)
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma(tmem, smem_desc(smem_u32(sa + j * 16384) + kk * 32, 16, 1024),
-                             smem_desc(smem_u32(sb) + (j * 64 + kk * 16) * 128, (uint32_t)P * 128, 1024), idesc,
-                             (it > 0 || j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&sh.free_bar[slot]);
-                if (it + 2 < total) {                           // refill the slot stage it-1 used, once its MMAs are done
-                    if (it >= 1) ok = mbar_wait(&sh.free_bar[(it + 2) % 3], ((it - 1) / 3) & 1);
-                    if (ok) load_b(it + 2);
-                }
+                for (int kk = 0; kk < 4; ++kk)
+                    umma(tmem, smem_desc(smem_u32(sa + j * 16384) + kk * 32, 16, 1024),
+                         smem_desc(smem_u32(sb) + (j * 64 + kk * 16) * 128, (uint32_t)P * 128, 1024), idesc,
+                         (it > 0 || j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&sh.free_bar[slot]);
+            if (it >= 1 && it + 2 < total) {                    // refill the slot stage it-1 used, once its MMAs are done
+                ok = mbar_wait(&sh.free_bar[(it + 2) % 3], ((it - 1) / 3) & 1);
+                if (ok) load_stage(it + 2);
             }
         }
     }
