@@ -3,8 +3,11 @@
 //
 // Per CTA: one (batch, chunk, group), a 128 x 128 tile of (l, s).  For every head the g and x tiles arrive by TMA into a
 // three-deep ring; G2_h = g_h x_h^T goes into one of two TMEM accumulators, so the MMA of head h+1 runs while the
-// threads weight head h with its decay factors (log2-domain tables, double buffered, built one head ahead) and add it
-// to the running sum they keep in registers.
+// threads weight head h with its decay factors and add it to the running sum they keep in registers.  The factors:
+// log2-domain tables per head (double buffered; their inputs are fetched two heads ahead, the tables written one head
+// ahead).  A 16-column strip that lies wholly on one side of the diagonal of all 32 rows of a warp uses the factorised
+// form  2^(f2[l] - tf[s]) = 2^(f2[l] - f2[ref]) * 2^(f2[ref] - tf[s])  with ref the strip's last column (first column
+// and the b tables on the other side): one ex2 per row and strip plus a per-column table entry, both exponents <= 0.
 #pragma once
 #include "tc_scan_tma.cuh"
 
@@ -16,10 +19,10 @@ struct DcbShared {
     uint32_t tmem_base;
 };
 
-inline size_t dcb_tma_smem(int P, int Q) { return 1024 + 3 * 2 * (size_t)(P / 64) * 16384 + 2 * 4 * (size_t)Q * 4; }
+inline size_t dcb_tma_smem(int P, int Q) { return 1024 + 3 * 2 * (size_t)(P / 64) * 16384 + 2 * 6 * (size_t)Q * 4; }
 
 template <class T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
         const float *cs_f, const float *cs_b, float *dCB, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -28,7 +31,7 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
     const int npb = P / 64;
     const int stage_bytes = 2 * npb * 16384;
     uint8_t *base_sm = smem_align1024(dyn);
-    float *tabs = reinterpret_cast<float *>(base_sm + 3 * stage_bytes);          // [2][4][Q]: f2, b2, tf, tb
+    float *tabs = reinterpret_cast<float *>(base_sm + 3 * stage_bytes);          // [2][6][Q]: f2, b2, tf, tb, colF, colB
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
     const int l0 = blockIdx.y * kTileM, s0 = blockIdx.z * 128;
@@ -42,17 +45,30 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
         mbar_init(&sh.mma_done[1], 1);
         fence_mbar_init();
     }
-    auto build_tables = [&](int hr) {
+    // table entry tid of head hr: inputs into registers (fetch_tab), table written later (write_tab)
+    float pcf = 0.f, pcb = 0.f, pdt = 1.f, pcfr = 0.f, pcbr = 0.f;
+    auto fetch_tab = [&](int hr) {
         const int h = g * R + hr;
         const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
-        float *t = tabs + (hr & 1) * 4 * Q;
-        for (int i = tid; i < Q; i += kThreads) {
-            const float cf = cs_f[base + i] * 1.4426950408889634f, cb_ = cs_b[base + i] * 1.4426950408889634f;
-            const float lg = __log2f(dt_out[base + i]);
-            t[i] = cf;
-            t[Q + i] = cb_;
-            t[2 * Q + i] = cf - lg;
-            t[3 * Q + i] = cb_ - lg;
+        if (tid < Q) {
+            pcf = cs_f[base + tid];
+            pcb = cs_b[base + tid];
+            pdt = dt_out[base + tid];
+            pcfr = cs_f[base + (tid | 15)];                     // reference columns of the factorised form
+            pcbr = cs_b[base + (tid & ~15)];
+        }
+    };
+    auto write_tab = [&](int hr) {
+        float *t = tabs + (hr & 1) * 6 * Q;
+        if (tid < Q) {
+            const float cf = pcf * 1.4426950408889634f, cb_ = pcb * 1.4426950408889634f;
+            const float lg = __log2f(pdt);
+            t[tid] = cf;
+            t[Q + tid] = cb_;
+            t[2 * Q + tid] = cf - lg;
+            t[3 * Q + tid] = cb_ - lg;
+            t[4 * Q + tid] = ex2_approx(pcfr * 1.4426950408889634f - (cf - lg));
+            t[5 * Q + tid] = ex2_approx(pcbr * 1.4426950408889634f - (cb_ - lg));
         }
     };
     auto load_head = [&](int hr) {                              // thread 0: both tiles of head hr into ring slot hr % 3
@@ -78,7 +94,9 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
         umma_commit(&sh.mma_done[hr & 1]);
         return true;
     };
-    build_tables(0);
+    fetch_tab(0);
+    write_tab(0);
+    if (R > 1) fetch_tab(1);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -95,31 +113,36 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
 #pragma unroll 1
     for (int hr = 0; hr < R; ++hr) {
         if (tid == 0 && ok && hr + 1 < R) ok = issue_head(hr + 1, tmem);
-        if (hr + 1 < R) build_tables(hr + 1);
+        if (hr + 1 < R) {
+            write_tab(hr + 1);
+            if (hr + 2 < R) fetch_tab(hr + 2);
+        }
         if (ok) ok = mbar_wait(&sh.mma_done[hr & 1], (hr >> 1) & 1);
         if (ok) {
             tc_fence_after();
-            const float *t = tabs + (hr & 1) * 4 * Q;
+            const float *t = tabs + (hr & 1) * 6 * Q;
             const float fl = t[min(l, Q - 1)], bl = t[Q + min(l, Q - 1)];
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                const int c0 = half * 32 + ch * 64;
+            for (int ch = 0; ch < 4; ++ch) {                    // four 16-column strips per thread
+                const int c0 = half * 32 + (ch >> 1) * 64 + (ch & 1) * 16;
                 const int sb0 = s0 + c0;
-                float v[32];
-                tmem_ld32(tl + (hr & 1) * 128 + c0, v);
-                if (sb0 + 31 < wl_min) {                        // whole strip left of the diagonal for every row here
+                float v[16];
+                tmem_ld16(tl + (hr & 1) * 128 + c0, v);
+                if (sb0 + 15 < wl_min) {                        // whole strip left of the diagonal for every row here
+                    const float rf = ex2_approx(fl - t[sb0 + 15]);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(v[j], ex2_approx(fl - t[2 * Q + sb0 + j]), acc[ch * 32 + j]);
+                    for (int j = 0; j < 16; ++j) acc[ch * 16 + j] = fmaf(v[j] * t[4 * Q + sb0 + j], rf, acc[ch * 16 + j]);
                 } else if (sb0 > wl_max) {                      // whole strip right of it
+                    const float rb = ex2_approx(bl - t[Q + sb0]);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(v[j], ex2_approx(bl - t[3 * Q + sb0 + j]), acc[ch * 32 + j]);
+                    for (int j = 0; j < 16; ++j) acc[ch * 16 + j] = fmaf(v[j] * t[5 * Q + sb0 + j], rb, acc[ch * 16 + j]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         const int s = sb0 + j;
                         float a = (s <= l) ? fl - t[2 * Q + s] : bl - t[3 * Q + s];
                         if (s == l) a += 1.f;                   // the diagonal counts once per direction
-                        acc[ch * 32 + j] = fmaf(v[j], ex2_approx(a), acc[ch * 32 + j]);
+                        acc[ch * 16 + j] = fmaf(v[j], ex2_approx(a), acc[ch * 16 + j]);
                     }
                 }
             }
@@ -133,12 +156,12 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
     if (ok && l < Q) {
         float *out = dCB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0;
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-            const int c0 = half * 32 + ch * 64;
+        for (int ch = 0; ch < 4; ++ch) {
+            const int c0 = half * 32 + (ch >> 1) * 64 + (ch & 1) * 16;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
+            for (int j = 0; j < 16; j += 4)
                 *reinterpret_cast<float4 *>(out + c0 + j) =
-                    make_float4(acc[ch * 32 + j], acc[ch * 32 + j + 1], acc[ch * 32 + j + 2], acc[ch * 32 + j + 3]);
+                    make_float4(acc[ch * 16 + j], acc[ch * 16 + j + 1], acc[ch * 16 + j + 2], acc[ch * 16 + j + 3]);
         }
     }
     tc_fence_before();
