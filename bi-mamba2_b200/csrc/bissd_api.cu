@@ -95,7 +95,7 @@ struct FwdWs {
     size_t loc, cb, cb16, total;
 };
 struct BwdWs {
-    size_t cb, cbt, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    size_t cb, cbt, cbt16, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
     int nblk, nlt, nsplit;
 };
 
@@ -125,6 +125,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.E16 = take(2 * st * 2);                                        // passed state gradients in the input dtype
     w.g = take((size_t)d.b * d.L * d.H * d.P * 2);                   // gated output gradient dout * silu(z)
     w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
+    w.cbt16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);        // CB transposed, rounded to bf16 (TMA-fed dx)
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
     w.ddt_out = take(hq * 4);
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
@@ -446,9 +447,9 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
             const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
-            __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt);      // shares the fp32 copy's region
+            __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt16);
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
-                d, Cm, Bm, F(w.cb), ws_path ? nullptr : F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, status));
+                d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, status));
             bool dx_done = false;
             if (ws_path) {
                 CUtensorMap mB, mCBt, mEf, mEb, mG;
@@ -489,9 +490,6 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
 #undef BISSD_DX_WS
                     dx_done = true;
                     dd_slots = nlt_tc * 4;
-                } else {                                         // maps refused: produce the fp32 transposed tile after all
-                    BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
-                        d, Cm, Bm, nullptr, F(w.cbt), nullptr, nullptr, status));
                 }
             }
             if (!dx_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
@@ -603,7 +601,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     const size_t smem_s = tc::intra_sums_smem(d.Q);
                     BISSD_ALLOW(tc::intra_sums<T>, smem_s);
                     BISSD_LAUNCH("tc_intra_sums", tc::intra_sums<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_s, s>>>(
-                        dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
+                        dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cbt), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
                     intra_done = true;
                     use_u4 = true;
                 }
