@@ -271,11 +271,16 @@ def run_ours(args):
     value = tokens_per_step * args.steps / (ms * 1e-3)
 
     # ---- per-kernel device time (CUDA events on the launching stream, recorded by the library around each launch)
+    # The device status word is read after every pass of these steps: a bounded device-side wait that ran out would
+    # make the numbers above meaningless, so it has to end the run rather than pass unnoticed.
+    from ssd.bi import ssd_combined as _op_mod
     _cabi.trace_enable(True)
+    _op_mod.CHECK_STATUS = True
     tsteps = min(args.steps, 10)
     for _ in range(tsteps):
         step()
     torch.cuda.synchronize()
+    _op_mod.CHECK_STATUS = False
     trace = _cabi.trace_read()
     _cabi.trace_enable(False)
     peaks = load_peaks()

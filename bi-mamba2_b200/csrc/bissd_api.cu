@@ -95,7 +95,7 @@ struct FwdWs {
     size_t loc, cb, cb16, total;
 };
 struct BwdWs {
-    size_t cb, cbt, cbt16, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    size_t cb, cbt, cbt16, cbs, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
     int nblk, nlt, nsplit;
 };
 
@@ -125,6 +125,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.E16 = take(2 * st * 2);                                        // passed state gradients in the input dtype
     w.g = take((size_t)d.b * d.L * d.H * d.P * 2);                   // gated output gradient dout * silu(z)
     w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
+    w.cbs = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB in strips of 16 columns (tc::intra_sums)
     w.cbt16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);        // CB transposed, rounded to bf16 (TMA-fed dx)
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
     w.ddt_out = take(hq * 4);
@@ -279,7 +280,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                 const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
                 __nv_bfloat16 *CB16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cb16);
                 BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
-                    d, Cm, Bm, ws_path ? nullptr : CB, nullptr, ws_path ? CB16 : nullptr, nullptr, status));
+                    d, Cm, Bm, ws_path ? nullptr : CB, nullptr, ws_path ? CB16 : nullptr, nullptr, nullptr, status));
                 bool tma_done = false;
                 if (ws_path) {
                     CUtensorMap mC, mCB, mSf, mSb, mX;
@@ -320,7 +321,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                         tma_done = true;
                     } else {                                     // maps refused: produce the fp32 tile after all
                         BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
-                            d, Cm, Bm, CB, nullptr, nullptr, nullptr, status));
+                            d, Cm, Bm, CB, nullptr, nullptr, nullptr, nullptr, status));
                     }
                 }
                 if (!tma_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
@@ -447,9 +448,10 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const size_t smem_cb = tc::smem_bytes(ntQ, 0), smem_dx = tc::smem_bytes(ntP, 3 * d.Q), smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
             const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
+            const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
             __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt16);
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
-                d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, status));
+                d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, sums_path ? F(w.cbs) : nullptr, status));
             bool dx_done = false;
             if (ws_path) {
                 CUtensorMap mB, mCBt, mEf, mEb, mG;
@@ -594,14 +596,15 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
             }
             bool intra_done = false;
-            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q) && !no_sums()) {
+            const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
+            if (sums_path) {
                 CUtensorMap mG, mX;
                 if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
                     map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
                     const size_t smem_s = tc::intra_sums_smem(d.Q);
                     BISSD_ALLOW(tc::intra_sums<T>, smem_s);
                     BISSD_LAUNCH("tc_intra_sums", tc::intra_sums<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_s, s>>>(
-                        dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cbt), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
+                        dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cbs), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
                     intra_done = true;
                     use_u4 = true;
                 }
@@ -646,7 +649,8 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         BISSD_LAUNCH("bmm_bwd", simt::bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, simt::TILE)), simt::TB, 0, s>>>(
             d, Bm, Cm, F(w.dCB), F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC));
     }
-    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
+    // four heads (warps) per CTA: twice the CTAs of an eight-warp launch, which balances better over the SMs
+    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 4)), 128, 4 * d.Q * sizeof(float), s>>>(
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
         F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), use_u4 ? nullptr : F(w.da_f), use_u4 ? nullptr : F(w.da_b),
         use_u4 ? F(w.u4) : nullptr, F(w.dTpart), pass_nblk, nsplit, a.ddt,

@@ -840,7 +840,7 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
 // The intra-chunk decay gradients come either as da_f / da_b (already dominance sums) or, when u4 is given, as the
 // per-index differences u_f / u_b = column sums - row sums (four arrays: row tile 0 f, b, row tile 1 f, b), which are
 // added to the terms that are prefix-summed (u_f) and suffix-summed (u_b) exclusively; da_f / da_b are then null.
-// dynamic smem: 8 * Q floats.
+// dynamic smem: (warps per CTA) * Q floats.
 __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
                                                  long long dsh, const float *A, const float *dt_bias,
                                                  const float *dt_out, const float *ddt_out, const float *nf,
@@ -850,7 +850,7 @@ __global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
-    const int h = blockIdx.y * 8 + warp;
+    const int h = blockIdx.y * (blockDim.x >> 5) + warp;         // one warp per head; any number of warps per CTA
     if (h >= d.H) return;
     float *acc = sm + warp * d.Q;
     const int lim = min(d.Q, d.L - c * d.Q);

@@ -28,7 +28,7 @@ inline size_t intra_sums_smem(int Q) { return smem_bytes(Q, 6 * Q); }
 template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
-           const float *cs_f, const float *cs_b, const float *CBt, float *u4, long long hq, int *status) {
+           const float *cs_f, const float *cs_b, const float *CBs, float *u4, long long hq, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
     __shared__ float rsum[2][2][kTileM];                          // [column half][direction][row]
@@ -110,16 +110,18 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
                                        (((jc & 7) ^ (kl & 7)) << 4)) = v;
         };
         const bool row_on = l < lim;
-        // C.B^T is read from its transposed copy: for one column s the 32 rows of a warp are 128 contiguous bytes (one
-        // request per column and warp), whereas 32 row pieces of the untransposed matrix are 32 separate lines
-        const float *cbcol = CBt + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + min(l, Q - 1);
+        // C.B^T is read from its copy in strips of 16 columns ([Q/16][Q][16]): this thread's 16 values of a strip are 64
+        // contiguous bytes and the 32 rows of a warp 2 KB, whereas 32 row pieces of the row-major matrix are 32
+        // separate lines
+        const float *cbstrip = CBs + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + min(l, Q - 1) * 16;
         const float fl = sf[min(l, Q - 1)], bl = sb[min(l, Q - 1)];
         float rf = 0.f, rb = 0.f;
         const int cbeg = colhalf * (Q / 2), cend = cbeg + Q / 2;
-        float cbn[16];
+        float4 cbn[4];
         auto load_cb = [&](int c0) {
+            const float4 *src = reinterpret_cast<const float4 *>(cbstrip + (long long)(c0 >> 4) * Q * 16);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) cbn[j] = row_on ? __ldg(cbcol + (long long)(c0 + j) * Q) : 0.f;
+            for (int q = 0; q < 4; ++q) cbn[q] = row_on ? __ldg(src + q) : make_float4(0.f, 0.f, 0.f, 0.f);
         };
         // the accumulator columns and the CB values of strip k+1 are requested before strip k is worked on
         uint32_t rn[16];
@@ -132,7 +134,9 @@ intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(rn[j]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) cbv[j] = cbn[j];
+            for (int q = 0; q < 4; ++q) {
+                cbv[4 * q] = cbn[q].x; cbv[4 * q + 1] = cbn[q].y; cbv[4 * q + 2] = cbn[q].z; cbv[4 * q + 3] = cbn[q].w;
+            }
             if (c0 + 16 < cend) {
                 tmem_ld16_nowait(tmem_lane_base(p.tmem) + c0 + 16, rn);
                 load_cb(c0 + 16);

@@ -63,10 +63,11 @@ template <class T> __device__ __forceinline__ uint4 pack8f(const float *p) {
 // ---------------------------------------------------------------------------------------------------------
 // CB[b,c,g,l,s] = C[l].B[s].   grid (b*nc*G, ceil(Q/128)); n_tile = round16(Q); tables: none.
 // Outputs, each optional: CB (fp32), CBt (fp32, transposed), CB16 / CBt16 (the same two rounded to bf16, for the
-// kernels that take the tile by TMA and only use it as a factor of a 16-bit MMA operand).
+// kernels that take the tile by TMA and only use it as a factor of a 16-bit MMA operand), CBs (fp32 in strips of 16
+// columns, [Q/16][Q rows][16]: a thread that owns a row reads 64 contiguous bytes per strip, a warp 2 KB).
 template <class T>
 __global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, float *CB, float *CBt, __nv_bfloat16 *CB16,
-                                                   __nv_bfloat16 *CBt16, int *status) {
+                                                   __nv_bfloat16 *CBt16, float *CBs, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
     const int nt = round_up(d.Q, 16);
@@ -102,6 +103,13 @@ __global__ void __launch_bounds__(kThreads) bmm_cb(Dims d, View Cm, View Bm, flo
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < d.Q) ot[(long long)(c0 + j) * d.Q] = v[j];
+                }
+                if (CBs) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (c0 + j < d.Q)
+                            *reinterpret_cast<float4 *>(CBs + tile + (long long)((c0 + j) >> 4) * d.Q * 16 + l * 16 + ((c0 + j) & 15)) =
+                                make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
                 if (CB16) {
                     __nv_bfloat16 *out = CB16 + tile + (long long)l * d.Q;

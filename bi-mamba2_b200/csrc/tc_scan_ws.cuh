@@ -43,7 +43,11 @@ constexpr int kWsMStages = 3;
 
 struct WsShared {
     uint64_t grp_full, grp_done, st_full, st_done, tab_bar, fin_bar;
-    uint64_t red_bar[4];                                        // MODE 1: row sums of the upper column half are in place
+    // MODE 1: row sums of the upper column half are in place; one barrier per (row quarter, rowred slot).  The upper
+    // half can run two tiles ahead of its partner, so a single barrier per quarter could be two phases ahead of a
+    // waiter - which a parity wait cannot tell from "not yet" (and at the end of the tile list nothing would follow
+    // to release it).  With one barrier per slot it is at most zero phases ahead.
+    uint64_t red_bar[4][3];
     uint64_t x_full[4], x_free[4];
     uint64_t m_full[kWsMStages], m_free[kWsMStages];
     uint64_t acc_full[2], acc_free[2];
@@ -63,20 +67,22 @@ inline bool scan_ws_ok(int P, int N, int Q) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// bounded wait that also gives up when another role has already failed
-__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile int *fail) {
+// Bounded wait that also gives up when another role has already failed.  `id` names the wait (role * 10 + barrier);
+// the first wait that runs out leaves its id in the CTA-wide flag, from where it reaches the status word.
+__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile int *fail, int id) {
     if (mbar_test(bar, parity)) return true;
     for (uint32_t i = 0; i < kWaitAttempts; ++i) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 7) == 7 && *fail) return false;
     }
-    *fail = 1;
+    if (!*fail) *fail = id;
     return false;
 }
 // the same for a whole warp: every lane polls, the outcome is made uniform so that .aligned instructions stay legal
-__device__ __forceinline__ bool ws_wait_warp(uint64_t *bar, uint32_t parity, volatile int *fail) {
-    return __all_sync(0xffffffffu, ws_wait(bar, parity, fail));
+__device__ __forceinline__ bool ws_wait_warp(uint64_t *bar, uint32_t parity, volatile int *fail, int id) {
+    return __all_sync(0xffffffffu, ws_wait(bar, parity, fail, id));
 }
+constexpr int kErrWsWait = 0x1000;                              // status word = kErrWsWait + id of the wait that ran out
 
 // Walks (batch, chunk, row tile, head) tiles in the order head fastest; grp numbers the (batch, chunk, row tile,
 // group) sets whose tiles share C and C.B^T.
@@ -183,7 +189,7 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
     for (int s = 0; s < ns; ++s) {
         const int s0 = s * 64, sc = s0 + cc * 8;
         if (ring.used >= kWsMStages &&
-            !ws_wait_warp(&m_free[ring.mb], ((ring.par >> ring.mb) & 1) ^ 1, fail))
+            !ws_wait_warp(&m_free[ring.mb], ((ring.par >> ring.mb) & 1) ^ 1, fail, 33))
             return false;
         const uint8_t *slab = smCB + s * 16384;
         uint8_t *stage = smM + ring.mb * kAStageBytes;
@@ -316,7 +322,7 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
         }
         const float Dh = (d.has_D && !d.D_hdim) ? a.D[it.h] : 0.f;
         T *pdx = static_cast<T *>(a.out.ptr) + it.b * a.out.sb + (long long)(it.c * Q + l) * a.out.sl + it.h * a.out.sh + ch;
-        if (!ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail)) break;
+        if (!ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail, 21)) break;
         tc_fence_after();
         const float wf = live ? __expf(e1) : 0.f, wb = live ? __expf(e2) : 0.f;
         const uint32_t acc = tl + buf * 3 * P + ch;
@@ -369,9 +375,9 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
             rowred[slot][1][r] = rsf;
             rowred[slot][2][r] = rsb;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.red_bar[quarter]);
+            if (lane == 0) mbar_arrive(&sh.red_bar[quarter][slot]);
         } else {
-            if (!ws_wait_warp(&sh.red_bar[quarter], i & 1, fail)) break;
+            if (!ws_wait_warp(&sh.red_bar[quarter][slot], (i / 3) & 1, fail, 22)) break;
             rs += rowred[slot][0][r];
             rsf += rowred[slot][1][r];
             rsb += rowred[slot][2][r];
@@ -422,7 +428,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
         mbar_init(&sh.tab_bar, kWsBuilderWarps);
         mbar_init(&sh.fin_bar, 1);
         for (int i = 0; i < 4; ++i) {
-            mbar_init(&sh.red_bar[i], 1);
+            for (int k = 0; k < 3; ++k) mbar_init(&sh.red_bar[i][k], 1);
             mbar_init(&sh.x_full[i], 1);
             mbar_init(&sh.x_free[i], 1);
         }
@@ -458,12 +464,12 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 const int buf = i & 1;
                 const uint32_t acc = tmem + buf * 3 * P;
                 if (it.grp != cur_grp) {
-                    ok = ws_wait(&sh.grp_full, ngrp & 1, fail);
+                    ok = ws_wait(&sh.grp_full, ngrp & 1, fail, 1);
                     ++ngrp;
                     cur_grp = it.grp;
                 }
-                if (ok && i >= 2) ok = ws_wait(&sh.acc_free[buf], ((i >> 1) - 1) & 1, fail);
-                ok = ok && ws_wait(&sh.st_full, i & 1, fail);
+                if (ok && i >= 2) ok = ws_wait(&sh.acc_free[buf], ((i >> 1) - 1) & 1, fail, 2);
+                ok = ok && ws_wait(&sh.st_full, i & 1, fail, 3);
                 if (!ok) break;
                 tc_fence_after();
                 // both directions in one N = 2P product: B rows 0..P-1 are S_f, rows P..2P-1 are S_b
@@ -476,7 +482,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 umma_commit(&sh.st_done);
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
-                    ok = ok && ws_wait(&sh.m_full[mb], (m_par >> mb) & 1, fail) && ws_wait(&sh.x_full[s], i & 1, fail);
+                    ok = ok && ws_wait(&sh.m_full[mb], (m_par >> mb) & 1, fail, 4) && ws_wait(&sh.x_full[s], i & 1, fail, 5);
                     if (ok) {
                         tc_fence_after();
 #pragma unroll
@@ -495,7 +501,6 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 if (i + 1 < nt && it.grp != cur_grp) umma_commit(&sh.grp_done);   // C and C.B^T may be replaced
             }
             if (!ok) {
-                atomicExch(status, kErrMmaTimeout);
                 umma_commit(&sh.fin_bar);                       // leave no MMA in flight
                 mbar_wait(&sh.fin_bar, 0);
             }
@@ -510,7 +515,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             int ngrp = 0, loads_st = 0, loads_x[4] = {0, 0, 0, 0};
             for (int j = 0; j < nt && ok; ++j) {
                 if (it.grp != cur_grp) {
-                    if (ngrp > 0) ok = ws_wait(&sh.grp_done, (ngrp - 1) & 1, fail);
+                    if (ngrp > 0) ok = ws_wait(&sh.grp_done, (ngrp - 1) & 1, fail, 11);
                     if (!ok) break;
                     mbar_expect_tx(&sh.grp_full, (uint32_t)((NSL + NS) * 16384));
 #pragma unroll
@@ -522,7 +527,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                     cur_grp = it.grp;
                     ++ngrp;
                 }
-                if (j > 0) ok = ws_wait(&sh.st_done, (j - 1) & 1, fail);
+                if (j > 0) ok = ws_wait(&sh.st_done, (j - 1) & 1, fail, 12);
                 if (!ok) break;
                 const int tile = (it.b * d.nc + it.c) * d.H + it.h;
                 mbar_expect_tx(&sh.st_full, (uint32_t)(2 * NSL * P * 128));
@@ -534,7 +539,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 ++loads_st;
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
-                    if (j > 0) ok = ok && ws_wait(&sh.x_free[s], (j - 1) & 1, fail);
+                    if (j > 0) ok = ok && ws_wait(&sh.x_free[s], (j - 1) & 1, fail, 13);
                     if (ok) {
                         mbar_expect_tx(&sh.x_full[s], 8192u);
                         tma_load4(smX + s * 8192, &tmX, 0, it.h, it.c * Q + s * 64, it.b, &sh.x_full[s]);
@@ -544,7 +549,6 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 it.next(d, nrt);
             }
             if (!ok) {                                          // leave no load in flight
-                atomicExch(status, kErrMmaTimeout);
                 if (loads_st) mbar_wait(&sh.st_full, (loads_st - 1) & 1);
                 for (int s = 0; s < NS; ++s)
                     if (loads_x[s]) mbar_wait(&sh.x_full[s], (loads_x[s] - 1) & 1);
@@ -592,7 +596,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             const int hh = it.h, bb = it.b, row = it.c * Q + l;
             T *po = static_cast<T *>(out.ptr) + bb * out.sb + (long long)row * out.sl + hh * out.sh + ch;
             T *px = static_cast<T *>(out_x.ptr) + bb * out_x.sb + (long long)row * out_x.sl + hh * out_x.sh + ch;
-            ok = ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail);
+            ok = ws_wait_warp(&sh.acc_full[buf], (i >> 1) & 1, fail, 21);
             if (!ok) break;
             tc_fence_after();
             const float ef = live ? __expf(ecf) : 0.f, eb = live ? __expf(ecb) : 0.f;
@@ -690,7 +694,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             write_tab(0);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.tab_bar);
-            ok = ws_wait_warp(&sh.tab_bar, 0, fail);
+            ok = ws_wait_warp(&sh.tab_bar, 0, fail, 31);
         }
         for (int i = 0; i < nt && ok; ++i) {
             const float dfold = pD;
@@ -699,7 +703,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             it.next(d, nrt);
             if (i + 1 < nt) fetch_tab(it);
             if (grp != cur_grp) {
-                ok = ws_wait_warp(&sh.grp_full, ngrp & 1, fail);
+                ok = ws_wait_warp(&sh.grp_full, ngrp & 1, fail, 32);
                 ++ngrp;
                 cur_grp = grp;
                 if (!ok) break;
@@ -711,13 +715,13 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 write_tab((i + 1) & 1);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh.tab_bar);
-                ok = ws_wait_warp(&sh.tab_bar, (i + 1) & 1, fail);
+                ok = ws_wait_warp(&sh.tab_bar, (i + 1) & 1, fail, 31);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (sh.fail && tid == 0) atomicExch(status, kErrMmaTimeout);
+    if (sh.fail && tid == 0) atomicExch(status, kErrWsWait + sh.fail);
     if (warp == 0) {
         __syncwarp();
         tmem_dealloc(tmem, ncols);

@@ -297,3 +297,16 @@ def test_config2_full_size_batch_independence_and_determinism():
     part = run_gpu(part_inp, 256, True)
     for k in ("out", "dx", "ddt", "dB", "dC", "dz"):
         assert torch.equal(part[k], full[k][:2]), k
+
+
+def test_config2_many_passes_leave_the_status_word_clean():
+    """Stress for the persistent warp-specialised kernels: their roles run at timing-dependent offsets from one
+    another, so a protocol error between them (a barrier that can run two phases ahead of a waiter, say) shows only
+    once in a few hundred launches - as a bounded wait that runs out.  The status word is read after every pass
+    (BISSD_CHECK_STATUS=1 in conftest.py), which raises on the first such event; results must also stay bit-identical."""
+    inp = _config2()
+    first = run_gpu(inp, 256, True)
+    for _ in range(400):
+        cur = run_gpu(inp, 256, True)
+    for k in ("out", "dx", "ddt", "dA"):
+        assert torch.equal(first[k], cur[k]), k
