@@ -105,9 +105,9 @@ def kernel_model(name, cfg):
 
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the heaviest kernels at the benchmark
-# shape, from ncu captures on a batch-2 case scaled by 4 (traffic is proportional to batch: every CTA reads its own
-# tiles); see profiles/ncu_full_dx_tma_intra_decay_grad_chunk_scan_tma_b2.md.
-NCU_TRAFFIC_BYTES = {"tc_intra_decay_grad": 122.5e6, "tc_dx_tma": 180.1e6, "tc_chunk_scan_tma": 187.6e6}
+# shape, from ncu captures on a batch-2 case scaled by 4 (traffic is proportional to batch: every tile reads its own
+# operands); see profiles/ncu_full_ws_kernel_scan_dx_intra_sums_b2.md.
+NCU_TRAFFIC_BYTES = {"tc_intra_sums": 122.5e6, "tc_dx_ws": 170.8e6, "tc_chunk_scan_ws": 173.2e6}
 
 
 class ClockSampler:
