@@ -226,7 +226,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
     if (a.phases & BISSD_PHASE_LOCAL) {
         int rc = note_cuda(cudaMemsetAsync(ws, 0, kWsHeader, s), "cudaMemsetAsync");
         if (rc != BISSD_OK) return rc;
-        BISSD_LAUNCH("cumsum_fwd", simt::cumsum_fwd<<<dim3(d.b * d.nc, ceil_div(d.H, 8)), simt::TB, 8 * d.Q * sizeof(float), s>>>(
+        BISSD_LAUNCH("cumsum_fwd", simt::cumsum_fwd<<<d.b * d.nc * d.H, 256, 0, s>>>(
             d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
             a.cs_f, a.cs_b));
         if constexpr (TcKernels<T>::available) {
@@ -438,6 +438,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     if (!(a.phases & BISSD_PHASE_FINISH)) return BISSD_OK;
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
+    bool have_fp32_cb = true;                                    // fp32 CB (and its transpose) are in the workspace
     bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
@@ -451,7 +452,16 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
             __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt16);
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
-                d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, ws_path ? CBt16 : nullptr, sums_path ? F(w.cbs) : nullptr, status));
+                d, Cm, Bm, (sums_path && ws_path) ? nullptr : F(w.cb), ws_path ? nullptr : F(w.cbt), nullptr,
+                ws_path ? CBt16 : nullptr, sums_path ? F(w.cbs) : nullptr, status));   // only the copies that will be read
+            have_fp32_cb = !ws_path;                             // ws path: only the copies its kernels read were written
+            auto ensure_fp32_cb = [&]() -> int {                 // for the kernels that read them, should a planned path fall through
+                if (have_fp32_cb) return BISSD_OK;
+                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
+                    d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, nullptr, nullptr, status));
+                have_fp32_cb = true;
+                return BISSD_OK;
+            };
             bool dx_done = false;
             if (ws_path) {
                 CUtensorMap mB, mCBt, mEf, mEb, mG;
@@ -493,6 +503,10 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     dx_done = true;
                     dd_slots = nlt_tc * 4;
                 }
+            }
+            if (!dx_done) {
+                const int rc = ensure_fp32_cb();
+                if (rc != BISSD_OK) return rc;
             }
             if (!dx_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mB, mEf, mEb, mG;
@@ -609,6 +623,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     use_u4 = true;
                 }
             }
+            if (!intra_done && !have_fp32_cb) {                  // the prefix-sweep kernels read the fp32 matrix
+                const size_t smem_cb = tc::smem_bytes(ntQ, 0);
+                BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
+                    d, Cm, Bm, F(w.cb), F(w.cbt), nullptr, nullptr, nullptr, status));
+                have_fp32_cb = true;
+            }
             if (!intra_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mG, mX;
                 if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
@@ -649,8 +669,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         BISSD_LAUNCH("bmm_bwd", simt::bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, simt::TILE)), simt::TB, 0, s>>>(
             d, Bm, Cm, F(w.dCB), F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC));
     }
-    // four heads (warps) per CTA: twice the CTAs of an eight-warp launch, which balances better over the SMs
-    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<dim3(d.b * d.nc, ceil_div(d.H, 4)), 128, 4 * d.Q * sizeof(float), s>>>(
+    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<d.b * d.nc * d.H, 256, 0, s>>>(
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
         F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), use_u4 ? nullptr : F(w.da_f), use_u4 ? nullptr : F(w.da_b),
         use_u4 ? F(w.u4) : nullptr, F(w.dTpart), pass_nblk, nsplit, a.ddt,

@@ -88,51 +88,43 @@ __device__ __forceinline__ float warp_incl_scan(float v, int lane) {
     return v;
 }
 
-// ---------------------------------------------------------------------------------------------------------
-// Discretisation + both cumulative sums.  One warp per (batch, chunk, head).
-// Takes over _chunk_cumsum_fwd_kernel (src/ssd/bi/ssd_chunk_state.py:34-91).
-// dynamic smem: 8 * Q floats.
-__global__ void __launch_bounds__(TB) cumsum_fwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
-                                                 long long dsh, const float *A, const float *dt_bias, float *dt_out,
-                                                 float *cs_f, float *cs_b) {
-    extern __shared__ float sm[];
+__device__ __forceinline__ float warp_incl_scan_rev(float v, int lane) {   // v[lane] + v[lane+1] + ... + v[31]
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float t = __shfl_down_sync(0xffffffffu, v, o);
+        if (lane + o < 32) v += t;
+    }
+    return v;
+}
+// Inclusive scans over the 256 threads of a CTA (thread t = position t), ascending for a and b, descending for c and
+// e, all four at once: warp scans, the eight warp totals through shared memory (tot[4][8]), fixed order of additions.
+__device__ __forceinline__ void block_scan4(float &a, float &b, float &c, float &e, float (*tot)[8]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
-    const int h = blockIdx.y * 8 + warp;
-    if (h >= d.H) return;
-    float *sa = sm + warp * d.Q;
-    const int lim = min(d.Q, d.L - c * d.Q);
-    const float Ah = A[h];
-    const float bias = d.has_bias ? dt_bias[h] : 0.f;
-    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
-    float carry = 0.f;
-    for (int l0 = 0; l0 < d.Q; l0 += 32) {
-        const int l = l0 + lane;
-        float v = 0.f;
-        if (l < lim) {
-            v = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
-            if (d.softplus) v = softplus_ref(v);
-            v = fminf(fmaxf(v, d.dt_min), d.dt_max);
-        }
-        const float a = v * Ah;
-        const float inc = warp_incl_scan(a, lane) + carry;
-        carry = __shfl_sync(0xffffffffu, inc, 31);
-        if (l < d.Q) {
-            dt_out[base + l] = v;
-            cs_f[base + l] = inc;
-            sa[l] = a;
-        }
+    a = warp_incl_scan(a, lane);
+    b = warp_incl_scan(b, lane);
+    c = warp_incl_scan_rev(c, lane);
+    e = warp_incl_scan_rev(e, lane);
+    if (lane == 31) {
+        tot[0][warp] = a;
+        tot[1][warp] = b;
     }
-    __syncwarp();
-    carry = 0.f;
-    const int ntile = ceil_div(d.Q, 32);
-    for (int t = ntile - 1; t >= 0; --t) {
-        const int l = t * 32 + (31 - lane);            // lane 0 holds the last element of the tile
-        const float a = (l < d.Q) ? sa[l] : 0.f;
-        const float inc = warp_incl_scan(a, lane) + carry;
-        carry = __shfl_sync(0xffffffffu, inc, 31);
-        if (l < d.Q) cs_b[base + l] = inc;
+    if (lane == 0) {
+        tot[2][warp] = c;
+        tot[3][warp] = e;
     }
+    __syncthreads();
+    float pa = 0.f, pb = 0.f, pc = 0.f, pe = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        pa += (w < warp) ? tot[0][w] : 0.f;
+        pb += (w < warp) ? tot[1][w] : 0.f;
+        pc += (w > warp) ? tot[2][w] : 0.f;
+        pe += (w > warp) ? tot[3][w] : 0.f;
+    }
+    a += pa;
+    b += pb;
+    c += pc;
+    e += pe;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -832,7 +824,39 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Assemble d(a) from its six terms, go back through the discretisation.  One warp per (batch, chunk, head).
+// Discretisation + both cumulative sums, and their backward.  One CTA of 256 threads per (batch, chunk, head), thread
+// l holding position l of the chunk (chunk <= 256): every global operand is requested at once and each scan is one
+// warp scan plus a combine over the eight warp totals (a warp walking the chunk in eight steps was latency-bound).
+// grid (b * nc * H), head fastest.
+//
+// cumsum_fwd takes over _chunk_cumsum_fwd_kernel (src/ssd/bi/ssd_chunk_state.py:34-91):
+//   dt_out = clamp(softplus(dt + bias)), a = dt_out A, cs_f[l] = sum_{j<=l} a_j, cs_b[l] = sum_{j>=l} a_j; zero tail.
+__global__ void __launch_bounds__(256) cumsum_fwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
+                                                      long long dsh, const float *A, const float *dt_bias, float *dt_out,
+                                                      float *cs_f, float *cs_b) {
+    __shared__ float tot[4][8];
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int l = threadIdx.x;
+    const int lim = min(d.Q, d.L - c * d.Q);
+    const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
+    float v = 0.f;
+    if (l < lim) {
+        v = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + (d.has_bias ? dt_bias[h] : 0.f);
+        if (d.softplus) v = softplus_ref(v);
+        v = fminf(fmaxf(v, d.dt_min), d.dt_max);
+    }
+    const float a = (l < d.Q) ? v * A[h] : 0.f;
+    float f = a, dummy1 = 0.f, r = a, dummy2 = 0.f;
+    block_scan4(f, dummy1, r, dummy2, tot);
+    if (l < d.Q) {
+        dt_out[base + l] = v;
+        cs_f[base + l] = f;
+        cs_b[base + l] = r;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Assemble d(a) from its six terms, go back through the discretisation.  One CTA per (batch, chunk, head), see above.
 //   ddA = da_f + da_b + exclcumsum(nf) + exclrevcumsum(nb) + revcumsum(pf, +dT_f at Q-1) + cumsum(pb, +dT_b at 0)
 //   ddt = (ddA A + ddt_out), zero where the clamp is active, times sigmoid(pre) when softplus (pre <= 20)
 // Takes over the host glue at src/ssd/bi/ssd_combined.py:456-466 and _chunk_cumsum_bwd_kernel
@@ -840,112 +864,74 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
 // The intra-chunk decay gradients come either as da_f / da_b (already dominance sums) or, when u4 is given, as the
 // per-index differences u_f / u_b = column sums - row sums (four arrays: row tile 0 f, b, row tile 1 f, b), which are
 // added to the terms that are prefix-summed (u_f) and suffix-summed (u_b) exclusively; da_f / da_b are then null.
-// dynamic smem: (warps per CTA) * Q floats.
-__global__ void __launch_bounds__(TB) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
-                                                 long long dsh, const float *A, const float *dt_bias,
-                                                 const float *dt_out, const float *ddt_out, const float *nf,
-                                                 const float *nb, const float *pf, const float *pb, const float *da_f,
-                                                 const float *da_b, const float *u4, const float *dTpart, int nblk,
-                                                 int nsplit, void *ddt, float *dApart, float *dbiaspart) {
-    extern __shared__ float sm[];
+__global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
+                                                      long long dsh, const float *A, const float *dt_bias,
+                                                      const float *dt_out, const float *ddt_out, const float *nf,
+                                                      const float *nb, const float *pf, const float *pb, const float *da_f,
+                                                      const float *da_b, const float *u4, const float *dTpart, int nblk,
+                                                      int nsplit, void *ddt, float *dApart, float *dbiaspart) {
+    __shared__ float tot[4][8];
+    __shared__ float red[2][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.x / d.nc, c = blockIdx.x % d.nc;
-    const int h = blockIdx.y * (blockDim.x >> 5) + warp;         // one warp per head; any number of warps per CTA
-    if (h >= d.H) return;
-    float *acc = sm + warp * d.Q;
+    const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
+    const int l = threadIdx.x;
     const int lim = min(d.Q, d.L - c * d.Q);
     const long long base = ((long long)(b * d.H + h) * d.nc + c) * d.Q;
     const long long tix = (long long)(b * d.H + h) * d.nc + c;
     const long long split_stride = (long long)d.b * d.H * d.nc * d.Q;   // nf/nb/pf/pb hold nsplit partial copies
-    float dTf = 0.f, dTb = 0.f;
-    for (int k = 0; k < nblk; ++k) {
-        dTf += dTpart[tix * nblk + k];
-        dTb += dTpart[((long long)d.b * d.H * d.nc + tix) * nblk + k];
-    }
-    // Every global operand of a pass is requested before the first scan step (chunk <= 256: at most 8 tiles of 32), so
-    // the loads of all tiles are in flight together instead of one round trip per tile.
-    constexpr int MAXT = 8;
-    const int ntile = ceil_div(d.Q, 32);
-    // ascending pass: exclusive cumsum of nf (+ u_f), inclusive cumsum of pb (+dT_b at index 0)
-    {
-        float a1[MAXT], a2[MAXT], ex[MAXT];
-#pragma unroll
-        for (int t = 0; t < MAXT; ++t) {
-            a1[t] = a2[t] = ex[t] = 0.f;
-            const int l = t * 32 + lane;
-            if (t < ntile && l < d.Q) {
-                for (int k = 0; k < nsplit; ++k) {
-                    a1[t] += nf[k * split_stride + base + l];
-                    a2[t] += pb[k * split_stride + base + l];
-                }
-                if (u4) a1[t] += u4[base + l] + u4[2 * split_stride + base + l];      // u_f of the two row tiles
-                if (da_f) ex[t] = da_f[base + l] + da_b[base + l];
-                if (l == 0) a2[t] += dTb;
-            }
+    // the four scanned sequences: nf (+u_f) and pb ascending, nb (+u_b) and pf descending
+    float v1 = 0.f, v2 = 0.f, w1 = 0.f, w2 = 0.f, ex = 0.f, dto = 0.f, dlo = 0.f, pre = 0.f;
+    if (l < d.Q) {
+        for (int k = 0; k < nsplit; ++k) {
+            v1 += nf[k * split_stride + base + l];
+            v2 += pb[k * split_stride + base + l];
+            w1 += nb[k * split_stride + base + l];
+            w2 += pf[k * split_stride + base + l];
         }
-        float c1 = 0.f, c2 = 0.f;
-#pragma unroll
-        for (int t = 0; t < MAXT; ++t) {
-            if (t < ntile) {
-                const int l = t * 32 + lane;
-                const float i1 = warp_incl_scan(a1[t], lane) + c1, i2 = warp_incl_scan(a2[t], lane) + c2;
-                c1 = __shfl_sync(0xffffffffu, i1, 31);
-                c2 = __shfl_sync(0xffffffffu, i2, 31);
-                if (l < d.Q) acc[l] = (i1 - a1[t]) + i2 + ex[t];
-            }
+        if (u4) {
+            v1 += u4[base + l] + u4[2 * split_stride + base + l];            // u_f of the two row tiles
+            w1 += u4[split_stride + base + l] + u4[3 * split_stride + base + l];   // u_b
+        }
+        if (da_f) ex = da_f[base + l] + da_b[base + l];
+        if (l == 0)                                                       // dT_b enters at index 0, dT_f at index Q-1
+            for (int k = 0; k < nblk; ++k) v2 += dTpart[((long long)d.b * d.H * d.nc + tix) * nblk + k];
+        if (l == d.Q - 1)
+            for (int k = 0; k < nblk; ++k) w2 += dTpart[tix * nblk + k];
+        if (l < lim) {
+            dto = ddt_out[base + l];
+            dlo = dt_out[base + l];
+            pre = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + (d.has_bias ? dt_bias[h] : 0.f);
         }
     }
-    __syncwarp();
-    // descending pass: exclusive reverse cumsum of nb (+ u_b), inclusive reverse cumsum of pf (+dT_f at index Q-1)
+    float s1 = v1, s2 = v2, r1 = w1, r2 = w2;
+    block_scan4(s1, s2, r1, r2, tot);
     float sumA = 0.f, sumB = 0.f;
-    const float Ah = A[h];
-    const float bias = d.has_bias ? dt_bias[h] : 0.f;
-    {
-        float a1[MAXT], a2[MAXT], dto[MAXT], pre[MAXT], dlo[MAXT];
-#pragma unroll
-        for (int t = 0; t < MAXT; ++t) {
-            a1[t] = a2[t] = dto[t] = pre[t] = dlo[t] = 0.f;
-            const int l = t * 32 + (31 - lane);
-            if (t < ntile && l < d.Q) {
-                for (int k = 0; k < nsplit; ++k) {
-                    a1[t] += nb[k * split_stride + base + l];
-                    a2[t] += pf[k * split_stride + base + l];
-                }
-                if (u4) a1[t] += u4[split_stride + base + l] + u4[3 * split_stride + base + l];   // u_b of the two row tiles
-                if (l == d.Q - 1) a2[t] += dTf;
-                if (l < lim) {
-                    dto[t] = ddt_out[base + l];
-                    dlo[t] = dt_out[base + l];
-                    pre[t] = ld_any(dt, dt_dtype, b * dsb + (long long)(c * d.Q + l) * dsl + h * dsh) + bias;
-                }
-            }
-        }
-        float c1 = 0.f, c2 = 0.f;
-#pragma unroll
-        for (int t = MAXT - 1; t >= 0; --t) {
-            if (t < ntile) {
-                const int l = t * 32 + (31 - lane);
-                const float i1 = warp_incl_scan(a1[t], lane) + c1, i2 = warp_incl_scan(a2[t], lane) + c2;
-                c1 = __shfl_sync(0xffffffffu, i1, 31);
-                c2 = __shfl_sync(0xffffffffu, i2, 31);
-                if (l < lim) {
-                    const float ddA = acc[l] + (i1 - a1[t]) + i2;
-                    float g = ddA * Ah + dto[t];
-                    const float val = d.softplus ? softplus_ref(pre[t]) : pre[t];
-                    if (val < d.dt_min || val > d.dt_max) g = 0.f;
-                    if (d.softplus && pre[t] <= 20.f) g *= sigmoidf_(pre[t]);
-                    st_any(ddt, dt_dtype, ((long long)b * d.L + c * d.Q + l) * d.H + h, g);
-                    sumA += ddA * dlo[t];
-                    sumB += g;
-                }
-            }
-        }
+    if (l < lim) {
+        const float ddA = (s1 - v1) + s2 + ex + (r1 - w1) + r2;
+        float g = ddA * A[h] + dto;
+        const float val = d.softplus ? softplus_ref(pre) : pre;
+        if (val < d.dt_min || val > d.dt_max) g = 0.f;
+        if (d.softplus && pre <= 20.f) g *= sigmoidf_(pre);
+        st_any(ddt, dt_dtype, ((long long)b * d.L + c * d.Q + l) * d.H + h, g);
+        sumA = ddA * dlo;
+        sumB = g;
     }
     sumA = warp_sum(sumA);
     sumB = warp_sum(sumB);
     if (lane == 0) {
-        dApart[(long long)(b * d.nc + c) * d.H + h] = sumA;
-        dbiaspart[(long long)(b * d.nc + c) * d.H + h] = sumB;
+        red[0][warp] = sumA;
+        red[1][warp] = sumB;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float ta = 0.f, tb = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            ta += red[0][w];
+            tb += red[1][w];
+        }
+        dApart[(long long)(b * d.nc + c) * d.H + h] = ta;
+        dbiaspart[(long long)(b * d.nc + c) * d.H + h] = tb;
     }
 }
 
