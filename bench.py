@@ -96,9 +96,9 @@ def kernel_model(name, cfg):
         "dx": (t * (4 * Q * P * N + 2 * Q * Q * P), 4 * X + BC + 2 * 2 * ST + CB + 5 * HQ),
     }
     model["intra_sums"] = model["intra_decay_grad"]
-    # tensor-core kernels are reported as tc_<phase>[_tma|_ws]; they do the same algorithmic work as the phase they replace
+    # tensor-core kernels are reported as tc_<phase>[_tma|_ws|_grp]; they do the same algorithmic work as the phase they replace
     key = name[3:] if name.startswith("tc_") else name
-    for suffix in ("_tma", "_ws"):
+    for suffix in ("_tma", "_ws", "_grp"):
         if key.endswith(suffix):
             key = key[:-len(suffix)]
     return model.get(key, model.get(key + "_kernel", (0, 0)))

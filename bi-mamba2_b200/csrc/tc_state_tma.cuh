@@ -119,5 +119,161 @@ state_gemm_tma(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
     if (warp == 0) tmem_dealloc(tmem, ncols);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same two products, pipelined over the heads of a group (headdim 64).  The B / C tile [Q x 128 n] - the same for
+// every head of the group - is loaded once per CTA; per head the x / g tile [Q x 64] arrives twice by TMA (ring of two
+// stages), is scaled in place once with the forward and once with the backward row factor, and ONE chain of Q/16 MMAs
+// with N = 128 (columns 0-63 forward, 64-127 backward) forms both directions.  Accumulators are double-buffered in
+// TMEM: the epilogue of head h (128 x 128 fp32 to global memory) runs while the MMAs of head h+1 execute.  Row
+// factors are fetched one head ahead.
+// grid (b*nc*G*ks, N/128): ks CTAs share the heads of a group (R % ks == 0).
+struct StateGrpShared {
+    uint64_t bar_a, full[2], done[2];
+    uint32_t tmem_base;
+};
+inline bool state_grp_ok(int P, int N, int Q, int R) { return P == 64 && N % 128 == 0 && N <= 256 && (Q == 128 || Q == 256) && R >= 2; }
+inline size_t state_grp_smem(int Q) { return 1024 + 2 * (size_t)Q * 128 + 2 * 2 * (size_t)Q * 128 + 2 * 2 * (size_t)Q * 4; }
+inline int state_grp_ksplit(int groups_total, int R, int sms) {      // CTAs per group: fill the SMs once, keep >= 2 heads per CTA
+    int ks = 1;
+    for (int k = 1; k <= R / 2; ++k)
+        if (R % k == 0 && (long long)groups_total * k <= sms) ks = k;
+    return ks;
+}
+
+template <class T, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol, int ks,
+               const float *dt_out, const float *cs_f, const float *cs_b, float *out, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ StateGrpShared sh;
+    constexpr int P = 64;
+    const int N = d.N, Q = d.Q, R = d.R;
+    uint8_t *smA = smem_align1024(dyn);                         // 2 blocks [Q x 64 n], MN-major
+    uint8_t *smX = smA + 2 * Q * 128;                           // 2 stages x (forward | backward) blocks [Q x 64 p]
+    float *sc = reinterpret_cast<float *>(smX + 4 * Q * 128);   // [2 bufs][2 dirs][Q]
+    const int stage_bytes = 2 * Q * 128;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int k = blockIdx.x % ks, bx = blockIdx.x / ks;
+    const int grp = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int n0 = blockIdx.y * 128;
+    const int lim = min(Q, d.L - c * Q);
+    const int nh = R / ks, h0 = grp * R + k * nh;               // this CTA's heads h0 .. h0 + nh - 1
+    auto load_head = [&](int i) {                               // thread 0: the x / g tile of head i, twice, into stage i & 1
+        uint8_t *dst = smX + (i & 1) * stage_bytes;
+        mbar_expect_tx(&sh.full[i & 1], (uint32_t)stage_bytes);
+        tma_load4(dst, &tmCol, 0, h0 + i, c * Q, b, &sh.full[i & 1]);
+        tma_load4(dst + Q * 128, &tmCol, 0, h0 + i, c * Q, b, &sh.full[i & 1]);
+    };
+    if (warp == 0) tmem_alloc(&sh.tmem_base, 256);
+    if (tid == 0) {
+        mbar_init(&sh.bar_a, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.done[i], 1);
+        }
+        fence_mbar_init();
+        mbar_expect_tx(&sh.bar_a, (uint32_t)(2 * Q * 128));
+        for (int j = 0; j < 2; ++j) tma_load4(smA + j * Q * 128, &tmRow, n0 + j * 64, grp, c * Q, b, &sh.bar_a);
+        load_head(0);
+        if (nh > 1) load_head(1);
+    }
+    // row factors: thread l holds position l; inputs of head i + 1 are in flight while head i is worked on
+    float pf_ = 0.f, pb_ = 0.f, pTf = 0.f, pTb = 0.f, pdt = 0.f;
+    auto fetch_scale = [&](int i) {
+        const long long base = ((long long)(b * d.H + h0 + i) * d.nc + c) * Q;
+        if (tid < lim) {
+            pf_ = cs_f[base + tid];
+            pb_ = cs_b[base + tid];
+            if (MODE == 0) {
+                pTf = cs_f[base + Q - 1];
+                pTb = cs_b[base];
+                pdt = dt_out[base + tid];
+            }
+        }
+    };
+    auto write_scale = [&](int i) {
+        if (tid < Q) {
+            float wf = 0.f, wb = 0.f;
+            if (tid < lim) {
+                wf = (MODE == 0) ? pdt * __expf(pTf - pf_) : __expf(pf_);
+                wb = (MODE == 0) ? pdt * __expf(pTb - pb_) : __expf(pb_);
+            }
+            sc[((i & 1) * 2 + 0) * Q + tid] = wf;
+            sc[((i & 1) * 2 + 1) * Q + tid] = wb;
+        }
+    };
+    fetch_scale(0);
+    write_scale(0);
+    if (nh > 1) fetch_scale(1);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    const long long per_dir = (long long)d.b * d.nc * d.H * P * N;
+    const int n = n0 + (warp & 3) * 32 + lane, edir = warp >> 2;   // epilogue: row n, the 64 columns of one direction
+    bool ok = true;
+    auto epilogue = [&](int i) {                                // head i: accumulator i & 1 -> out[dir][p][n]
+        ok = mbar_wait(&sh.done[i & 1], (i >> 1) & 1);
+        if (!ok) return;
+        tc_fence_after();
+        float *o = out + edir * per_dir + ((long long)(b * d.nc + c) * d.H + h0 + i) * P * N + n;
+        const uint32_t tl = tmem_lane_base(tmem) + (i & 1) * 128 + edir * 64;
+        uint32_t v0[32], v1[32];                                // both halves requested before either is waited for
+        tmem_ld32_nowait(tl, v0);
+        tmem_ld32_nowait(tl + 32, v1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[(long long)j * N] = __uint_as_float(v0[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[(long long)(32 + j) * N] = __uint_as_float(v1[j]);
+        tc_fence_before();
+    };
+#pragma unroll 1
+    for (int i = 0; i < nh; ++i) {
+        uint8_t *sx = smX + (i & 1) * stage_bytes;
+        ok = mbar_wait(&sh.full[i & 1], (i >> 1) & 1);
+        if (ok) {                                               // rows l of both blocks times their factor, in place
+            const float *wf = sc + ((i & 1) * 2) * Q, *wb = wf + Q;
+            for (int q = tid; q < Q * 8; q += kThreads) {
+                uint4 *pf4 = reinterpret_cast<uint4 *>(sx) + q, *pb4 = reinterpret_cast<uint4 *>(sx + Q * 128) + q;
+                const int l = q >> 3;
+                *pf4 = scale8_packed<T>(*pf4, wf[l]);
+                *pb4 = scale8_packed<T>(*pb4, wb[l]);
+            }
+            fence_async_smem();
+            if (i + 1 < nh) {
+                write_scale(i + 1);
+                if (i + 2 < nh) fetch_scale(i + 2);
+            }
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0) {
+            if (i == 0) ok = mbar_wait(&sh.bar_a, 0);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t idesc = instr_desc(AbFmt<T>::v, true, true, 128);
+                for (int kk = 0; kk < Q / 16; ++kk)
+                    umma(tmem + (i & 1) * 128, smem_desc(smem_u32(smA) + kk * 2048, (uint32_t)Q * 128, 1024),
+                         smem_desc(smem_u32(sx) + kk * 2048, (uint32_t)Q * 128, 1024), idesc, kk > 0 ? 1u : 0u);
+                umma_commit(&sh.done[i & 1]);
+            }
+        }
+        if (i >= 1) {
+            epilogue(i - 1);                                    // overlaps the MMAs just issued
+            // stage (i - 1) & 1 is free (its MMAs have completed) and so is accumulator (i - 1) & 1 after the sync below
+            if (ok && tid == 0 && i + 1 < nh) load_head(i + 1);
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+    }
+    if (ok) epilogue(nh - 1);
+    ok = __syncthreads_and(ok);
+    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
 }  // namespace tc
 }  // namespace bissd
