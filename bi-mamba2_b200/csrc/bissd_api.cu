@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "conv_kernels.cuh"
 #include "norm_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_intra_sums.cuh"
@@ -770,6 +771,49 @@ static int norm_backward_impl(const bissd_norm_args *a, const norm::NormDims &d,
     } while (0)
 
 
+// ---- depthwise conv1d + SiLU -----------------------------------------------------------------------------------
+static int conv_check(const bissd_conv_args *a, conv::ConvDims *d, bool backward) {
+    if (!a || !a->x || !a->weight) return BISSD_ERR_NULL;
+    if (!backward && !a->out) return BISSD_ERR_NULL;
+    if (backward && (!a->dout || !a->dx || !a->dweight || (a->bias && !a->dbias))) return BISSD_ERR_NULL;
+    if (a->batch <= 0 || a->seqlen <= 0 || a->channels <= 0 || a->channels % 8 != 0) return BISSD_ERR_SHAPE;
+    if (a->width <= 0 || a->width > conv::kMaxK || a->width % 2 == 0) return BISSD_ERR_SHAPE;
+    if (a->x_dtype < BISSD_F32 || a->x_dtype > BISSD_F16) return BISSD_ERR_DTYPE;
+    if (a->w_dtype != BISSD_F32 && a->w_dtype != a->x_dtype) return BISSD_ERR_DTYPE;
+    auto al = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (!al(a->x) || !al(a->out) || !al(a->dout) || !al(a->dx) || !al(a->bias)) return BISSD_ERR_ALIGN;
+    if (a->x_stride_batch % 8 || a->x_stride_row % 8 || a->out_stride_batch % 8 || a->out_stride_row % 8) return BISSD_ERR_ALIGN;
+    d->batch = a->batch; d->seqlen = a->seqlen; d->channels = a->channels; d->width = a->width;
+    d->xsb = a->x_stride_batch; d->xsl = a->x_stride_row; d->osb = a->out_stride_batch; d->osl = a->out_stride_row;
+    d->has_bias = a->bias != nullptr;
+    return BISSD_OK;
+}
+static inline int conv_row_blocks(int seqlen) { return (seqlen + conv::kRows - 1) / conv::kRows; }
+static inline size_t conv_dpre_bytes(const bissd_conv_args *a) {
+    return align256((size_t)a->batch * a->seqlen * a->channels * (a->x_dtype == BISSD_F32 ? 4 : 2));
+}
+template <class T, class W>
+static int conv_forward_impl(const bissd_conv_args *a, const conv::ConvDims &d, cudaStream_t s) {
+    const dim3 grid((d.channels / 8 + 127) / 128, conv_row_blocks(d.seqlen), d.batch);
+    BISSD_LAUNCH("dwconv_silu_fwd", conv::dwconv_silu_fwd<T, W><<<grid, 128, 0, s>>>(d, a->x, a->weight, a->bias, a->out));
+    return BISSD_OK;
+}
+template <class T, class W>
+static int conv_backward_impl(const bissd_conv_args *a, const conv::ConvDims &d, char *ws, cudaStream_t s) {
+    const dim3 grid((d.channels / 8 + 127) / 128, conv_row_blocks(d.seqlen), d.batch);
+    void *dpre = ws;
+    float *part = reinterpret_cast<float *>(ws + conv_dpre_bytes(a));
+    // dout is required to be contiguous (checked by the caller), so dpre shares its strides
+    BISSD_LAUNCH("dwconv_silu_bwd_pre", conv::dwconv_silu_bwd_pre<T, W><<<grid, 128, 0, s>>>(
+        d, a->x, a->weight, a->bias, a->dout, dpre, part));
+    BISSD_LAUNCH("dwconv_silu_bwd_dx", conv::dwconv_silu_bwd_dx<T, W><<<grid, 128, 0, s>>>(d, dpre, a->weight, a->dx));
+    const int nparts = d.batch * conv_row_blocks(d.seqlen);
+    const long long n = (long long)d.channels * (conv::kMaxK + 1);
+    BISSD_LAUNCH("conv_bwd_reduce", conv::conv_bwd_reduce<W><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
+        part, nparts, d.channels, d.width, a->dweight, a->dbias));
+    return BISSD_OK;
+}
+
 extern "C" {
 
 int bissd_abi_version(void) { return BISSD_ABI_VERSION; }
@@ -912,6 +956,40 @@ int bissd_rmsnorm_gated_backward(const bissd_norm_args *a, void *workspace, size
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     float *part = static_cast<float *>(workspace);
     BISSD_NORM_DISPATCH(norm_backward_impl, a, d, part, s);
+}
+
+int bissd_dwconv_silu_workspace_bytes(const bissd_conv_args *a, size_t *bwd_bytes) {
+    if (!a || !bwd_bytes) return BISSD_ERR_NULL;
+    if (a->batch <= 0 || a->seqlen <= 0 || a->channels <= 0) return BISSD_ERR_SHAPE;
+    *bwd_bytes = conv_dpre_bytes(a) +
+                 (size_t)a->batch * conv_row_blocks(a->seqlen) * a->channels * (conv::kMaxK + 1) * sizeof(float);
+    return BISSD_OK;
+}
+
+int bissd_dwconv_silu_forward(const bissd_conv_args *a, void *stream) {
+    conv::ConvDims d;
+    int rc = conv_check(a, &d, false);
+    if (rc != BISSD_OK) return rc;
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    BISSD_NORM_DISPATCH(conv_forward_impl, a, d, s);
+}
+
+int bissd_dwconv_silu_backward(const bissd_conv_args *a, void *workspace, size_t workspace_bytes, void *stream) {
+    conv::ConvDims d;
+    int rc = conv_check(a, &d, true);
+    if (rc != BISSD_OK) return rc;
+    if (!workspace) return BISSD_ERR_NULL;
+    size_t need = 0;
+    bissd_dwconv_silu_workspace_bytes(a, &need);
+    if (workspace_bytes < need) return BISSD_ERR_WORKSPACE;
+    if (a->out_stride_row != a->channels || a->out_stride_batch != (int64_t)a->seqlen * a->channels)
+        return BISSD_ERR_ALIGN;                                  // dout (and the dpre scratch) as contiguous rows
+    rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    BISSD_NORM_DISPATCH(conv_backward_impl, a, d, static_cast<char *>(workspace), s);
 }
 
 const char *bissd_kernel_path(const bissd_problem *p) {

@@ -54,10 +54,20 @@ class NormArgs(C.Structure):
                 ("dout", C.c_void_p), ("dx", C.c_void_p), ("dz", C.c_void_p), ("dweight", C.c_void_p)]
 
 
+class ConvArgs(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("seqlen", C.c_int32), ("channels", C.c_int32), ("width", C.c_int32),
+                ("x_dtype", C.c_int32), ("w_dtype", C.c_int32),
+                ("x_stride_batch", C.c_int64), ("x_stride_row", C.c_int64),
+                ("out_stride_batch", C.c_int64), ("out_stride_row", C.c_int64),
+                ("x", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p), ("out", C.c_void_p),
+                ("dout", C.c_void_p), ("dx", C.c_void_p), ("dweight", C.c_void_p), ("dbias", C.c_void_p)]
+
+
 EXPORTS = ("bissd_abi_version", "bissd_strerror", "bissd_last_cuda_error", "bissd_workspace_bytes", "bissd_forward",
            "bissd_backward", "bissd_kernel_path", "bissd_launch_count", "bissd_trace_enable", "bissd_trace_read", "bissd_selftest_gemm", "bissd_read_status",
            "bissd_forward_static_scratch", "bissd_rmsnorm_gated_workspace_bytes", "bissd_rmsnorm_gated_forward",
-           "bissd_rmsnorm_gated_backward")
+           "bissd_rmsnorm_gated_backward", "bissd_dwconv_silu_workspace_bytes", "bissd_dwconv_silu_forward",
+           "bissd_dwconv_silu_backward")
 
 STATIC_SCRATCH_BYTES = 16 << 20      # BISSD_STATIC_SCRATCH_BYTES
 ERR_TOO_LARGE = -9
@@ -104,6 +114,12 @@ def load():
     lib.bissd_rmsnorm_gated_forward.argtypes = [C.POINTER(NormArgs), C.c_void_p]
     lib.bissd_rmsnorm_gated_backward.restype = C.c_int
     lib.bissd_rmsnorm_gated_backward.argtypes = [C.POINTER(NormArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.bissd_dwconv_silu_workspace_bytes.restype = C.c_int
+    lib.bissd_dwconv_silu_workspace_bytes.argtypes = [C.POINTER(ConvArgs), C.POINTER(C.c_size_t)]
+    lib.bissd_dwconv_silu_forward.restype = C.c_int
+    lib.bissd_dwconv_silu_forward.argtypes = [C.POINTER(ConvArgs), C.c_void_p]
+    lib.bissd_dwconv_silu_backward.restype = C.c_int
+    lib.bissd_dwconv_silu_backward.argtypes = [C.POINTER(ConvArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.bissd_read_status.restype = C.c_int
     lib.bissd_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]
     lib.bissd_selftest_gemm.restype = C.c_int

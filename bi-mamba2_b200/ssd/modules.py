@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ssd.bi.conv_silu import dwconv1d_silu
 from ssd.bi.layernorm_gated import RMSNorm as RMSNormGated
 from ssd.bi.ssd_combined import bimamba_chunk_scan_combined
 
@@ -73,15 +74,17 @@ class BiMamba2(nn.Module):
         dt_limit_kwargs = {} if self.dt_limit == (0.0, float("inf")) else dict(dt_limit=self.dt_limit)
         z, xBC, dt = torch.split(
             zxbcdt, [self.d_inner, self.d_inner + 2 * self.ngroups * self.d_state, self.nheads], dim=-1)
-        dt = F.softplus(dt + self.dt_bias)
         assert self.activation in ["silu", "swish"]
-        xBC = self.act(self.conv1d(xBC.transpose(1, 2)).transpose(1, 2))
+        # depthwise conv + SiLU channels-last (no transposes; x / B / C below are strided views the scan reads in
+        # place); softplus(dt + dt_bias) is done inside the scan operator
+        xBC = dwconv1d_silu(xBC, self.conv1d.weight, self.conv1d.bias)
         x, B, C = torch.split(xBC, [self.d_inner, self.ngroups * self.d_state, self.ngroups * self.d_state], dim=-1)
         b, l = x.shape[0], x.shape[1]
         y = bimamba_chunk_scan_combined(
             x.unflatten(-1, (self.nheads, self.headdim)), dt, A,
             B.unflatten(-1, (self.ngroups, self.d_state)), C.unflatten(-1, (self.ngroups, self.d_state)),
-            chunk_size=self.chunk_size, D=self.D, z=None, **dt_limit_kwargs)
+            chunk_size=self.chunk_size, D=self.D, z=None, dt_bias=self.dt_bias.float(), dt_softplus=True,
+            **dt_limit_kwargs)
         y = y.reshape(b, l, self.d_inner)
         y = self.norm(y, z)
         return self.out_proj(y)

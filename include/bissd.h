@@ -182,6 +182,30 @@ int bissd_rmsnorm_gated_workspace_bytes(const bissd_norm_args *args, size_t *bwd
 int bissd_rmsnorm_gated_forward(const bissd_norm_args *args, void *stream);
 int bissd_rmsnorm_gated_backward(const bissd_norm_args *args, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- depthwise conv1d + SiLU, channels-last (the front end of BiMamba2) -------------------------------------------
+ * Takes over `self.act(self.conv1d(xBC.transpose(1, 2)).transpose(1, 2))` of src/ssd/modules.py:164-167 (nn.Conv1d with
+ * groups = channels, padding = width / 2, then SiLU) without the two transposes:
+ *     out[b,l,c] = silu(bias[c] + sum_k weight[c,k] x[b, l + k - width/2, c]),   zero outside 0 <= l < seqlen.
+ * x, dx: (batch, seqlen, channels) with channel stride 1 and the given batch / row strides (elements, multiples of 8);
+ * out, dout: the same shape, contiguous rows of `channels`; weight, dweight: (channels, width) contiguous, bias /
+ * dbias: (channels) or NULL; w_dtype fp32 or x's dtype.  channels % 8 == 0, width odd and <= 8, 16-byte aligned
+ * pointers.  The backward needs bissd_dwconv_silu_workspace_bytes() of scratch (dpre and the partial weight
+ * gradients). */
+typedef struct bissd_conv_args {
+    int32_t batch, seqlen, channels, width;
+    int32_t x_dtype, w_dtype;            /* bissd_dtype */
+    int64_t x_stride_batch, x_stride_row;       /* x and dx */
+    int64_t out_stride_batch, out_stride_row;   /* out and dout */
+    const void *x, *weight, *bias;
+    void *out;                           /* forward result */
+    const void *dout;                    /* backward only, as are the next three */
+    void *dx, *dweight, *dbias;
+} bissd_conv_args;
+
+int bissd_dwconv_silu_workspace_bytes(const bissd_conv_args *args, size_t *bwd_bytes);
+int bissd_dwconv_silu_forward(const bissd_conv_args *args, void *stream);
+int bissd_dwconv_silu_backward(const bissd_conv_args *args, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
 const char *bissd_kernel_path(const bissd_problem *p);
 

@@ -1,0 +1,53 @@
+"""Depthwise conv1d + SiLU kernels (csrc/conv_kernels.cuh, through the C ABI) against the reference expression
+`silu(conv1d(x^T, w, b, padding=K//2, groups=C))^T` evaluated by PyTorch in fp32 on the same (rounded) inputs.
+Tolerances: max |got - ref| / max |ref| per tensor <= 1e-5 for fp32, 2e-2 for bf16 / fp16."""
+import pytest
+import torch
+
+from oracle.bissd_oracle import max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # name, (batch, seqlen, channels), width, dtype, weight dtype, bias
+    ("module_shape_bf16", (2, 300, 2304), 7, torch.bfloat16, torch.bfloat16, True),
+    ("fp32_width3", (3, 77, 64), 3, torch.float32, torch.float32, True),
+    ("fp16_no_bias", (1, 130, 520), 5, torch.float16, torch.float32, False),
+    ("short_sequence", (4, 3, 128), 7, torch.float32, torch.float32, True),
+]
+
+
+@pytest.mark.parametrize("name,shape,K,dtype,wdtype,has_bias", CASES, ids=[c[0] for c in CASES])
+def test_forward_and_backward_match_reference_expression(name, shape, K, dtype, wdtype, has_bias):
+    from ssd.bi.conv_silu import _kernel_ok, dwconv1d_silu, dwconv1d_silu_ref
+    b, L, C = shape
+    g = torch.Generator().manual_seed(sum(name.encode()))
+    x = torch.randn(b, L, C, generator=g).to(dtype).cuda()
+    w = (0.4 * torch.randn(C, 1, K, generator=g)).to(wdtype).cuda()
+    bias = (0.2 * torch.randn(C, generator=g)).to(wdtype).cuda() if has_bias else None
+    dout = torch.randn(b, L, C, generator=g).to(dtype).cuda()
+    assert _kernel_ok(x, w, bias)
+    leaves = [t.clone().requires_grad_(True) if t is not None else None for t in (x, w, bias)]
+    out = dwconv1d_silu(*leaves)
+    out.backward(dout)
+    ref_leaves = [t.detach().float().requires_grad_(True) if t is not None else None for t in (x, w, bias)]
+    ref = dwconv1d_silu_ref(*ref_leaves)
+    ref.backward(dout.float())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert out.dtype == dtype and out.shape == x.shape and out.is_contiguous()
+    assert max_rel_err(out, ref) < tol
+    for got, want, nm in zip(leaves, ref_leaves, ("dx", "dw", "db")):
+        if got is not None:
+            assert got.grad.shape == got.shape and got.grad.dtype == got.dtype
+            assert max_rel_err(got.grad, want.grad) < tol, nm
+
+
+def test_strided_input_slice_is_read_in_place_and_results_repeat():
+    from ssd.bi.conv_silu import dwconv1d_silu, dwconv1d_silu_ref
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(2, 200, 1024 + 512 + 24, generator=g).bfloat16().cuda()
+    x = big[..., 1024:1536]                                  # what BiMamba2 does: a channel slice of in_proj's output
+    w = (0.3 * torch.randn(512, 1, 7, generator=g)).cuda()
+    a, b2 = dwconv1d_silu(x, w), dwconv1d_silu(x, w)
+    assert torch.equal(a, b2)
+    assert max_rel_err(a, dwconv1d_silu_ref(x.float(), w)) < 2e-2
