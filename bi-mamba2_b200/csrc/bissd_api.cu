@@ -748,11 +748,13 @@ static int norm_forward_impl(const bissd_norm_args *a, const norm::NormDims &d, 
 template <class T, class W>
 static int norm_backward_impl(const bissd_norm_args *a, const norm::NormDims &d, float *part, cudaStream_t s) {
     const int grid = norm_grid(d);
-    const size_t smem = (size_t)d.hidden * sizeof(float);
+    const size_t smem = (size_t)norm::kWarps * d.hidden * sizeof(float);
     if (d.hidden <= 2048) {
+        BISSD_ALLOW((norm::rmsnorm_gated_bwd<T, W, 8>), smem);
         BISSD_LAUNCH("rmsnorm_gated_bwd", norm::rmsnorm_gated_bwd<T, W, 8><<<grid, norm::kThreads, smem, s>>>(
             d, a->x, a->z, a->weight, a->dout, a->rstd, a->dx, a->dz, part));
     } else {
+        BISSD_ALLOW((norm::rmsnorm_gated_bwd<T, W, 16>), smem);
         BISSD_LAUNCH("rmsnorm_gated_bwd", norm::rmsnorm_gated_bwd<T, W, 16><<<grid, norm::kThreads, smem, s>>>(
             d, a->x, a->z, a->weight, a->dout, a->rstd, a->dx, a->dz, part));
     }
@@ -805,7 +807,8 @@ static int conv_backward_impl(const bissd_conv_args *a, const conv::ConvDims &d,
     float *part = reinterpret_cast<float *>(ws + conv_dpre_bytes(a));
     // dout is required to be contiguous (checked by the caller), so dpre shares its strides
     BISSD_LAUNCH("dwconv_silu_bwd_pre", conv::dwconv_silu_bwd_pre<T, W><<<grid, 128, 0, s>>>(
-        d, a->x, a->weight, a->bias, a->dout, dpre, part));
+        d, a->x, a->weight, a->bias, a->dout, dpre));
+    BISSD_LAUNCH("dwconv_silu_bwd_dw", conv::dwconv_silu_bwd_dw<T><<<grid, 128, 0, s>>>(d, a->x, dpre, part));
     BISSD_LAUNCH("dwconv_silu_bwd_dx", conv::dwconv_silu_bwd_dx<T, W><<<grid, 128, 0, s>>>(d, dpre, a->weight, a->dx));
     const int nparts = d.batch * conv_row_blocks(d.seqlen);
     const long long n = (long long)d.channels * (conv::kMaxK + 1);

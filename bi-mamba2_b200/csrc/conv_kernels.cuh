@@ -8,7 +8,8 @@
 //   dw[c,k] = sum_{b,l} dpre[b,l,c] x[b, l + k - K/2, c];  dbias[c] = sum_{b,l} dpre[b,l,c]
 //
 // HBM-bound: every thread owns 8 adjacent channels (one 16-byte access per row) and walks a run of rows; the K
-// neighbouring rows of a window are re-read from L1 / L2.  The backward recomputes pre instead of saving it.  Weight
+// neighbouring rows of a window are re-read from L1 / L2.  The backward recomputes pre instead of saving it and runs
+// as three light kernels (dpre; weight / bias gradient partials; dx) rather than one register-heavy one.  Weight
 // and bias gradients: per-thread accumulators over the thread's rows, one partial row per (batch, row block) in the
 // workspace, summed in a fixed order by conv_bwd_reduce - no float atomics.  Width K <= 8.
 #pragma once
@@ -33,7 +34,7 @@ using norm::sigmoidn;
 
 // grid (channels / 8 / 128 rounded up, ceil(L / kRows), batch); block 128: thread = 8 channels, kRows rows.
 template <class T, class W>
-__global__ void __launch_bounds__(128) dwconv_silu_fwd(ConvDims d, const void *x, const void *weight, const void *bias,
+__global__ void __launch_bounds__(128, 4) dwconv_silu_fwd(ConvDims d, const void *x, const void *weight, const void *bias,
                                                        void *out) {
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
     if (c0 >= d.channels) return;
@@ -70,58 +71,78 @@ __global__ void __launch_bounds__(128) dwconv_silu_fwd(ConvDims d, const void *x
     }
 }
 
-// Backward, first pass: dpre (stored in the activation dtype) and the partial weight / bias gradients.
-// part: [batch * row blocks][channels][kMaxK + 1] fp32 (slot kMaxK holds the bias gradient).
+// Backward, first pass: dpre = dout silu'(pre), pre recomputed, stored in the activation dtype.
 template <class T, class W>
-__global__ void __launch_bounds__(128) dwconv_silu_bwd_pre(ConvDims d, const void *x, const void *weight, const void *bias,
-                                                           const void *dout, void *dpre, float *part) {
+__global__ void __launch_bounds__(128, 4) dwconv_silu_bwd_pre(ConvDims d, const void *x, const void *weight, const void *bias,
+                                                              const void *dout, void *dpre) {
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
     if (c0 >= d.channels) return;
     const int b = blockIdx.z, l0 = blockIdx.y * kRows, l1 = min(d.seqlen, l0 + kRows), pad = d.width / 2;
-    float w[kMaxK][8], bv[8], dw[kMaxK][8], db[8];
+    float w[kMaxK][8], bv[8];
 #pragma unroll
     for (int k = 0; k < kMaxK; ++k)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 8; ++j)
             w[k][j] = (k < d.width) ? (sizeof(W) == 4 ? static_cast<const float *>(weight)[(long long)(c0 + j) * d.width + k]
                                                        : static_cast<float>(static_cast<const W *>(weight)[(long long)(c0 + j) * d.width + k]))
                                     : 0.f;
-            dw[k][j] = 0.f;
-        }
     if (d.has_bias) load8<W>(bias, c0, bv);
+    else
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (!d.has_bias) bv[j] = 0.f;
-        db[j] = 0.f;
-    }
+        for (int j = 0; j < 8; ++j) bv[j] = 0.f;
     for (int l = l0; l < l1; ++l) {
-        float acc[8], xw[kMaxK][8];
+        float acc[8], g[8];
+        load8<T>(dout, b * d.osb + l * d.osl + c0, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = bv[j];
 #pragma unroll
         for (int k = 0; k < kMaxK; ++k) {
             const int ls = l + k - pad;
-            const bool in = k < d.width && ls >= 0 && ls < d.seqlen;
-            if (in) load8<T>(x, b * d.xsb + ls * d.xsl + c0, xw[k]);
+            if (k < d.width && ls >= 0 && ls < d.seqlen) {
+                float xv[8];
+                load8<T>(x, b * d.xsb + ls * d.xsl + c0, xv);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (!in) xw[k][j] = 0.f;
-                acc[j] = fmaf(w[k][j], xw[k][j], acc[j]);
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(w[k][j], xv[j], acc[j]);
             }
         }
-        float g[8];
-        load8<T>(dout, b * d.osb + l * d.osl + c0, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float sg = sigmoidn(acc[j]);
             g[j] *= sg * (1.f + acc[j] * (1.f - sg));
-            db[j] += g[j];
         }
-#pragma unroll
-        for (int k = 0; k < kMaxK; ++k)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) dw[k][j] = fmaf(g[j], xw[k][j], dw[k][j]);
         store8<T>(dpre, b * d.osb + l * d.osl + c0, g);
+    }
+}
+
+// Backward, weight / bias gradients from dpre and x.
+// part: [batch * row blocks][channels][kMaxK + 1] fp32 (slot kMaxK holds the bias gradient).
+template <class T>
+__global__ void __launch_bounds__(128, 4) dwconv_silu_bwd_dw(ConvDims d, const void *x, const void *dpre, float *part) {
+    const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
+    if (c0 >= d.channels) return;
+    const int b = blockIdx.z, l0 = blockIdx.y * kRows, l1 = min(d.seqlen, l0 + kRows), pad = d.width / 2;
+    float dw[kMaxK][8], db[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        db[j] = 0.f;
+#pragma unroll
+        for (int k = 0; k < kMaxK; ++k) dw[k][j] = 0.f;
+    }
+    for (int l = l0; l < l1; ++l) {
+        float g[8];
+        load8<T>(dpre, b * d.osb + l * d.osl + c0, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) db[j] += g[j];
+#pragma unroll
+        for (int k = 0; k < kMaxK; ++k) {
+            const int ls = l + k - pad;
+            if (k < d.width && ls >= 0 && ls < d.seqlen) {
+                float xv[8];
+                load8<T>(x, b * d.xsb + ls * d.xsl + c0, xv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dw[k][j] = fmaf(g[j], xv[j], dw[k][j]);
+            }
+        }
     }
     float *p = part + ((long long)(b * gridDim.y + blockIdx.y) * d.channels + c0) * (kMaxK + 1);
 #pragma unroll
@@ -134,7 +155,7 @@ __global__ void __launch_bounds__(128) dwconv_silu_bwd_pre(ConvDims d, const voi
 
 // Backward, second pass: dx = correlation of dpre with the weights.  Same grid as the forward.
 template <class T, class W>
-__global__ void __launch_bounds__(128) dwconv_silu_bwd_dx(ConvDims d, const void *dpre, const void *weight, void *dx) {
+__global__ void __launch_bounds__(128, 4) dwconv_silu_bwd_dx(ConvDims d, const void *dpre, const void *weight, void *dx) {
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
     if (c0 >= d.channels) return;
     const int b = blockIdx.z, l0 = blockIdx.y * kRows, l1 = min(d.seqlen, l0 + kRows), pad = d.width / 2;

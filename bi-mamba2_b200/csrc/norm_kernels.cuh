@@ -147,22 +147,24 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_gated_fwd(NormDims d, const 
     }
 }
 
-// Backward.  dw_part: [gridDim.x][hidden] fp32, one partial row per CTA.  dynamic shared memory: hidden floats.
+// Backward.  dw_part: [gridDim.x][hidden] fp32, one partial row per CTA.
+// dynamic shared memory: kWarps * hidden floats - every warp accumulates its rows' weight gradient in a row of its own
+// (registers would cost 8 * NS per thread and halve the occupancy of a kernel that lives on memory latency).
 //   xhat = u rstd,  dy = dout (silu(z) if the gate follows the norm),  du = rstd (dy w - xhat mean_group(dy w xhat))
 //   gate after the norm:  dx = du,  dz = dout (xhat w) silu'(z);   gate before:  dx = du silu(z),  dz = du x silu'(z)
 //   dw = sum over rows of dy xhat
 template <class T, class W, int NS>
-__global__ void __launch_bounds__(kThreads) rmsnorm_gated_bwd(NormDims d, const void *x, const void *z, const void *weight,
+__global__ void __launch_bounds__(kThreads, 2) rmsnorm_gated_bwd(NormDims d, const void *x, const void *z, const void *weight,
                                                               const void *dout, const float *rstd, void *dx, void *dz,
                                                               float *dw_part) {
     extern __shared__ float red[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsteps = d.hidden / 256, spg = d.group / 256;
-    float dwa[NS][8];
-#pragma unroll
-    for (int k = 0; k < NS; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dwa[k][j] = 0.f;
+    float *mine = red + warp * d.hidden;
+    for (int cidx = lane * 8; cidx < d.hidden; cidx += 256) {
+        *reinterpret_cast<float4 *>(mine + cidx) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4 *>(mine + cidx + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (long long row = (long long)blockIdx.x * kWarps + warp; row < d.rows; row += (long long)gridDim.x * kWarps) {
         // pass 1: per step, the sum of (dy w) xhat; per group its mean
         float dot[NS], mean[NS];
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_gated_bwd(NormDims d, const 
             if (k < nsteps) {
                 const int c0 = k * 256 + lane * 8;
                 const float r = rstd[row * d.ngroups + k / spg];
-                float xv[8], gv[8], wv[8], zz[8], ox[8], oz[8];
+                float xv[8], gv[8], wv[8], zz[8], ox[8], oz[8], dwv[8];
                 load8<T>(x, row * d.sx + c0, xv);
                 load8<T>(dout, row * d.so + c0, gv);
                 load8<W>(weight, c0, wv);
@@ -224,30 +226,29 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_gated_bwd(NormDims d, const 
                     const float du = r * (dy * wv[j] - xhat * mean[k]);
                     ox[j] = before ? du * sl : du;
                     oz[j] = after ? gv[j] * xhat * wv[j] * dsl : (before ? du * xv[j] * dsl : 0.f);
-                    dwa[k][j] = fmaf(dy, xhat, dwa[k][j]);
+                    dwv[j] = dy * xhat;
+                }
+                {
+                    float4 *acc4 = reinterpret_cast<float4 *>(mine + c0);
+                    float4 a0 = acc4[0], a1 = acc4[1];
+                    a0.x += dwv[0]; a0.y += dwv[1]; a0.z += dwv[2]; a0.w += dwv[3];
+                    a1.x += dwv[4]; a1.y += dwv[5]; a1.z += dwv[6]; a1.w += dwv[7];
+                    acc4[0] = a0;
+                    acc4[1] = a1;
                 }
                 store8<T>(dx, row * d.sx + c0, ox);
                 if (d.has_z) store8<T>(dz, row * d.sz + c0, oz);
             }
         }
     }
-    // the eight warps' accumulators are added in warp order through shared memory, then written as this CTA's row
-    for (int wsel = 0; wsel < kWarps; ++wsel) {
-        if (warp == wsel) {
+    // the eight warps' rows are added in warp order and written as this CTA's partial row
+    __syncthreads();
+    for (int cidx = threadIdx.x; cidx < d.hidden; cidx += kThreads) {
+        float v = 0.f;
 #pragma unroll
-            for (int k = 0; k < NS; ++k) {
-                if (k < nsteps) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int cidx = k * 256 + lane * 8 + j;
-                        red[cidx] = (wsel == 0 ? 0.f : red[cidx]) + dwa[k][j];
-                    }
-                }
-            }
-        }
-        __syncthreads();
+        for (int w = 0; w < kWarps; ++w) v += red[w * d.hidden + cidx];
+        dw_part[(long long)blockIdx.x * d.hidden + cidx] = v;
     }
-    for (int cidx = threadIdx.x; cidx < d.hidden; cidx += kThreads) dw_part[(long long)blockIdx.x * d.hidden + cidx] = red[cidx];
 }
 
 // dw[c] = sum over the partial rows, in row order.  grid ceil(hidden / 256).
