@@ -234,15 +234,15 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
                 bool st_done = false;
-                if (!no_tma() && tc::state_tma_ok(d.P, d.N, d.Q)) {
+                if (!no_tma() && (tc::state_tma_ok(d.P, d.N, d.Q) || (!no_ws() && tc::state_grp_ok(d.P, d.N, d.Q, d.R)))) {
                     CUtensorMap mRow, mCol;
                     if (map_bshd(&mRow, a.p.x_dtype, a.B.ptr, a.B.stride_batch, a.B.stride_seq, a.B.stride_head, d.N, d.G, d.L, d.b, d.Q) &&
                         map_bshd(&mCol, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
                         if (!no_ws() && tc::state_grp_ok(d.P, d.N, d.Q, d.R)) {
                             const size_t smem_g = tc::state_grp_smem(d.Q);
-                            const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * (d.N / 128), d.R, sm_count());
+                            const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 0>), smem_g);
-                            BISSD_LAUNCH("tc_chunk_state_grp", tc::state_gemm_grp<T, 0><<<dim3(d.b * d.nc * d.G * ks, d.N / 128), tc::kThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_chunk_state_grp", tc::state_gemm_grp<T, 0><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kThreads, smem_g, s>>>(
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, loc, status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
@@ -405,15 +405,15 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             if (tcp) {
                 const size_t smem = tc::smem_bytes(ntP, 2 * d.Q);
                 bool st_done = false;
-                if (!no_tma() && tc::state_tma_ok(d.P, d.N, d.Q)) {
+                if (!no_tma() && (tc::state_tma_ok(d.P, d.N, d.Q) || (!no_ws() && tc::state_grp_ok(d.P, d.N, d.Q, d.R)))) {
                     CUtensorMap mRow, mCol;
                     if (map_bshd(&mRow, a.p.x_dtype, a.C.ptr, a.C.stride_batch, a.C.stride_seq, a.C.stride_head, d.N, d.G, d.L, d.b, d.Q) &&
                         map_bshd(&mCol, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, d.Q)) {
                         if (!no_ws() && tc::state_grp_ok(d.P, d.N, d.Q, d.R)) {
                             const size_t smem_g = tc::state_grp_smem(d.Q);
-                            const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * (d.N / 128), d.R, sm_count());
+                            const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 1>), smem_g);
-                            BISSD_LAUNCH("tc_dstates_grp", tc::state_gemm_grp<T, 1><<<dim3(d.b * d.nc * d.G * ks, d.N / 128), tc::kThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_dstates_grp", tc::state_gemm_grp<T, 1><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kThreads, smem_g, s>>>(
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);

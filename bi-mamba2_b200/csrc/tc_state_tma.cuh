@@ -131,7 +131,11 @@ struct StateGrpShared {
     uint64_t bar_a, full[2], done[2];
     uint32_t tmem_base;
 };
-inline bool state_grp_ok(int P, int N, int Q, int R) { return P == 64 && N % 128 == 0 && N <= 256 && (Q == 128 || Q == 256) && R >= 2; }
+// dstate 64 runs as half a 128-row tile: the TMA box of the second 64 state columns lies outside the tensor and reads
+// as zeros, the epilogue skips those rows.
+inline bool state_grp_ok(int P, int N, int Q, int R) {
+    return P == 64 && (N == 64 || (N % 128 == 0 && N <= 256)) && (Q == 128 || Q == 256) && R >= 2;
+}
 inline size_t state_grp_smem(int Q) { return 1024 + 2 * (size_t)Q * 128 + 2 * 2 * (size_t)Q * 128 + 2 * 2 * (size_t)Q * 4; }
 inline int state_grp_ksplit(int groups_total, int R, int sms) {      // CTAs per group: fill the SMs once, keep >= 2 heads per CTA
     int ks = 1;
@@ -222,10 +226,12 @@ state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
         tmem_ld32_nowait(tl, v0);
         tmem_ld32_nowait(tl + 32, v1);
         tmem_ld_wait();
+        if (n < N) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[(long long)j * N] = __uint_as_float(v0[j]);
+            for (int j = 0; j < 32; ++j) o[(long long)j * N] = __uint_as_float(v0[j]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[(long long)(32 + j) * N] = __uint_as_float(v1[j]);
+            for (int j = 0; j < 32; ++j) o[(long long)(32 + j) * N] = __uint_as_float(v1[j]);
+        }
         tc_fence_before();
     };
 #pragma unroll 1
