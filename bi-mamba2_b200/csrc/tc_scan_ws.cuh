@@ -57,7 +57,7 @@ struct WsShared {
 
 inline size_t scan_ws_smem(int P, int N, int Q) {
     return 1024 + (size_t)(N / 64) * 16384 + (size_t)(Q / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 + (size_t)Q * 128 +
-           (size_t)kWsMStages * kAStageBytes + 2 * 4 * (size_t)Q * 4;
+           (size_t)kWsMStages * kAStageBytes + 2 * 6 * (size_t)Q * 4;
 }
 inline bool scan_ws_ok(int P, int N, int Q) {
     if (P != 64 || (N != 64 && N != 128) || (Q != 128 && Q != 256)) return false;
@@ -183,7 +183,7 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
                                               int lane, float dfold, WsRing &ring, uint64_t *m_full, uint64_t *m_free,
                                               volatile int *fail) {
     const int cc = bt & 7, r0 = bt >> 3, Q = ns * 64;
-    const float *f2 = tabp, *b2 = f2 + Q, *tf = b2 + Q, *tb = tf + Q;
+    const float *f2 = tabp, *b2 = f2 + Q, *tf = b2 + Q, *tb = tf + Q, *colF = tb + Q, *colB = colF + Q;
     const uint32_t swz = (uint32_t)((cc ^ (r0 & 7)) << 4);      // r & 7 is the same for this thread's four rows
 #pragma unroll 1
     for (int s = 0; s < ns; ++s) {
@@ -193,18 +193,16 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
             return false;
         const uint8_t *slab = smCB + s * 16384;
         uint8_t *stage = smM + ring.mb * kAStageBytes;
-        float tfv[8], tbv[8], col[8];
-        {
-            const float4 a = *reinterpret_cast<const float4 *>(tf + sc), b = *reinterpret_cast<const float4 *>(tf + sc + 4);
-            tfv[0] = a.x; tfv[1] = a.y; tfv[2] = a.z; tfv[3] = a.w; tfv[4] = b.x; tfv[5] = b.y; tfv[6] = b.z; tfv[7] = b.w;
-            const float4 c = *reinterpret_cast<const float4 *>(tb + sc), e = *reinterpret_cast<const float4 *>(tb + sc + 4);
-            tbv[0] = c.x; tbv[1] = c.y; tbv[2] = c.z; tbv[3] = c.w; tbv[4] = e.x; tbv[5] = e.y; tbv[6] = e.z; tbv[7] = e.w;
-        }
-        // a stage has blocks below the diagonal or above it, never both (rows span 128, columns 64)
+        // a stage has blocks below the diagonal or above it, never both (rows span 128, columns 64); the column
+        // factors around the stage's reference index come from the per-tile tables
         const bool below = l0 + 127 > s0 + 63 && !(l0 < s0);
         const float ref = below ? f2[s0 + 63] : b2[s0];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) col[j] = ex2_approx(ref - (below ? tfv[j] : tbv[j]));
+        float col[8];
+        {
+            const float *cp = (below ? colF : colB) + sc;
+            const float4 a = *reinterpret_cast<const float4 *>(cp), b = *reinterpret_cast<const float4 *>(cp + 4);
+            col[0] = a.x; col[1] = a.y; col[2] = a.z; col[3] = a.w; col[4] = b.x; col[5] = b.y; col[6] = b.z; col[7] = b.w;
+        }
         // rows in two halves of 64 (two 32-row blocks of the same kind each), the two blocks interleaved
 #pragma unroll 1
         for (int qp = 0; qp < 2; ++qp) {
@@ -219,6 +217,13 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
                 oa = ws_scale8<T>(rawa, rfa, col);
                 ob = ws_scale8<T>(rawb, rfb, col);
             } else {
+                float tfv[8], tbv[8];
+                {
+                    const float4 a = *reinterpret_cast<const float4 *>(tf + sc), b = *reinterpret_cast<const float4 *>(tf + sc + 4);
+                    tfv[0] = a.x; tfv[1] = a.y; tfv[2] = a.z; tfv[3] = a.w; tfv[4] = b.x; tfv[5] = b.y; tfv[6] = b.z; tfv[7] = b.w;
+                    const float4 c = *reinterpret_cast<const float4 *>(tb + sc), e = *reinterpret_cast<const float4 *>(tb + sc + 4);
+                    tbv[0] = c.x; tbv[1] = c.y; tbv[2] = c.z; tbv[3] = c.w; tbv[4] = e.x; tbv[5] = e.y; tbv[6] = e.z; tbv[7] = e.w;
+                }
                 float va[8], vb[8];
                 unpack8<__nv_bfloat16>(rawa, va);
                 unpack8<__nv_bfloat16>(rawb, vb);
@@ -410,7 +415,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
     uint8_t *smS = smCB + NS * 16384;                         // per K slab: S_f [P x 64] then S_b [P x 64]
     uint8_t *smX = smS + 2 * NSL * P * 128;                   // [Q x 64], MN-major, in NS pieces of 64 rows
     uint8_t *smM = smX + Q * 128;                             // kWsMStages stages [128 x 64]
-    float *tab = reinterpret_cast<float *>(smM + kWsMStages * kAStageBytes);   // 2 x (f2, b2, tf, tb)[Q]
+    float *tab = reinterpret_cast<float *>(smM + kWsMStages * kAStageBytes);   // 2 x (f2, b2, tf, tb, colF, colB)[Q]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int *fail = &sh.fail;
 
@@ -659,6 +664,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
         uint32_t ngrp = 0;
         WsRing ring;
         float pcf = 0.f, pcb = 0.f, pdt = 1.f, pD = 0.f;        // next tile's table inputs for entry bt, and its D
+        float pr1 = 0.f, pr2 = 0.f;                              // ... and the reference values of its column factors
         const bool fold = MODE == 0 && d.has_D && !d.D_hdim;
         auto fetch_tab = [&](const WsIter &w) {
             if (bt < Q) {
@@ -666,19 +672,24 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 pcf = cs_f[base + bt];
                 pcb = cs_b[base + bt];
                 pdt = dt_out[base + bt];
+                pr1 = (MODE == 0 ? cs_f : cs_b)[base + (bt | 63)];      // last column of bt's stage
+                pr2 = (MODE == 0 ? cs_b : cs_f)[base + (bt & ~63)];     // first column of it
             }
             if (fold) pD = D[w.h];
         };
         auto write_tab = [&](int which) {
             if (bt < Q) {
-                float *t = tab + which * 4 * Q;
+                float *t = tab + which * 6 * Q;
                 const float cf = pcf * 1.4426950408889634f, cb_ = pcb * 1.4426950408889634f;
+                const float r1 = pr1 * 1.4426950408889634f, r2 = pr2 * 1.4426950408889634f;
                 if constexpr (MODE == 0) {
                     const float lg = __log2f(pdt);               // -inf for the zero-padded tail: those columns vanish
                     t[bt] = cf;
                     t[Q + bt] = cb_;
                     t[2 * Q + bt] = cf - lg;
                     t[3 * Q + bt] = cb_ - lg;
+                    t[4 * Q + bt] = ex2_approx(r1 - (cf - lg));  // colF[s] = 2^(F[last column of the stage] - TF[s])
+                    t[5 * Q + bt] = ex2_approx(r2 - (cb_ - lg)); // colB[s] = 2^(B[first column of the stage] - TB[s])
                 } else {
                     // transposed tile: below the diagonal 2^(b2[s] - b2[l]), above it 2^(f2[s] - f2[l]); with the
                     // tables negated and swapped the builder's forward formulas produce exactly these
@@ -686,6 +697,8 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                     t[Q + bt] = -cf;
                     t[2 * Q + bt] = -cb_;
                     t[3 * Q + bt] = -cf;
+                    t[4 * Q + bt] = ex2_approx(cb_ - r1);
+                    t[5 * Q + bt] = ex2_approx(cf - r2);
                 }
             }
         };
@@ -708,7 +721,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 cur_grp = grp;
                 if (!ok) break;
             }
-            const float *tb_ = tab + (i & 1) * 4 * Q;
+            const float *tb_ = tab + (i & 1) * 6 * Q;
             ok = ws_build_tile<T>(smCB, smM, tb_, NS, rt * kTileM, bt, lane, dfold, ring, sh.m_full, sh.m_free, fail);
             if (!ok) break;
             if (i + 1 < nt) {
