@@ -242,7 +242,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                             const size_t smem_g = tc::state_grp_smem(d.Q);
                             const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 0>), smem_g);
-                            BISSD_LAUNCH("tc_chunk_state_grp", tc::state_gemm_grp<T, 0><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_chunk_state_grp", tc::state_gemm_grp<T, 0><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s>>>(
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, loc, status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
@@ -413,7 +413,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                             const size_t smem_g = tc::state_grp_smem(d.Q);
                             const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 1>), smem_g);
-                            BISSD_LAUNCH("tc_dstates_grp", tc::state_gemm_grp<T, 1><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_dstates_grp", tc::state_gemm_grp<T, 1><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s>>>(
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);

@@ -64,26 +64,6 @@ inline bool scan_ws_ok(int P, int N, int Q) {
     return scan_ws_smem(P, N, Q) <= 227 * 1024;
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait that also gives up when another role has already failed.  `id` names the wait (role * 10 + barrier);
-// the first wait that runs out leaves its id in the CTA-wide flag, from where it reaches the status word.
-__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile int *fail, int id) {
-    if (mbar_test(bar, parity)) return true;
-    for (uint32_t i = 0; i < kWaitAttempts; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 7) == 7 && *fail) return false;
-    }
-    if (!*fail) *fail = id;
-    return false;
-}
-// the same for a whole warp: every lane polls, the outcome is made uniform so that .aligned instructions stay legal
-__device__ __forceinline__ bool ws_wait_warp(uint64_t *bar, uint32_t parity, volatile int *fail, int id) {
-    return __all_sync(0xffffffffu, ws_wait(bar, parity, fail, id));
-}
-constexpr int kErrWsWait = 0x1000;                              // status word = kErrWsWait + id of the wait that ran out
-
 // Walks (batch, chunk, row tile, head) tiles in the order head fastest; grp numbers the (batch, chunk, row tile,
 // group) sets whose tiles share C and C.B^T.
 struct WsIter {

@@ -128,8 +128,9 @@ state_gemm_tma(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
 // factors are fetched one head ahead.
 // grid (b*nc*G*ks, N/128): ks CTAs share the heads of a group (R % ks == 0).
 struct StateGrpShared {
-    uint64_t bar_a, full[2], done[2];
+    uint64_t bar_a, full[2], scaled[2], done[2], accfree[2], wbar;
     uint32_t tmem_base;
+    int fail;
 };
 // dstate 64 runs as half a 128-row tile: the TMA box of the second 64 state columns lies outside the tensor and reads
 // as zeros, the epilogue skips those rows.
@@ -143,9 +144,13 @@ inline int state_grp_ksplit(int groups_total, int R, int sms) {      // CTAs per
         if (R % k == 0 && (long long)groups_total * k <= sms) ks = k;
     return ks;
 }
+constexpr int kStateGrpThreads = 2 * kThreads + 32;             // eight scaling warps, eight epilogue warps, one controller warp
 
+// Warps 0-7 scale the tiles of head i while warps 8-15 store the accumulator of head i - 1 and lane 0 of warp 16
+// issues every TMA load and every MMA, so that the three never wait behind one another.  Every blocking point is a
+// bounded mbarrier wait (ids 41-47 in the status word).
 template <class T, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(576, 1)
 state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol, int ks,
                const float *dt_out, const float *cs_f, const float *cs_b, float *out, int *status) {
     extern __shared__ uint8_t dyn[];
@@ -162,26 +167,31 @@ state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
     const int n0 = blockIdx.y * 128;
     const int lim = min(Q, d.L - c * Q);
     const int nh = R / ks, h0 = grp * R + k * nh;               // this CTA's heads h0 .. h0 + nh - 1
-    auto load_head = [&](int i) {                               // thread 0: the x / g tile of head i, twice, into stage i & 1
+    volatile int *fail = &sh.fail;
+    auto load_head = [&](int i) {                               // the x / g tile of head i, twice, into stage i & 1
         uint8_t *dst = smX + (i & 1) * stage_bytes;
         mbar_expect_tx(&sh.full[i & 1], (uint32_t)stage_bytes);
         tma_load4(dst, &tmCol, 0, h0 + i, c * Q, b, &sh.full[i & 1]);
         tma_load4(dst + Q * 128, &tmCol, 0, h0 + i, c * Q, b, &sh.full[i & 1]);
     };
     if (warp == 0) tmem_alloc(&sh.tmem_base, 256);
-    if (tid == 0) {
+    if (tid == 2 * kThreads) {                                  // the controller: barriers and the first loads
         mbar_init(&sh.bar_a, 1);
+        mbar_init(&sh.wbar, 8);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.scaled[i], 8);
             mbar_init(&sh.done[i], 1);
+            mbar_init(&sh.accfree[i], 8);
         }
+        sh.fail = 0;
         fence_mbar_init();
         mbar_expect_tx(&sh.bar_a, (uint32_t)(2 * Q * 128));
         for (int j = 0; j < 2; ++j) tma_load4(smA + j * Q * 128, &tmRow, n0 + j * 64, grp, c * Q, b, &sh.bar_a);
         load_head(0);
         if (nh > 1) load_head(1);
     }
-    // row factors: thread l holds position l; inputs of head i + 1 are in flight while head i is worked on
+    // row factors: scaling thread l holds position l; inputs of head i + 1 are in flight while head i is worked on
     float pf_ = 0.f, pb_ = 0.f, pTf = 0.f, pTb = 0.f, pdt = 0.f;
     auto fetch_scale = [&](int i) {
         const long long base = ((long long)(b * d.H + h0 + i) * d.nc + c) * Q;
@@ -206,57 +216,28 @@ state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
             sc[((i & 1) * 2 + 1) * Q + tid] = wb;
         }
     };
-    fetch_scale(0);
-    write_scale(0);
-    if (nh > 1) fetch_scale(1);
+    if (warp < 8) {
+        fetch_scale(0);
+        write_scale(0);
+        if (nh > 1) fetch_scale(1);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
-    const long long per_dir = (long long)d.b * d.nc * d.H * P * N;
-    const int n = n0 + (warp & 3) * 32 + lane, edir = warp >> 2;   // epilogue: row n, the 64 columns of one direction
-    bool ok = true;
-    auto epilogue = [&](int i) {                                // head i: accumulator i & 1 -> out[dir][p][n]
-        ok = mbar_wait(&sh.done[i & 1], (i >> 1) & 1);
-        if (!ok) return;
-        tc_fence_after();
-        float *o = out + edir * per_dir + ((long long)(b * d.nc + c) * d.H + h0 + i) * P * N + n;
-        const uint32_t tl = tmem_lane_base(tmem) + (i & 1) * 128 + edir * 64;
-        uint32_t v0[32], v1[32];                                // both halves requested before either is waited for
-        tmem_ld32_nowait(tl, v0);
-        tmem_ld32_nowait(tl + 32, v1);
-        tmem_ld_wait();
-        if (n < N) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[(long long)j * N] = __uint_as_float(v0[j]);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[(long long)(32 + j) * N] = __uint_as_float(v1[j]);
-        }
-        tc_fence_before();
-    };
-#pragma unroll 1
-    for (int i = 0; i < nh; ++i) {
-        uint8_t *sx = smX + (i & 1) * stage_bytes;
-        ok = mbar_wait(&sh.full[i & 1], (i >> 1) & 1);
-        if (ok) {                                               // rows l of both blocks times their factor, in place
-            const float *wf = sc + ((i & 1) * 2) * Q, *wb = wf + Q;
-            for (int q = tid; q < Q * 8; q += kThreads) {
-                uint4 *pf4 = reinterpret_cast<uint4 *>(sx) + q, *pb4 = reinterpret_cast<uint4 *>(sx + Q * 128) + q;
-                const int l = q >> 3;
-                *pf4 = scale8_packed<T>(*pf4, wf[l]);
-                *pb4 = scale8_packed<T>(*pb4, wb[l]);
-            }
-            fence_async_smem();
-            if (i + 1 < nh) {
-                write_scale(i + 1);
-                if (i + 2 < nh) fetch_scale(i + 2);
-            }
-        }
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (tid == 0) {
-            if (i == 0) ok = mbar_wait(&sh.bar_a, 0);
-            if (ok) {
+    if (warp == 16) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < nh && ok; ++i) {
+                uint8_t *sx = smX + (i & 1) * stage_bytes;
+                if (i >= 1 && i + 1 < nh) {                     // stage (i + 1) & 1 is free once the MMAs of head i - 1 are done
+                    ok = ws_wait(&sh.done[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 44);
+                    if (ok) load_head(i + 1);
+                }
+                ok = ok && ws_wait(&sh.scaled[i & 1], (i >> 1) & 1, fail, 41);
+                if (ok && i >= 2) ok = ws_wait(&sh.accfree[i & 1], ((i >> 1) - 1) & 1, fail, 42);
+                if (ok && i == 0) ok = ws_wait(&sh.bar_a, 0, fail, 43);
+                if (!ok) break;
                 tc_fence_after();
                 const uint32_t idesc = instr_desc(AbFmt<T>::v, true, true, 128);
                 for (int kk = 0; kk < Q / 16; ++kk)
@@ -265,20 +246,66 @@ state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_c
                 umma_commit(&sh.done[i & 1]);
             }
         }
-        if (i >= 1) {
-            epilogue(i - 1);                                    // overlaps the MMAs just issued
-            // stage (i - 1) & 1 is free (its MMAs have completed) and so is accumulator (i - 1) & 1 after the sync below
-            if (ok && tid == 0 && i + 1 < nh) load_head(i + 1);
+    } else if (warp >= 8) {                                     // epilogue: accumulator i & 1 -> out[dir][p][n]
+        const long long per_dir = (long long)d.b * d.nc * d.H * P * N;
+        const int ew = warp - 8;
+        const int n = n0 + (ew & 3) * 32 + lane, edir = ew >> 2;   // row n, the 64 columns of one direction
+        bool ok = true;
+#pragma unroll 1
+        for (int i = 0; i < nh && ok; ++i) {
+            ok = ws_wait_warp(&sh.done[i & 1], (i >> 1) & 1, fail, 45);
+            if (!ok) break;
+            tc_fence_after();
+            float *o = out + edir * per_dir + ((long long)(b * d.nc + c) * d.H + h0 + i) * P * N + n;
+            const uint32_t tl = tmem_lane_base(tmem) + (i & 1) * 128 + edir * 64;
+            uint32_t v0[32], v1[32];                            // both halves requested before either is waited for
+            tmem_ld32_nowait(tl, v0);
+            tmem_ld32_nowait(tl + 32, v1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.accfree[i & 1]);
+            if (n < N) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[(long long)j * N] = __uint_as_float(v0[j]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[(long long)(32 + j) * N] = __uint_as_float(v1[j]);
+            }
         }
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
+    } else {
+        bool ok = true;
+#pragma unroll 1
+        for (int i = 0; i < nh && ok; ++i) {
+            uint8_t *sx = smX + (i & 1) * stage_bytes;
+            ok = ws_wait_warp(&sh.full[i & 1], (i >> 1) & 1, fail, 46);
+            if (!ok) break;
+            const float *wf = sc + ((i & 1) * 2) * Q, *wb = wf + Q;
+            for (int q = tid; q < Q * 8; q += kThreads) {       // rows l of both blocks times their factor, in place
+                uint4 *pf4 = reinterpret_cast<uint4 *>(sx) + q, *pb4 = reinterpret_cast<uint4 *>(sx + Q * 128) + q;
+                const int l = q >> 3;
+                *pf4 = scale8_packed<T>(*pf4, wf[l]);
+                *pb4 = scale8_packed<T>(*pb4, wb[l]);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.scaled[i & 1]);
+            if (i + 1 < nh) {
+                write_scale(i + 1);
+                if (i + 2 < nh) fetch_scale(i + 2);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.wbar);
+            // every scaling warp is done with head i and the factors of head i + 1 are written
+            ok = ws_wait_warp(&sh.wbar, i & 1, fail, 47);
+        }
     }
-    if (ok) epilogue(nh - 1);
-    ok = __syncthreads_and(ok);
-    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (sh.fail && tid == 0) atomicExch(status, kErrWsWait + sh.fail);
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem, 256);
+    }
 }
 
 }  // namespace tc
