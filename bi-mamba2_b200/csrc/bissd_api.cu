@@ -578,6 +578,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     if (!map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128) ||
                         !map_bshd(&mG128, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128))
                         return BISSD_ERR_ALIGN;
+                    if (!no_ws() && tc::dbc_grp_ok(d.P, d.N, d.Q)) {
+                        const size_t smem_g = tc::dbc_grp_smem(d.Q, std::min(d.N, 128));
+                        BISSD_ALLOW(tc::dbc_accum_grp<T>, smem_g);
+                        BISSD_LAUNCH("tc_dbc_accum_grp", tc::dbc_accum_grp<T><<<dim3(d.b * d.nc * d.G * w.nsplit, 1, 2), tc::kDbcGrpThreads, smem_g, s>>>(
+                            d, mEf, mEb, mSf, mSb, mX128, mG128, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
+                    } else
                     BISSD_LAUNCH("tc_dbc_accum_tma", tc::dbc_accum_tma<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_a, s>>>(
                         d, mEf, mEb, mSf, mSb, mX128, mG128, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
                     dbc_done = true;

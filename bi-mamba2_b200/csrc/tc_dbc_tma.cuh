@@ -163,6 +163,179 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// The same sums with one CTA per (batch, chunk, group, 128 state columns) that walks the heads of its group: the CTA
+// owns all Q rows (one 128-column accumulator per 128-row block), so the state tiles E_f / E_b (or S_f / S_b) of a head
+// are fetched once instead of once per row block, and the x / g tile once per direction.  Roles as in
+// state_gemm_grp: warps 0-7 scale the two copies of the left tile in place, lane 0 of warp 8 issues every TMA
+// load and every MMA; two stages of (2 left copies + 2 right tiles).  All heads accumulate in tensor memory, which
+// is read once at the end.  Bounded waits, ids 51-55 in the status word.
+// grid (b*nc*G*nsplit, 1, 2); blockIdx.z: 0 = dB, 1 = dC.
+struct DbcGrpShared {
+    uint64_t full[2], scaled[2], done[2], wbar;
+    uint32_t tmem_base;
+    int fail;
+};
+inline bool dbc_grp_ok(int P, int N, int Q) { return P == 64 && (N == 64 || N % 128 == 0) && (Q == 128 || Q == 256); }
+inline size_t dbc_grp_smem(int Q, int nt) {
+    return 1024 + 2 * (2 * (size_t)Q * 128 + 2 * (size_t)(nt / 64) * 64 * 128) + 2 * 2 * (size_t)Q * 4;
+}
+constexpr int kDbcGrpThreads = kThreads + 32;
+
+template <class T>
+__global__ void __launch_bounds__(kDbcGrpThreads, 1)
+dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_constant__ CUtensorMap tmEb,
+              const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
+              const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG, const float *dt_out,
+              const float *cs_f, const float *cs_b, float *dB_part, float *dC_part, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ DbcGrpShared sh;
+    constexpr int P = 64;
+    const int N = d.N, Q = d.Q, R = d.R;
+    const int nsplit = (N + 127) / 128, nt = min(N, 128), nnb = nt / 64, nrb = Q / 128;
+    const int left_bytes = 2 * Q * 128, right_bytes = 2 * nnb * P * 128, stage_bytes = left_bytes + right_bytes;
+    uint8_t *base_sm = smem_align1024(dyn);                     // per stage: left [dir][Q rows x 128 B], right [dir][nnb][P x 128 B]
+    float *sc = reinterpret_cast<float *>(base_sm + 2 * stage_bytes);   // [2 bufs][2 dirs][Q]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % nsplit, bx = blockIdx.x / nsplit;
+    const int grp = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int which = blockIdx.z;
+    const int lim = min(Q, d.L - c * Q);
+    const int n0 = split * 128, h0 = grp * R;
+    const uint32_t ncols = tmem_cols(nrb * nt);
+    volatile int *fail = &sh.fail;
+    auto load_head = [&](int i) {                               // both copies of the left tile and both state tiles of head i
+        uint8_t *sl = base_sm + (i & 1) * stage_bytes, *sr = sl + left_bytes;
+        const int tile = (b * d.nc + c) * d.H + h0 + i;
+        mbar_expect_tx(&sh.full[i & 1], (uint32_t)stage_bytes);
+        for (int j = 0; j < 2 * nrb; ++j)
+            tma_load4(sl + j * 16384, which ? &tmG : &tmX, 0, h0 + i, c * Q + (j % nrb) * 128, b, &sh.full[i & 1]);
+        for (int dir = 0; dir < 2; ++dir) {
+            const CUtensorMap *m = which ? (dir ? &tmSb : &tmSf) : (dir ? &tmEb : &tmEf);
+            for (int j = 0; j < nnb; ++j) tma_load2(sr + (dir * nnb + j) * P * 128, m, n0 + j * 64, tile * P, &sh.full[i & 1]);
+        }
+    };
+    if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
+    if (tid == kThreads) {                                      // the controller: barriers and the first loads
+        mbar_init(&sh.wbar, 8);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.scaled[i], 8);
+            mbar_init(&sh.done[i], 1);
+        }
+        sh.fail = 0;
+        fence_mbar_init();
+        load_head(0);
+        if (R > 1) load_head(1);
+    }
+    // row factors: scaling thread l holds row l in both directions; the inputs of head i + 2 are in flight while head i is scaled
+    float pf_ = 0.f, pb_ = 0.f, pTf = 0.f, pTb = 0.f, pdt = 0.f;
+    auto fetch_scale = [&](int i) {
+        const long long base = ((long long)(b * d.H + h0 + i) * d.nc + c) * Q;
+        if (tid < lim) {
+            pf_ = cs_f[base + tid];
+            pb_ = cs_b[base + tid];
+            if (!which) {
+                pTf = cs_f[base + Q - 1];
+                pTb = cs_b[base];
+                pdt = dt_out[base + tid];
+            }
+        }
+    };
+    auto write_scale = [&](int i) {
+        if (tid < Q) {
+            float wf = 0.f, wb = 0.f;
+            if (tid < lim) {
+                wf = which ? __expf(pf_) : pdt * __expf(pTf - pf_);
+                wb = which ? __expf(pb_) : pdt * __expf(pTb - pb_);
+            }
+            sc[((i & 1) * 2 + 0) * Q + tid] = wf;
+            sc[((i & 1) * 2 + 1) * Q + tid] = wb;
+        }
+    };
+    if (warp < 8) {
+        fetch_scale(0);
+        write_scale(0);
+        if (R > 1) fetch_scale(1);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    if (warp == 8) {
+        if (lane == 0) {
+            bool ok = true;
+            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, true, nt);
+            for (int i = 0; i < R && ok; ++i) {
+                if (i >= 1 && i + 1 < R) {                      // stage (i + 1) & 1 is free once the MMAs of head i - 1 are done
+                    ok = ws_wait(&sh.done[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 51);
+                    if (ok) load_head(i + 1);
+                }
+                ok = ok && ws_wait(&sh.scaled[i & 1], (i >> 1) & 1, fail, 52);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sl = smem_u32(base_sm + (i & 1) * stage_bytes), sr = sl + left_bytes;
+                for (int rb = 0; rb < nrb; ++rb)
+                    for (int dir = 0; dir < 2; ++dir)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma(tmem + rb * nt, smem_desc(sl + (dir * nrb + rb) * 16384 + kk * 32, 16, 1024),
+                                 smem_desc(sr + dir * nnb * P * 128 + kk * 16 * 128, (uint32_t)P * 128, 1024), idesc,
+                                 (i > 0 || dir > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sh.done[i & 1]);
+            }
+        }
+    } else {
+        bool ok = true;
+#pragma unroll 1
+        for (int i = 0; i < R && ok; ++i) {
+            uint8_t *sl = base_sm + (i & 1) * stage_bytes;
+            ok = ws_wait_warp(&sh.full[i & 1], (i >> 1) & 1, fail, 53);
+            if (!ok) break;
+            const float *w2 = sc + ((i & 1) * 2) * Q;           // [dir][Q], and the left copies are [dir][Q rows]: one index
+            for (int q = tid; q < 2 * Q * 8; q += kThreads) {
+                uint4 *ptr = reinterpret_cast<uint4 *>(sl) + q;
+                *ptr = scale8_packed<T>(*ptr, w2[q >> 3]);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.scaled[i & 1]);
+            if (i + 1 < R) {
+                write_scale(i + 1);
+                if (i + 2 < R) fetch_scale(i + 2);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.wbar);
+            // every scaling warp is done with head i and the factors of head i + 1 are written
+            ok = ws_wait_warp(&sh.wbar, i & 1, fail, 54);
+        }
+        if (ok) ok = ws_wait_warp(&sh.done[(R - 1) & 1], ((R - 1) >> 1) & 1, fail, 55);
+        if (ok) {
+            tc_fence_after();
+            for (int rb = 0; rb < nrb; ++rb) {
+                const int l = rb * 128 + (warp & 3) * 32 + lane;
+                float *part = (which ? dC_part : dB_part) + (((long long)b * d.nc * Q + c * Q + l) * d.G + grp) * N + n0;
+                for (int c0 = (warp >> 2) * 32; c0 < nt; c0 += 64) {
+                    float v[32];
+                    tmem_ld32(tmem_lane_base(tmem) + rb * nt + c0, v);
+                    if (l < lim) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4 *>(part + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (sh.fail && tid == 0) atomicExch(status, kErrWsWait + sh.fail);
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem, ncols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // "prev" decay terms:  pf[l] = e^{cs_f[l]} sum_p g[l,p] (C[l,:].S_f[p,:]),  pb[l] likewise with S_b / cs_b  - the row sums
 // the reference takes inside _chunk_scan_bwd_dc_kernel (src/ssd/bi/ssd_chunk_scan.py:598-623).  C and both entering
 // states arrive by TMA; nothing is staged by threads.   grid (b*nc*H, Q/128).
