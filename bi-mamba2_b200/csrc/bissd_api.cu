@@ -570,14 +570,22 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
                     tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P)) {
                     const size_t smem_p = tc::prev_tma_smem(d.P, d.N), smem_a = tc::dbc_tma_smem(d.P, std::min(d.N, 128));
-                    BISSD_ALLOW(tc::prev_terms_tma<T>, smem_p);
-                    BISSD_LAUNCH("tc_prev_terms_tma", tc::prev_terms_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_p, s>>>(
-                        d, mC, mSf, mSb, gv, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
-                    BISSD_ALLOW(tc::dbc_accum_tma<T>, smem_a);
                     CUtensorMap mX128, mG128;
                     if (!map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128) ||
                         !map_bshd(&mG128, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128))
                         return BISSD_ERR_ALIGN;
+                    if (!no_ws() && tc::prev_grp_ok(d.P, d.N, d.Q, d.R)) {
+                        const size_t smem_g = tc::prev_grp_smem(d.N, d.Q);
+                        const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G, d.R, sm_count());
+                        BISSD_ALLOW(tc::prev_terms_grp<T>, smem_g);
+                        BISSD_LAUNCH("tc_prev_terms_grp", tc::prev_terms_grp<T><<<dim3(d.b * d.nc * d.G * ks), tc::kPrevGrpThreads, smem_g, s>>>(
+                            d, mC, mSf, mSb, mG128, ks, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
+                    } else {
+                        BISSD_ALLOW(tc::prev_terms_tma<T>, smem_p);
+                        BISSD_LAUNCH("tc_prev_terms_tma", tc::prev_terms_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_p, s>>>(
+                            d, mC, mSf, mSb, gv, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
+                    }
+                    BISSD_ALLOW(tc::dbc_accum_tma<T>, smem_a);
                     if (!no_ws() && tc::dbc_grp_ok(d.P, d.N, d.Q)) {
                         const size_t smem_g = tc::dbc_grp_smem(d.Q, std::min(d.N, 128));
                         BISSD_ALLOW(tc::dbc_accum_grp<T>, smem_g);

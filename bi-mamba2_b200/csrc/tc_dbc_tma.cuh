@@ -444,5 +444,183 @@ prev_terms_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     if (warp == 0) tmem_dealloc(tmem, ncols);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same row sums with one CTA per (batch, chunk, group[, head range]) that keeps the C tile of all Q rows resident
+// and walks its heads: per head both entering states (one [2P x dstate] K-major tile, so one N = 2P product per
+// 128-row block) and the g tile arrive by TMA into two-deep rings; warps 0-7 read the products out of double-buffered
+// tensor memory and dot them with their g row while lane 0 of warp 8 issues the loads and MMAs of the next head.
+// Bounded waits, ids 61-66 in the status word.   grid (b*nc*G*ks).
+struct PrevGrpShared {
+    uint64_t bar_c, full_s[2], full_g[2], done[2], accfree[2], gfree[2];
+    uint32_t tmem_base;
+    int fail;
+};
+inline bool prev_grp_ok(int P, int N, int Q, int R) { return P == 64 && (N == 64 || N == 128) && (Q == 128 || Q == 256) && R >= 2; }
+inline size_t prev_grp_smem(int N, int Q) {
+    return 1024 + (size_t)(Q / 128) * (N / 64) * 16384 + 2 * 2 * (size_t)(N / 64) * 8192 + 2 * (size_t)(Q / 128) * 16384;
+}
+constexpr int kPrevGrpThreads = kThreads + 32;
+
+template <class T>
+__global__ void __launch_bounds__(kPrevGrpThreads, 1)
+prev_terms_grp(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmSf,
+               const __grid_constant__ CUtensorMap tmSb, const __grid_constant__ CUtensorMap tmG, int ks, const float *cs_f,
+               const float *cs_b, float *pf, float *pb, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ PrevGrpShared sh;
+    constexpr int P = 64;
+    const int N = d.N, Q = d.Q, R = d.R;
+    const int nsl = N / 64, nrb = Q / 128;
+    const int c_bytes = nrb * nsl * 16384, s_bytes = 2 * nsl * 8192, g_bytes = nrb * 16384;
+    uint8_t *smC = smem_align1024(dyn);                         // [row block][slab of 64 n][128 rows x 128 B]
+    uint8_t *smS = smC + c_bytes;                               // 2 stages x [slab][f | b][64 p x 128 B]
+    uint8_t *smG = smS + 2 * s_bytes;                           // 2 stages x [row block][128 rows x 128 B]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int k = blockIdx.x % ks, bx = blockIdx.x / ks;
+    const int grp = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int lim = min(Q, d.L - c * Q);
+    const int nh = R / ks, h0 = grp * R + k * nh;
+    volatile int *fail = &sh.fail;
+    auto load_s = [&](int i) {
+        uint8_t *dst = smS + (i & 1) * s_bytes;
+        const int tile = (b * d.nc + c) * d.H + h0 + i;
+        mbar_expect_tx(&sh.full_s[i & 1], (uint32_t)s_bytes);
+        for (int j = 0; j < nsl; ++j) {
+            tma_load2(dst + (j * 2 + 0) * 8192, &tmSf, j * 64, tile * P, &sh.full_s[i & 1]);
+            tma_load2(dst + (j * 2 + 1) * 8192, &tmSb, j * 64, tile * P, &sh.full_s[i & 1]);
+        }
+    };
+    auto load_g = [&](int i) {
+        uint8_t *dst = smG + (i & 1) * g_bytes;
+        mbar_expect_tx(&sh.full_g[i & 1], (uint32_t)g_bytes);
+        for (int rb = 0; rb < nrb; ++rb) tma_load4(dst + rb * 16384, &tmG, 0, h0 + i, c * Q + rb * 128, b, &sh.full_g[i & 1]);
+    };
+    const uint32_t ncols = 2 * nrb * 128;                       // two accumulator sets of nrb x 128 columns
+    if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
+    if (tid == kThreads) {                                      // the controller: barriers and the first loads
+        mbar_init(&sh.bar_c, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.full_s[i], 1);
+            mbar_init(&sh.full_g[i], 1);
+            mbar_init(&sh.done[i], 1);
+            mbar_init(&sh.accfree[i], 8);
+            mbar_init(&sh.gfree[i], 8);
+        }
+        sh.fail = 0;
+        fence_mbar_init();
+        mbar_expect_tx(&sh.bar_c, (uint32_t)c_bytes);
+        for (int rb = 0; rb < nrb; ++rb)
+            for (int j = 0; j < nsl; ++j)
+                tma_load4(smC + (rb * nsl + j) * 16384, &tmC, j * 64, grp, c * Q + rb * 128, b, &sh.bar_c);
+        load_s(0);
+        load_g(0);
+        if (nh > 1) {
+            load_s(1);
+            load_g(1);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    if (warp == 8) {
+        if (lane == 0) {
+            bool ok = ws_wait(&sh.bar_c, 0, fail, 61);
+            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, 2 * P);
+            for (int i = 0; i < nh && ok; ++i) {
+                ok = ws_wait(&sh.full_s[i & 1], (i >> 1) & 1, fail, 62);
+                if (ok && i >= 2) ok = ws_wait(&sh.accfree[i & 1], ((i >> 1) - 1) & 1, fail, 63);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t ss = smem_u32(smS + (i & 1) * s_bytes);
+                for (int rb = 0; rb < nrb; ++rb)
+                    for (int j = 0; j < nsl; ++j)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma(tmem + ((i & 1) * nrb + rb) * 128, smem_desc(smem_u32(smC + (rb * nsl + j) * 16384) + kk * 32, 16, 1024),
+                                 smem_desc(ss + j * 16384 + kk * 32, 16, 1024), idesc, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sh.done[i & 1]);
+                if (i >= 1 && i + 1 < nh) {                     // the rings of head i - 1 are refilled as they drain
+                    ok = ws_wait(&sh.done[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 64);
+                    if (ok) load_s(i + 1);
+                    ok = ok && ws_wait(&sh.gfree[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 65);
+                    if (ok) load_g(i + 1);
+                }
+            }
+        }
+    } else {
+        const int quad = warp & 3, dir = warp >> 2;             // rows quad * 32 + lane of every row block, one direction
+        const float *cs = dir ? cs_b : cs_f;
+        float *po = dir ? pb : pf;
+        bool ok = true;
+        float ecs[2] = {0.f, 0.f}, ecs_next[2] = {0.f, 0.f};
+        auto fetch_cs = [&](int i, float (&e)[2]) {
+            const long long base = ((long long)(b * d.H + h0 + i) * d.nc + c) * Q;
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb) {
+                const int l = rb * 128 + quad * 32 + lane;
+                e[rb] = (rb < nrb && l < lim) ? cs[base + l] : 0.f;
+            }
+        };
+        fetch_cs(0, ecs);
+#pragma unroll 1
+        for (int i = 0; i < nh && ok; ++i) {
+            if (i + 1 < nh) fetch_cs(i + 1, ecs_next);
+            ok = ws_wait_warp(&sh.done[i & 1], (i >> 1) & 1, fail, 66) && ws_wait_warp(&sh.full_g[i & 1], (i >> 1) & 1, fail, 66);
+            if (!ok) break;
+            tc_fence_after();
+            const long long base = ((long long)(b * d.H + h0 + i) * d.nc + c) * Q;
+            float sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb) {
+                if (rb < nrb) {
+                    const int r = quad * 32 + lane;
+                    uint32_t v0[32], v1[32];
+                    const uint32_t tl = tmem_lane_base(tmem) + ((i & 1) * nrb + rb) * 128 + dir * 64;
+                    tmem_ld32_nowait(tl, v0);
+                    tmem_ld32_nowait(tl + 32, v1);
+                    const uint8_t *grow = smG + (i & 1) * g_bytes + rb * 16384 + r * 128;
+                    uint4 gq[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) gq[q] = *reinterpret_cast<const uint4 *>(grow + ((q ^ (r & 7)) << 4));
+                    tmem_ld_wait();
+                    float acc = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        float gv[8];
+                        unpack8<T>(gq[q], gv);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int col = q * 8 + e;
+                            acc = fmaf(__uint_as_float(col < 32 ? v0[col] : v1[col - 32]), gv[e], acc);
+                        }
+                    }
+                    sum[rb] = acc;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&sh.accfree[i & 1]);
+                mbar_arrive(&sh.gfree[i & 1]);
+            }
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb) {
+                const int l = rb * 128 + quad * 32 + lane;
+                if (rb < nrb) po[base + l] = (l < lim) ? __expf(ecs[rb]) * sum[rb] : 0.f;
+            }
+            ecs[0] = ecs_next[0];
+            ecs[1] = ecs_next[1];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (sh.fail && tid == 0) atomicExch(status, kErrWsWait + sh.fail);
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem, ncols);
+    }
+}
+
 }  // namespace tc
 }  // namespace bissd
