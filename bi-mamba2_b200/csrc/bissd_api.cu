@@ -615,6 +615,8 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             F(w.nf), F(w.nb), F(w.pf), F(w.pb)));
     }
     bool intra_tc = false;
+    bool bmm_tma = false;                                        // dCB is then a 16-bit array read by TMA
+    CUtensorMap mBb, mCb, mDm, mDk;
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
             intra_tc = true;
@@ -628,10 +630,19 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                 const unsigned long long sG4[3] = {(unsigned long long)gv.sh * 2, (unsigned long long)gv.sl * 2, (unsigned long long)gv.sb * 2};
                 const unsigned bx4[4] = {64, 1, 128, 1};
                 if (tc::make_map4(&mX, a.p.x_dtype, a.x.ptr, dX4, sX4, bx4) && tc::make_map4(&mG, a.p.x_dtype, gv.ptr, dX4, sG4, bx4)) {
+                    // the product with B / C reads dCB by TMA from a 16-bit copy when it can
+                    const unsigned long long dBC4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                    const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
+                    const unsigned long long sC4b[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+                    const unsigned long long dcb_rows = (unsigned long long)d.b * d.nc * d.G * d.Q;
+                    bmm_tma = !no_ws() && tc::bmm_bwd_tma_ok(d.N, d.Q) &&
+                              tc::make_map4(&mBb, a.p.x_dtype, a.B.ptr, dBC4, sB4, bx4) && tc::make_map4(&mCb, a.p.x_dtype, a.C.ptr, dBC4, sC4b, bx4) &&
+                              tc::make_map2(&mDm, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, d.Q) &&
+                              tc::make_map2(&mDk, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, 128);
                     const size_t smem_t = tc::dcb_tma_smem(d.P, d.Q);
                     BISSD_ALLOW(tc::dcb_tma<T>, smem_t);
                     BISSD_LAUNCH("tc_dcb_tma", tc::dcb_tma<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_t, s>>>(
-                        d, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
+                        d, mG, mX, a.dt_out, a.cs_f, a.cs_b, bmm_tma ? nullptr : F(w.dCB), bmm_tma ? static_cast<void *>(F(w.dCB)) : nullptr, status));
                     dcb_done = true;
                 }
             }
@@ -688,7 +699,13 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     }
     bool bmm_tc = false;
     if constexpr (TcKernels<T>::available) {
-        if (tcp) {
+        if (tcp && bmm_tma) {
+            bmm_tc = true;
+            const size_t smem_b = tc::bmm_bwd_tma_smem(d.Q);
+            BISSD_ALLOW(tc::bmm_bwd_tma<T>, smem_b);
+            BISSD_LAUNCH("tc_bmm_bwd_tma", tc::bmm_bwd_tma<T><<<dim3(d.b * d.nc * d.G * 2, d.Q / 128, d.N / 64), tc::kThreads, smem_b, s>>>(
+                d, mDm, mDk, mBb, mCb, F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC, status));
+        } else if (tcp) {
             bmm_tc = true;
             const size_t smem_n = tc::smem_bytes(ntN, 0);
             BISSD_ALLOW(tc::bmm_bwd<T>, smem_n);

@@ -24,7 +24,7 @@ inline size_t dcb_tma_smem(int P, int Q) { return 1024 + 3 * 2 * (size_t)(P / 64
 template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
-        const float *cs_f, const float *cs_b, float *dCB, int *status) {
+        const float *cs_f, const float *cs_b, float *dCB, void *dCB16, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ DcbShared sh;
     const int P = d.P, Q = d.Q, R = d.R;
@@ -153,7 +153,21 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
         if (!ok) break;
     }
     if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
-    if (ok && l < Q) {
+    if (ok && l < Q && dCB16) {                                 // the rounded copy bmm_bwd_tma multiplies with; zero outside the sequence
+        const int lim = min(Q, d.L - c * Q);
+        T *out = static_cast<T *>(dCB16) + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            const int c0 = half * 32 + (ch >> 1) * 64 + (ch & 1) * 16;
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = (l < lim && s0 + c0 + j + i < lim) ? acc[ch * 16 + j + i] : 0.f;
+                *reinterpret_cast<uint4 *>(out + c0 + j) = pack8<T>(o);
+            }
+        }
+    } else if (ok && l < Q) {
         float *out = dCB + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -167,6 +181,97 @@ dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dB[s,n] = sum_l dCB[l,s] C[l,n] + dB_part[s,n];  dC[l,n] = sum_s dCB[l,s] B[s,n] + dC_part[l,n]   (see simt::bmm_bwd),
+// from the 16-bit copy of dCB that dcb_tma writes (the reference's kernel rounds dCB to the input type as well).
+// One shot per CTA: 128 output rows x 64 state columns; both operands by TMA - dCB once as [l x 128 s] (MN-major,
+// for dB) or as [128 l x s] (K-major, for dC), B or C as [Q rows x 64 n] (MN-major) - then Q/16 MMAs and the
+// epilogue that adds the per-group partial sums of dbc_accum.   grid (b*nc*G*2, Q/128, N/64); two CTAs per SM.
+inline bool bmm_bwd_tma_ok(int N, int Q) { return N % 64 == 0 && (Q == 128 || Q == 256); }
+inline size_t bmm_bwd_tma_smem(int Q) { return 1024 + (size_t)Q * 256 + (size_t)Q * 128; }
+
+template <class T>
+__global__ void __launch_bounds__(kThreads, 2)
+bmm_bwd_tma(Dims d, const __grid_constant__ CUtensorMap tmDm, const __grid_constant__ CUtensorMap tmDk,
+            const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const float *dB_part,
+            const float *dC_part, int part_heads, void *dB, void *dC, int *status) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ uint64_t bar_in, bar_done;
+    __shared__ uint32_t tmem_slot;
+    const int N = d.N, Q = d.Q;
+    uint8_t *smA = smem_align1024(dyn), *smB = smA + Q * 256;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int which = blockIdx.x & 1, bx = blockIdx.x >> 1;
+    const int g = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
+    const int lim = min(Q, d.L - c * Q);
+    const int r0 = blockIdx.y * kTileM, n0 = blockIdx.z * 64;
+    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    if (tid == 32) {                                            // barriers and loads by the same thread, before the sync
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_done, 1);
+        fence_mbar_init();
+        const int row0 = ((b * d.nc + c) * d.G + g) * Q;        // first row of this group's dCB
+        mbar_expect_tx(&bar_in, (uint32_t)(Q * 256 + Q * 128));
+        if (which == 0)
+            for (int j = 0; j < 2; ++j) tma_load2(smA + j * Q * 128, &tmDm, r0 + j * 64, row0, &bar_in);
+        else
+            for (int j = 0; j < Q / 64; ++j) tma_load2(smA + j * 16384, &tmDk, j * 64, row0 + r0, &bar_in);
+        for (int rb = 0; rb < Q / 128; ++rb) tma_load4(smB + rb * 16384, which ? &tmB : &tmC, n0, g, c * Q + rb * 128, b, &bar_in);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool ok = true;
+    if (tid == 0) {
+        ok = mbar_wait(&bar_in, 0);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t idesc = instr_desc(AbFmt<T>::v, which == 0, true, 64);
+            for (int kk = 0; kk < Q / 16; ++kk) {
+                const uint64_t da = which == 0 ? smem_desc(smem_u32(smA) + kk * 2048, (uint32_t)Q * 128, 1024)
+                                               : smem_desc(smem_u32(smA) + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                umma(tmem, da, smem_desc(smem_u32(smB) + kk * 2048, (uint32_t)Q * 128, 1024), idesc, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&bar_done);
+        }
+    }
+    const int row = r0 + (warp & 3) * 32 + lane, c0 = (warp >> 2) * 32;
+    const int rp = part_heads / d.G;
+    const float *part = (which ? dC_part : dB_part) + (((long long)b * d.nc * Q + c * Q + row) * part_heads + g * rp) * N + n0 + c0;
+    float o[32];                                                // the partial sums are on their way while the MMAs run
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = 0.f;
+    if (row < lim)
+        for (int q = 0; q < rp; ++q)
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 t = *reinterpret_cast<const float4 *>(part + (long long)q * N + j);
+                o[j] += t.x, o[j + 1] += t.y, o[j + 2] += t.z, o[j + 3] += t.w;
+            }
+    if (ok) ok = mbar_wait(&bar_done, 0);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
+    if (ok) {
+        float v[32];
+        tmem_ld32(tmem_lane_base(tmem) + c0, v);
+        if (row < lim) {
+            T *out = static_cast<T *>(which ? dC : dB) + (((long long)b * d.L + c * Q + row) * d.G + g) * N + n0 + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t[i] = v[j + i] + o[j + i];
+                *reinterpret_cast<uint4 *>(out + j) = pack8<T>(t);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
 }  // namespace tc
