@@ -165,19 +165,20 @@ dbc_accum_tma(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
 // ---------------------------------------------------------------------------------------------------------
 // The same sums with one CTA per (batch, chunk, group, 128 state columns) that walks the heads of its group: the CTA
 // owns all Q rows (one 128-column accumulator per 128-row block), so the state tiles E_f / E_b (or S_f / S_b) of a head
-// are fetched once instead of once per row block, and the x / g tile once per direction.  Roles as in
-// state_gemm_grp: warps 0-7 scale the two copies of the left tile in place, lane 0 of warp 8 issues every TMA
-// load and every MMA; two stages of (2 left copies + 2 right tiles).  All heads accumulate in tensor memory, which
-// is read once at the end.  Bounded waits, ids 51-55 in the status word.
+// are fetched once instead of once per row block, and the x / g tile once.  Roles as in state_gemm_grp: warps 0-7
+// turn the left tile as it landed into its two row-scaled copies (one buffer: the copies of head i + 1 are written
+// once the MMAs of head i are done), lane 0 of warp 8 issues every TMA load and every MMA; two stages of (left
+// tile + 2 right tiles).  All heads accumulate in tensor memory, which is read once at the end.  Bounded waits,
+// ids 51-56 in the status word.
 // grid (b*nc*G*nsplit, 1, 2); blockIdx.z: 0 = dB, 1 = dC.
 struct DbcGrpShared {
-    uint64_t full[2], scaled[2], done[2], wbar;
+    uint64_t full[2], scaled, done[2], wbar;
     uint32_t tmem_base;
     int fail;
 };
 inline bool dbc_grp_ok(int P, int N, int Q) { return P == 64 && (N == 64 || N % 128 == 0) && (Q == 128 || Q == 256); }
 inline size_t dbc_grp_smem(int Q, int nt) {
-    return 1024 + 2 * (2 * (size_t)Q * 128 + 2 * (size_t)(nt / 64) * 64 * 128) + 2 * 2 * (size_t)Q * 4;
+    return 1024 + 2 * ((size_t)Q * 128 + 2 * (size_t)(nt / 64) * 64 * 128) + 2 * (size_t)Q * 128 + 2 * 2 * (size_t)Q * 4;
 }
 constexpr int kDbcGrpThreads = kThreads + 32;
 
@@ -192,9 +193,10 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
     constexpr int P = 64;
     const int N = d.N, Q = d.Q, R = d.R;
     const int nsplit = (N + 127) / 128, nt = min(N, 128), nnb = nt / 64, nrb = Q / 128;
-    const int left_bytes = 2 * Q * 128, right_bytes = 2 * nnb * P * 128, stage_bytes = left_bytes + right_bytes;
-    uint8_t *base_sm = smem_align1024(dyn);                     // per stage: left [dir][Q rows x 128 B], right [dir][nnb][P x 128 B]
-    float *sc = reinterpret_cast<float *>(base_sm + 2 * stage_bytes);   // [2 bufs][2 dirs][Q]
+    const int left_bytes = Q * 128, right_bytes = 2 * nnb * P * 128, stage_bytes = left_bytes + right_bytes;
+    uint8_t *base_sm = smem_align1024(dyn);                     // per stage: left [Q rows x 128 B], right [dir][nnb][P x 128 B]
+    uint8_t *smScaled = base_sm + 2 * stage_bytes;              // [dir][Q rows x 128 B]
+    float *sc = reinterpret_cast<float *>(smScaled + 2 * left_bytes);   // [2 bufs][2 dirs][Q]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x % nsplit, bx = blockIdx.x / nsplit;
     const int grp = bx % d.G, c = (bx / d.G) % d.nc, b = bx / (d.G * d.nc);
@@ -203,12 +205,12 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
     const int n0 = split * 128, h0 = grp * R;
     const uint32_t ncols = tmem_cols(nrb * nt);
     volatile int *fail = &sh.fail;
-    auto load_head = [&](int i) {                               // both copies of the left tile and both state tiles of head i
+    auto load_head = [&](int i) {                               // the left tile and both state tiles of head i
         uint8_t *sl = base_sm + (i & 1) * stage_bytes, *sr = sl + left_bytes;
         const int tile = (b * d.nc + c) * d.H + h0 + i;
         mbar_expect_tx(&sh.full[i & 1], (uint32_t)stage_bytes);
-        for (int j = 0; j < 2 * nrb; ++j)
-            tma_load4(sl + j * 16384, which ? &tmG : &tmX, 0, h0 + i, c * Q + (j % nrb) * 128, b, &sh.full[i & 1]);
+        for (int j = 0; j < nrb; ++j)
+            tma_load4(sl + j * 16384, which ? &tmG : &tmX, 0, h0 + i, c * Q + j * 128, b, &sh.full[i & 1]);
         for (int dir = 0; dir < 2; ++dir) {
             const CUtensorMap *m = which ? (dir ? &tmSb : &tmSf) : (dir ? &tmEb : &tmEf);
             for (int j = 0; j < nnb; ++j) tma_load2(sr + (dir * nnb + j) * P * 128, m, n0 + j * 64, tile * P, &sh.full[i & 1]);
@@ -217,9 +219,9 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
     if (warp == 0) tmem_alloc(&sh.tmem_base, ncols);
     if (tid == kThreads) {                                      // the controller: barriers and the first loads
         mbar_init(&sh.wbar, 8);
+        mbar_init(&sh.scaled, 8);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.full[i], 1);
-            mbar_init(&sh.scaled[i], 8);
             mbar_init(&sh.done[i], 1);
         }
         sh.fail = 0;
@@ -270,10 +272,10 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
                     ok = ws_wait(&sh.done[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 51);
                     if (ok) load_head(i + 1);
                 }
-                ok = ok && ws_wait(&sh.scaled[i & 1], (i >> 1) & 1, fail, 52);
+                ok = ok && ws_wait(&sh.scaled, i & 1, fail, 52);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sl = smem_u32(base_sm + (i & 1) * stage_bytes), sr = sl + left_bytes;
+                const uint32_t sl = smem_u32(smScaled), sr = smem_u32(base_sm + (i & 1) * stage_bytes) + left_bytes;
                 for (int rb = 0; rb < nrb; ++rb)
                     for (int dir = 0; dir < 2; ++dir)
 #pragma unroll
@@ -290,15 +292,18 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
         for (int i = 0; i < R && ok; ++i) {
             uint8_t *sl = base_sm + (i & 1) * stage_bytes;
             ok = ws_wait_warp(&sh.full[i & 1], (i >> 1) & 1, fail, 53);
+            // the scaled copies of head i - 1 have been read by its MMAs
+            if (ok && i >= 1) ok = ws_wait_warp(&sh.done[(i - 1) & 1], ((i - 1) >> 1) & 1, fail, 56);
             if (!ok) break;
-            const float *w2 = sc + ((i & 1) * 2) * Q;           // [dir][Q], and the left copies are [dir][Q rows]: one index
-            for (int q = tid; q < 2 * Q * 8; q += kThreads) {
-                uint4 *ptr = reinterpret_cast<uint4 *>(sl) + q;
-                *ptr = scale8_packed<T>(*ptr, w2[q >> 3]);
+            const float *wf = sc + ((i & 1) * 2) * Q, *wb = wf + Q;
+            for (int q = tid; q < Q * 8; q += kThreads) {
+                const uint4 raw = reinterpret_cast<const uint4 *>(sl)[q];
+                reinterpret_cast<uint4 *>(smScaled)[q] = scale8_packed<T>(raw, wf[q >> 3]);
+                reinterpret_cast<uint4 *>(smScaled + left_bytes)[q] = scale8_packed<T>(raw, wb[q >> 3]);
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.scaled[i & 1]);
+            if (lane == 0) mbar_arrive(&sh.scaled);
             if (i + 1 < R) {
                 write_scale(i + 1);
                 if (i + 2 < R) fetch_scale(i + 2);
