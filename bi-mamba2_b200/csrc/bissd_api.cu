@@ -16,6 +16,7 @@
 #include "tc_kernels.cuh"
 #include "tc_dbc_tma.cuh"
 #include "tc_dcb_tma.cuh"
+#include "tc_bmm_tma.cuh"
 #include "tc_dx_tma.cuh"
 #include "tc_scan_tma.cuh"
 #include "tc_scan_ws.cuh"
@@ -71,6 +72,15 @@ struct TraceScope {
         int rc_ = note_cuda(cudaGetLastError(), name);            \
         if (rc_ != BISSD_OK) return rc_;                          \
     } while (0)
+
+// C and B as (dstate, group, seqlen, batch) tensors read in boxes of 64 state columns x 128 rows
+template <class Args> static bool make_cb_maps(const Args &a, const Dims &d, CUtensorMap *mC, CUtensorMap *mB) {
+    const unsigned long long dims[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+    const unsigned long long sC[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+    const unsigned long long sB[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
+    const unsigned box[4] = {64, 1, 128, 1};
+    return tc::make_map4(mC, a.p.x_dtype, a.C.ptr, dims, sC, box) && tc::make_map4(mB, a.p.x_dtype, a.B.ptr, dims, sB, box);
+}
 
 static int make_dims(const bissd_problem &p, Dims *d) {
     if (p.batch <= 0 || p.seqlen <= 0 || p.nheads <= 0 || p.headdim <= 0 || p.ngroups <= 0 || p.dstate <= 0)
@@ -288,6 +298,13 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                 BISSD_ALLOW(tc::bmm_cb<T>, smem_cb);
                 const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
                 __nv_bfloat16 *CB16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cb16);
+                CUtensorMap mCc, mBc;
+                if (ws_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
+                    const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
+                    BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
+                    BISSD_LAUNCH("tc_bmm_cb_tma", tc::bmm_cb_tma<T><<<dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s>>>(
+                        d, mCc, mBc, CB16, nullptr, nullptr, status));
+                } else
                 BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
                     d, Cm, Bm, ws_path ? nullptr : CB, nullptr, ws_path ? CB16 : nullptr, nullptr, nullptr, status));
                 bool tma_done = false;
@@ -468,6 +485,13 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
             const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
             __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt16);
+            CUtensorMap mCc, mBc;
+            if (ws_path && sums_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
+                const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
+                BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
+                BISSD_LAUNCH("tc_bmm_cb_tma", tc::bmm_cb_tma<T><<<dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s>>>(
+                    d, mCc, mBc, nullptr, CBt16, F(w.cbs), status));
+            } else
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
                 d, Cm, Bm, (sums_path && ws_path) ? nullptr : F(w.cb), ws_path ? nullptr : F(w.cbt), nullptr,
                 ws_path ? CBt16 : nullptr, sums_path ? F(w.cbs) : nullptr, status));   // only the copies that will be read
