@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -64,6 +65,28 @@ struct TraceScope {
 };
 
 // Launch `...` (a full kernel<<<>>>() expression) on stream `s`, count it, bracket it with events when tracing.
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor drains and
+// waits for it in pdl_begin().  Only kernels that open with pdl_begin() go through here.  BISSD_NO_PDL=1 turns
+// the attribute off (plain stream order).
+static bool no_pdl() {
+    static const bool v = std::getenv("BISSD_NO_PDL") != nullptr;
+    return v;
+}
+template <class... Exp, class... Act>
+static cudaError_t launch_pdl(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Act &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl() ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
+}
+
 #define BISSD_LAUNCH(name, ...)                                   \
     do {                                                          \
         TraceScope ts_(name, s);                                  \
@@ -237,7 +260,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
     if (a.phases & BISSD_PHASE_LOCAL) {
         int rc = note_cuda(cudaMemsetAsync(ws, 0, kWsHeader, s), "cudaMemsetAsync");
         if (rc != BISSD_OK) return rc;
-        BISSD_LAUNCH("cumsum_fwd", simt::cumsum_fwd<<<d.b * d.nc * d.H, 256, 0, s>>>(
+        BISSD_LAUNCH("cumsum_fwd", launch_pdl(simt::cumsum_fwd, d.b * d.nc * d.H, 256, 0, s, 
             d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
             a.cs_f, a.cs_b));
         if constexpr (TcKernels<T>::available) {
@@ -252,7 +275,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                             const size_t smem_g = tc::state_grp_smem(d.Q);
                             const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 0>), smem_g);
-                            BISSD_LAUNCH("tc_chunk_state_grp", tc::state_gemm_grp<T, 0><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_chunk_state_grp", launch_pdl(tc::state_gemm_grp<T, 0>, dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s, 
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, loc, status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
@@ -284,7 +307,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
     const bool need_pass = (a.phases & BISSD_PHASE_LOCAL) || (a.init_f || a.init_b);
     if (need_pass) {
         if ((d.P * d.N) % 4 == 0) {
-            BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd4<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, 4 * simt::TB), 2), simt::TB, 0, s>>>(
+            BISSD_LAUNCH("state_passing_fwd", launch_pdl(simt::state_passing_fwd4<T>, dim3(d.b * d.H, ceil_div(d.P * d.N, 4 * simt::TB), 2), simt::TB, 0, s, 
                 d, loc, a.cs_f, a.cs_b, a.init_f, a.init_b, a.states_f, a.states_b, a.final_f, a.final_b));
         } else {
             BISSD_LAUNCH("state_passing_fwd", simt::state_passing_fwd<T><<<dim3(d.b * d.H, ceil_div(d.P * d.N, simt::TB), 2), simt::TB, 0, s>>>(
@@ -302,7 +325,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                 if (ws_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
                     const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
                     BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
-                    BISSD_LAUNCH("tc_bmm_cb_tma", tc::bmm_cb_tma<T><<<dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s>>>(
+                    BISSD_LAUNCH("tc_bmm_cb_tma", launch_pdl(tc::bmm_cb_tma<T>, dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s, 
                         d, mCc, mBc, CB16, nullptr, nullptr, status));
                 } else
                 BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_cb, s>>>(
@@ -336,7 +359,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
 #define BISSD_SCAN_WS(NSL, NS)                                                                                          \
     do {                                                                                                                \
         BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 0>), smem_t);                                                            \
-        BISSD_LAUNCH("tc_chunk_scan_ws", tc::ws_kernel<T, NSL, NS, 0><<<grid, tc::kWsThreads, smem_t, s>>>(             \
+        BISSD_LAUNCH("tc_chunk_scan_ws", launch_pdl(tc::ws_kernel<T, NSL, NS, 0>, grid, tc::kWsThreads, smem_t, s,              \
             d, mC, mCB, mSf, mSb, mX, wa, status));                                                                     \
     } while (0)
                         if (d.N == 128 && d.Q == 256) BISSD_SCAN_WS(2, 4);
@@ -416,7 +439,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         if constexpr (TcKernels<T>::available) {
             if (tcp && d.has_z) {
                 const long long chunks = (long long)d.b * d.L * d.H * (d.P / 8);
-                BISSD_LAUNCH("gate_bwd", tc::gate_bwd<T><<<(unsigned)((chunks + 255) / 256), 256, 0, s>>>(
+                BISSD_LAUNCH("gate_bwd", launch_pdl(tc::gate_bwd<T>, (unsigned)((chunks + 255) / 256), 256, 0, s, 
                     d, dout, z, out_x, ws + w.g, a.dz));
             }
             if (tcp) {
@@ -430,7 +453,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                             const size_t smem_g = tc::state_grp_smem(d.Q);
                             const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G * ceil_div(d.N, 128), d.R, sm_count());
                             BISSD_ALLOW((tc::state_gemm_grp<T, 1>), smem_g);
-                            BISSD_LAUNCH("tc_dstates_grp", tc::state_gemm_grp<T, 1><<<dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s>>>(
+                            BISSD_LAUNCH("tc_dstates_grp", launch_pdl(tc::state_gemm_grp<T, 1>, dim3(d.b * d.nc * d.G * ks, ceil_div(d.N, 128)), tc::kStateGrpThreads, smem_g, s, 
                                 d, mRow, mCol, ks, a.dt_out, a.cs_f, a.cs_b, F(w.gloc), status));
                         } else {
                             const size_t smem_t = tc::state_tma_smem(d.P, d.Q);
@@ -463,7 +486,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     if (need_pass) {
         if ((d.P * d.N) % 4 == 0) {
             pass_nblk = ceil_div(d.P * d.N, 4 * simt::TB);
-            BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd4<T><<<dim3(d.b * d.H, pass_nblk, 2), simt::TB, 0, s>>>(
+            BISSD_LAUNCH("state_passing_bwd", launch_pdl(simt::state_passing_bwd4<T>, dim3(d.b * d.H, pass_nblk, 2), simt::TB, 0, s, 
                 d, F(w.gloc), a.states_f, a.states_b, a.cs_f, a.cs_b, a.dfinal_f, a.dfinal_b, tcp ? nullptr : F(w.E), tcp ? E16 : nullptr, F(w.dTpart), a.dinit_f, a.dinit_b));
         } else {
             BISSD_LAUNCH("state_passing_bwd", simt::state_passing_bwd<T><<<dim3(d.b * d.H, w.nblk, 2), simt::TB, 0, s>>>(
@@ -489,7 +512,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             if (ws_path && sums_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
                 const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
                 BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
-                BISSD_LAUNCH("tc_bmm_cb_tma", tc::bmm_cb_tma<T><<<dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s>>>(
+                BISSD_LAUNCH("tc_bmm_cb_tma", launch_pdl(tc::bmm_cb_tma<T>, dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s, 
                     d, mCc, mBc, nullptr, CBt16, F(w.cbs), status));
             } else
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
@@ -533,7 +556,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
 #define BISSD_DX_WS(NSL, NS)                                                                                            \
     do {                                                                                                                \
         BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 1>), smem_t);                                                            \
-        BISSD_LAUNCH("tc_dx_ws", tc::ws_kernel<T, NSL, NS, 1><<<grid, tc::kWsThreads, smem_t, s>>>(                     \
+        BISSD_LAUNCH("tc_dx_ws", launch_pdl(tc::ws_kernel<T, NSL, NS, 1>, grid, tc::kWsThreads, smem_t, s,                      \
             d, mB, mCBt, mEf, mEb, mG, wa, status));                                                                    \
     } while (0)
                     if (d.N == 128 && d.Q == 256) BISSD_DX_WS(2, 4);
@@ -602,7 +625,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                         const size_t smem_g = tc::prev_grp_smem(d.N, d.Q);
                         const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G, d.R, sm_count());
                         BISSD_ALLOW(tc::prev_terms_grp<T>, smem_g);
-                        BISSD_LAUNCH("tc_prev_terms_grp", tc::prev_terms_grp<T><<<dim3(d.b * d.nc * d.G * ks), tc::kPrevGrpThreads, smem_g, s>>>(
+                        BISSD_LAUNCH("tc_prev_terms_grp", launch_pdl(tc::prev_terms_grp<T>, dim3(d.b * d.nc * d.G * ks), tc::kPrevGrpThreads, smem_g, s, 
                             d, mC, mSf, mSb, mG128, ks, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
                     } else {
                         BISSD_ALLOW(tc::prev_terms_tma<T>, smem_p);
@@ -613,7 +636,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     if (!no_ws() && tc::dbc_grp_ok(d.P, d.N, d.Q)) {
                         const size_t smem_g = tc::dbc_grp_smem(d.Q, std::min(d.N, 128));
                         BISSD_ALLOW(tc::dbc_accum_grp<T>, smem_g);
-                        BISSD_LAUNCH("tc_dbc_accum_grp", tc::dbc_accum_grp<T><<<dim3(d.b * d.nc * d.G * w.nsplit, 1, 2), tc::kDbcGrpThreads, smem_g, s>>>(
+                        BISSD_LAUNCH("tc_dbc_accum_grp", launch_pdl(tc::dbc_accum_grp<T>, dim3(d.b * d.nc * d.G * w.nsplit, 1, 2), tc::kDbcGrpThreads, smem_g, s, 
                             d, mEf, mEb, mSf, mSb, mX128, mG128, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
                     } else
                     BISSD_LAUNCH("tc_dbc_accum_tma", tc::dbc_accum_tma<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_a, s>>>(
@@ -665,7 +688,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                               tc::make_map2(&mDk, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, 128);
                     const size_t smem_t = tc::dcb_tma_smem(d.P, d.Q);
                     BISSD_ALLOW(tc::dcb_tma<T>, smem_t);
-                    BISSD_LAUNCH("tc_dcb_tma", tc::dcb_tma<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_t, s>>>(
+                    BISSD_LAUNCH("tc_dcb_tma", launch_pdl(tc::dcb_tma<T>, dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_t, s, 
                         d, mG, mX, a.dt_out, a.cs_f, a.cs_b, bmm_tma ? nullptr : F(w.dCB), bmm_tma ? static_cast<void *>(F(w.dCB)) : nullptr, status));
                     dcb_done = true;
                 }
@@ -683,7 +706,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {
                     const size_t smem_s = tc::intra_sums_smem(d.Q);
                     BISSD_ALLOW(tc::intra_sums<T>, smem_s);
-                    BISSD_LAUNCH("tc_intra_sums", tc::intra_sums<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_s, s>>>(
+                    BISSD_LAUNCH("tc_intra_sums", launch_pdl(tc::intra_sums<T>, dim3(bch, nlt_tc), tc::kThreads, smem_s, s, 
                         dg, mG, mX, a.dt_out, a.cs_f, a.cs_b, F(w.cbs), F(w.u4), (long long)d.b * d.H * d.nc * d.Q, status));
                     intra_done = true;
                     use_u4 = true;
@@ -727,7 +750,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             bmm_tc = true;
             const size_t smem_b = tc::bmm_bwd_tma_smem(d.Q);
             BISSD_ALLOW(tc::bmm_bwd_tma<T>, smem_b);
-            BISSD_LAUNCH("tc_bmm_bwd_tma", tc::bmm_bwd_tma<T><<<dim3(d.b * d.nc * d.G * 2, d.Q / 128, d.N / 64), tc::kThreads, smem_b, s>>>(
+            BISSD_LAUNCH("tc_bmm_bwd_tma", launch_pdl(tc::bmm_bwd_tma<T>, dim3(d.b * d.nc * d.G * 2, d.Q / 128, d.N / 64), tc::kThreads, smem_b, s, 
                 d, mDm, mDk, mBb, mCb, F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC, status));
         } else if (tcp) {
             bmm_tc = true;
@@ -741,12 +764,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         BISSD_LAUNCH("bmm_bwd", simt::bmm_bwd<T><<<dim3(d.b * d.nc * d.G * 2, w.nlt, ceil_div(d.N, simt::TILE)), simt::TB, 0, s>>>(
             d, Bm, Cm, F(w.dCB), F(w.dB_part), F(w.dC_part), part_heads, a.dB, a.dC));
     }
-    BISSD_LAUNCH("cumsum_bwd", simt::cumsum_bwd<<<d.b * d.nc * d.H, 256, 0, s>>>(
+    BISSD_LAUNCH("cumsum_bwd", launch_pdl(simt::cumsum_bwd, d.b * d.nc * d.H, 256, 0, s, 
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
         F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), use_u4 ? nullptr : F(w.da_f), use_u4 ? nullptr : F(w.da_b),
         use_u4 ? F(w.u4) : nullptr, F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
-    BISSD_LAUNCH("final_reduce", simt::final_reduce<1024><<<d.H, 1024, 0, s>>>(
+    BISSD_LAUNCH("final_reduce", launch_pdl(simt::final_reduce<1024>, d.H, 1024, 0, s, 
         d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,
         d.has_D ? a.dD : nullptr));
     return BISSD_OK;

@@ -67,4 +67,14 @@ __device__ __forceinline__ void st_any(void *p, int dtype, long long i, float v)
 __device__ __forceinline__ float softplus_ref(float v) { return v <= 20.f ? log1pf(expf(v)) : v; }
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
 
+
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may be scheduled while
+// the kernel before it in the stream is still draining.  Every such kernel opens with pdl_begin(): it lets its own
+// successor be scheduled early, then waits until the predecessor grid has completed and its writes are visible -
+// before that point the kernel touches nothing but its parameters.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_begin() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 }  // namespace bissd

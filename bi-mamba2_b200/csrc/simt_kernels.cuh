@@ -834,6 +834,7 @@ __global__ void __launch_bounds__(TB) bmm_bwd(Dims d, View Bm, View Cm, const fl
 __global__ void __launch_bounds__(256) cumsum_fwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
                                                       long long dsh, const float *A, const float *dt_bias, float *dt_out,
                                                       float *cs_f, float *cs_b) {
+    pdl_begin();
     __shared__ float tot[4][8];
     const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
     const int l = threadIdx.x;
@@ -870,6 +871,7 @@ __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt
                                                       const float *nb, const float *pf, const float *pb, const float *da_f,
                                                       const float *da_b, const float *u4, const float *dTpart, int nblk,
                                                       int nsplit, void *ddt, float *dApart, float *dbiaspart) {
+    pdl_begin();
     __shared__ float tot[4][8];
     __shared__ float red[2][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -940,6 +942,7 @@ __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt
 template <int NT>
 __global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, const float *dbiaspart,
                                                    const float *dDpart, int nlt, float *dA, float *ddt_bias, float *dD) {
+    pdl_begin();
     __shared__ float red[NT];
     const int h = blockIdx.x;
     const int nbc = d.b * d.nc;
@@ -1033,6 +1036,7 @@ template <class T>
 __global__ void __launch_bounds__(TB) state_passing_fwd4(Dims d, const float *loc, const float *cs_f, const float *cs_b,
                                                          const float *init_f, const float *init_b, void *states_f,
                                                          void *states_b, float *final_f, float *final_b) {
+    pdl_begin();
     const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
     const int dir = blockIdx.z;
     const int PN = d.P * d.N;
@@ -1068,6 +1072,7 @@ __global__ void __launch_bounds__(TB) state_passing_bwd4(Dims d, const float *gl
                                                          const void *states_b, const float *cs_f, const float *cs_b,
                                                          const float *dfinal_f, const float *dfinal_b, float *E,
                                                          void *E16, float *dTpart, float *dinit_f, float *dinit_b) {
+    pdl_begin();
     __shared__ float red[TB / 32];
     const int h = blockIdx.x % d.H, b = blockIdx.x / d.H;
     const int dir = blockIdx.z;

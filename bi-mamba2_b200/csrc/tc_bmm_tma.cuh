@@ -17,6 +17,7 @@ template <class T>
 __global__ void __launch_bounds__(kThreads)
 bmm_cb_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB, __nv_bfloat16 *CB16,
            __nv_bfloat16 *CBt16, float *CBs, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ uint64_t bar_in, bar_done;
     __shared__ uint32_t tmem_slot;

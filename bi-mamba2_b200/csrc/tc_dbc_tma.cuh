@@ -188,6 +188,7 @@ dbc_accum_grp(Dims d, const __grid_constant__ CUtensorMap tmEf, const __grid_con
               const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
               const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG, const float *dt_out,
               const float *cs_f, const float *cs_b, float *dB_part, float *dC_part, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ DbcGrpShared sh;
     constexpr int P = 64;
@@ -471,6 +472,7 @@ __global__ void __launch_bounds__(kPrevGrpThreads, 1)
 prev_terms_grp(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmSf,
                const __grid_constant__ CUtensorMap tmSb, const __grid_constant__ CUtensorMap tmG, int ks, const float *cs_f,
                const float *cs_b, float *pf, float *pb, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ PrevGrpShared sh;
     constexpr int P = 64;

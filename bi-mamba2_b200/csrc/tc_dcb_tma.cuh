@@ -25,6 +25,7 @@ template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 dcb_tma(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
         const float *cs_f, const float *cs_b, float *dCB, void *dCB16, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ DcbShared sh;
     const int P = d.P, Q = d.Q, R = d.R;
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 bmm_bwd_tma(Dims d, const __grid_constant__ CUtensorMap tmDm, const __grid_constant__ CUtensorMap tmDk,
             const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const float *dB_part,
             const float *dC_part, int part_heads, void *dB, void *dC, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ uint64_t bar_in, bar_done;
     __shared__ uint32_t tmem_slot;

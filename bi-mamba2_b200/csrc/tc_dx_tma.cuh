@@ -15,6 +15,7 @@ namespace tc {
 // Takes over _chunk_scan_bwd_dz_kernel (src/ssd/bi/ssd_chunk_scan.py:357-440) except its dD partials.
 template <class T>
 __global__ void __launch_bounds__(256) gate_bwd(Dims d, View dout, View z, View out_x, void *g_out, void *dz) {
+    pdl_begin();
     const long long pc = d.P / 8;
     const long long total = (long long)d.b * d.L * d.H * pc;
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;

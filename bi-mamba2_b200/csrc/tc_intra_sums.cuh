@@ -29,6 +29,7 @@ template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 intra_sums(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX, const float *dt_out,
            const float *cs_f, const float *cs_b, const float *CBs, float *u4, long long hq, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ PipeShared sh;
     __shared__ float rsum[2][2][kTileM];                          // [column half][direction][row]

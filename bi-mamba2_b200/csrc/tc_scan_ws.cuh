@@ -381,6 +381,7 @@ __global__ void __launch_bounds__(kWsThreads, 1)
 ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCB,
           const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
           const __grid_constant__ CUtensorMap tmX, const WsArgs a, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ WsShared sh;
     __shared__ float rowred[MODE == 1 ? 3 : 1][3][kTileM];       // MODE 1: three tiles deep, (rs, rsf, rsb) per row

@@ -153,6 +153,7 @@ template <class T, int MODE>
 __global__ void __launch_bounds__(576, 1)
 state_gemm_grp(Dims d, const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol, int ks,
                const float *dt_out, const float *cs_f, const float *cs_b, float *out, int *status) {
+    pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ StateGrpShared sh;
     constexpr int P = 64;
