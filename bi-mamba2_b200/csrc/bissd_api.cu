@@ -875,6 +875,18 @@ static inline size_t conv_dpre_bytes(const bissd_conv_args *a) {
 template <class T, class W>
 static int conv_forward_impl(const bissd_conv_args *a, const conv::ConvDims &d, cudaStream_t s) {
     const dim3 grid((d.channels / 8 + 127) / 128, conv_row_blocks(d.seqlen), d.batch);
+    if constexpr (sizeof(T) == 2) {
+#define BISSD_CONV_FWD(K)                                                                                              \
+    do {                                                                                                               \
+        BISSD_LAUNCH("dwconv_win_fwd", conv::dwconv_win<T, W, 0, K><<<grid, 128, 0, s>>>(d, a->x, a->weight, a->bias,  \
+                                                                                         nullptr, a->out, nullptr));   \
+        return BISSD_OK;                                                                                               \
+    } while (0)
+        if (d.width == 7) BISSD_CONV_FWD(7);                     // rolling-window form for the odd widths
+        if (d.width == 5) BISSD_CONV_FWD(5);
+        if (d.width == 3) BISSD_CONV_FWD(3);
+#undef BISSD_CONV_FWD
+    }
     BISSD_LAUNCH("dwconv_silu_fwd", conv::dwconv_silu_fwd<T, W><<<grid, 128, 0, s>>>(d, a->x, a->weight, a->bias, a->out));
     return BISSD_OK;
 }
@@ -884,10 +896,29 @@ static int conv_backward_impl(const bissd_conv_args *a, const conv::ConvDims &d,
     void *dpre = ws;
     float *part = reinterpret_cast<float *>(ws + conv_dpre_bytes(a));
     // dout is required to be contiguous (checked by the caller), so dpre shares its strides
-    BISSD_LAUNCH("dwconv_silu_bwd_pre", conv::dwconv_silu_bwd_pre<T, W><<<grid, 128, 0, s>>>(
-        d, a->x, a->weight, a->bias, a->dout, dpre));
-    BISSD_LAUNCH("dwconv_silu_bwd_dw", conv::dwconv_silu_bwd_dw<T><<<grid, 128, 0, s>>>(d, a->x, dpre, part));
-    BISSD_LAUNCH("dwconv_silu_bwd_dx", conv::dwconv_silu_bwd_dx<T, W><<<grid, 128, 0, s>>>(d, dpre, a->weight, a->dx));
+    bool win = false;
+    if constexpr (sizeof(T) == 2) {
+#define BISSD_CONV_BWD(K)                                                                                              \
+    do {                                                                                                               \
+        win = true;                                                                                                    \
+        BISSD_LAUNCH("dwconv_win_bwd_pre", conv::dwconv_win<T, W, 1, K><<<grid, 128, 0, s>>>(d, a->x, a->weight,       \
+                                                                                             a->bias, a->dout, dpre, nullptr)); \
+        BISSD_LAUNCH("dwconv_win_bwd_dw", conv::dwconv_win<T, W, 2, K><<<grid, 128, 0, s>>>(d, a->x, nullptr, nullptr, \
+                                                                                            dpre, nullptr, part));    \
+        BISSD_LAUNCH("dwconv_win_bwd_dx", conv::dwconv_win<T, W, 3, K><<<grid, 128, 0, s>>>(d, dpre, a->weight,        \
+                                                                                            nullptr, nullptr, a->dx, nullptr)); \
+    } while (0)
+        if (d.width == 7) BISSD_CONV_BWD(7);                     // rolling-window form for the odd widths
+        else if (d.width == 5) BISSD_CONV_BWD(5);
+        else if (d.width == 3) BISSD_CONV_BWD(3);
+#undef BISSD_CONV_BWD
+    }
+    if (!win) {
+        BISSD_LAUNCH("dwconv_silu_bwd_pre", conv::dwconv_silu_bwd_pre<T, W><<<grid, 128, 0, s>>>(
+            d, a->x, a->weight, a->bias, a->dout, dpre));
+        BISSD_LAUNCH("dwconv_silu_bwd_dw", conv::dwconv_silu_bwd_dw<T><<<grid, 128, 0, s>>>(d, a->x, dpre, part));
+        BISSD_LAUNCH("dwconv_silu_bwd_dx", conv::dwconv_silu_bwd_dx<T, W><<<grid, 128, 0, s>>>(d, dpre, a->weight, a->dx));
+    }
     const int nparts = d.batch * conv_row_blocks(d.seqlen);
     const long long n = (long long)d.channels * (conv::kMaxK + 1);
     BISSD_LAUNCH("conv_bwd_reduce", conv::conv_bwd_reduce<W><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(

@@ -7,8 +7,9 @@
 //   dpre = dout silu'(pre);  dx[b,l,c] = sum_k w[c,k] dpre[b, l - k + K/2, c];
 //   dw[c,k] = sum_{b,l} dpre[b,l,c] x[b, l + k - K/2, c];  dbias[c] = sum_{b,l} dpre[b,l,c]
 //
-// HBM-bound: every thread owns 8 adjacent channels (one 16-byte access per row) and walks a run of rows; the K
-// neighbouring rows of a window are re-read from L1 / L2.  The backward recomputes pre instead of saving it and runs
+// HBM-bound: every thread owns 8 adjacent channels (one 16-byte access per row) and walks a run of rows.  Two forms:
+// the general one (any dtype, any K <= 8) re-reads the K neighbouring rows of a window from L1 / L2; 16-bit
+// activations with K = 3, 5, 7 use the rolling-window kernel further down.  The backward recomputes pre instead of saving it and runs
 // as three light kernels (dpre; weight / bias gradient partials; dx) rather than one register-heavy one.  Weight
 // and bias gradients: per-thread accumulators over the thread's rows, one partial row per (batch, row block) in the
 // workspace, summed in a fixed order by conv_bwd_reduce - no float atomics.  Width K <= 8.
@@ -31,6 +32,7 @@ struct ConvDims {
 using norm::load8;
 using norm::store8;
 using norm::sigmoidn;
+using norm::unpack8n;
 
 // grid (channels / 8 / 128 rounded up, ceil(L / kRows), batch); block 128: thread = 8 channels, kRows rows.
 template <class T, class W>
@@ -182,6 +184,107 @@ __global__ void __launch_bounds__(128, 4) dwconv_silu_bwd_dx(ConvDims d, const v
             }
         }
         store8<T>(dx, b * d.xsb + l * d.xsl + c0, acc);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Odd width K, 16-bit activations: the same four passes with a rolling window.  A thread keeps the K - 1 previous rows
+// of its 8 channels in registers (packed, as loaded) and fetches each row of the source once, U rows per round with
+// all U loads in flight before the first is used - the row-at-a-time kernels above have one new row in flight per
+// thread and are bound by load latency, not by HBM.  MODE 0: out = silu(pre).  MODE 1: dpre = dout silu'(pre).
+// MODE 2: partial dw / dbias from x (window) and dpre.  MODE 3: dx from dpre (same window, weights reversed).
+//   src: x (MODE 0-2) or dpre (MODE 3);  aux: dout (MODE 1) or dpre (MODE 2);  dst: out, dpre, -, dx.
+template <class T>
+__device__ __forceinline__ uint4 conv_row(const void *base, long long rowoff, int l, int seqlen) {
+    return (l >= 0 && l < seqlen) ? __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(base) + rowoff)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+template <class T, class W, int MODE, int K>
+__global__ void __launch_bounds__(128, 3) dwconv_win(ConvDims d, const void *src, const void *weight, const void *bias,
+                                                     const void *aux, void *dst, float *part) {
+    constexpr int U = 4, PAD = K / 2;                            // the window covers rows l - PAD .. l + PAD
+    const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
+    if (c0 >= d.channels) return;
+    const int b = blockIdx.z, l0 = blockIdx.y * kRows, l1 = min(d.seqlen, l0 + kRows);
+    const long long ssb = MODE == 3 ? d.osb : d.xsb, ssl = MODE == 3 ? d.osl : d.xsl;      // source strides
+    const long long dsb = MODE == 3 ? d.xsb : d.osb, dsl = MODE == 3 ? d.xsl : d.osl;      // destination strides
+    float w[K][8], bv[8];                                        // w[o]: weight of window slot o; MODE 2: the dw accumulators
+#pragma unroll
+    for (int o = 0; o < K; ++o)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long wi = (long long)(c0 + j) * K + (MODE == 3 ? K - 1 - o : o);
+            if (MODE == 2) w[o][j] = 0.f;
+            else if constexpr (sizeof(W) == 4) w[o][j] = static_cast<const float *>(weight)[wi];
+            else w[o][j] = static_cast<float>(static_cast<const W *>(weight)[wi]);
+        }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bv[j] = 0.f;                     // MODE 2: the dbias accumulator
+    if (MODE <= 1 && d.has_bias) load8<W>(bias, c0, bv);
+    uint4 win[K - 1];
+#pragma unroll
+    for (int o = 0; o < K - 1; ++o) win[o] = conv_row<T>(src, b * ssb + (long long)(l0 - PAD + o) * ssl + c0, l0 - PAD + o, d.seqlen);
+    for (int lb = l0; lb < l1; lb += U) {
+        uint4 nw[U], au[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int ln = lb + u + PAD;
+            nw[u] = conv_row<T>(src, b * ssb + (long long)ln * ssl + c0, ln, d.seqlen);
+            if (MODE == 1 || MODE == 2) au[u] = conv_row<T>(aux, b * d.osb + (long long)(lb + u) * d.osl + c0, lb + u, l1);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int l = lb + u;
+            if (l < l1) {
+                float t[8];
+                if (MODE == 2) {
+                    float g[8];
+                    unpack8n<T>(au[u], g);
+#pragma unroll
+                    for (int o = 0; o < K; ++o) {
+                        unpack8n<T>(o < K - 1 ? win[o < K - 1 ? o : 0] : nw[u], t);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) w[o][j] = fmaf(g[j], t[j], w[o][j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) bv[j] += g[j];
+                } else {
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = bv[j];
+#pragma unroll
+                    for (int o = 0; o < K; ++o) {
+                        unpack8n<T>(o < K - 1 ? win[o < K - 1 ? o : 0] : nw[u], t);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(w[o][j], t[j], acc[j]);
+                    }
+                    if (MODE == 0) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] *= sigmoidn(acc[j]);
+                    } else if (MODE == 1) {
+                        unpack8n<T>(au[u], t);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float sg = sigmoidn(acc[j]);
+                            acc[j] = t[j] * sg * (1.f + acc[j] * (1.f - sg));
+                        }
+                    }
+                    store8<T>(dst, b * dsb + (long long)l * dsl + c0, acc);
+                }
+            }
+#pragma unroll
+            for (int o = 0; o + 1 < K - 1; ++o) win[o] = win[o + 1];
+            win[K - 2] = nw[u];
+        }
+    }
+    if (MODE == 2) {
+        float *p = part + ((long long)(b * gridDim.y + blockIdx.y) * d.channels + c0) * (kMaxK + 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) p[j * (kMaxK + 1) + k] = w[k][j];
+            p[j * (kMaxK + 1) + kMaxK] = bv[j];
+        }
     }
 }
 

@@ -14,6 +14,10 @@ CASES = [
     ("fp32_width3", (3, 77, 64), 3, torch.float32, torch.float32, True),
     ("fp16_no_bias", (1, 130, 520), 5, torch.float16, torch.float32, False),
     ("short_sequence", (4, 3, 128), 7, torch.float32, torch.float32, True),
+    # 16-bit rolling-window kernels at the edges: sequence shorter than the window, ragged last row block
+    ("bf16_width3_tiny", (2, 5, 64), 3, torch.bfloat16, torch.bfloat16, True),
+    ("bf16_width7_shorter_than_window", (1, 2, 128), 7, torch.bfloat16, torch.float32, True),
+    ("fp16_width7_ragged_blocks", (2, 131, 264), 7, torch.float16, torch.float16, False),
 ]
 
 
