@@ -825,7 +825,8 @@ static int norm_forward_impl(const bissd_norm_args *a, const norm::NormDims &d, 
 }
 template <class T, class W>
 static int norm_backward_impl(const bissd_norm_args *a, const norm::NormDims &d, float *part, cudaStream_t s) {
-    const int grid = norm_grid(d);
+    // two resident CTAs per SM and one partial weight-gradient row per CTA: a larger grid only adds rows to reduce
+    const int grid = std::min(norm_grid(d), 2 * sm_count());
     const size_t smem = (size_t)norm::kWarps * d.hidden * sizeof(float);
     if (d.hidden <= 2048) {
         BISSD_ALLOW((norm::rmsnorm_gated_bwd<T, W, 8>), smem);
@@ -897,13 +898,14 @@ static int conv_backward_impl(const bissd_conv_args *a, const conv::ConvDims &d,
     float *part = reinterpret_cast<float *>(ws + conv_dpre_bytes(a));
     // dout is required to be contiguous (checked by the caller), so dpre shares its strides
     bool win = false;
+    const dim3 grid_dw(grid.x, (d.seqlen + conv::kRowsDw - 1) / conv::kRowsDw, grid.z);   // the window form's dw pass
     if constexpr (sizeof(T) == 2) {
 #define BISSD_CONV_BWD(K)                                                                                              \
     do {                                                                                                               \
         win = true;                                                                                                    \
         BISSD_LAUNCH("dwconv_win_bwd_pre", conv::dwconv_win<T, W, 1, K><<<grid, 128, 0, s>>>(d, a->x, a->weight,       \
                                                                                              a->bias, a->dout, dpre, nullptr)); \
-        BISSD_LAUNCH("dwconv_win_bwd_dw", conv::dwconv_win<T, W, 2, K><<<grid, 128, 0, s>>>(d, a->x, nullptr, nullptr, \
+        BISSD_LAUNCH("dwconv_win_bwd_dw", conv::dwconv_win<T, W, 2, K><<<grid_dw, 128, 0, s>>>(d, a->x, nullptr, nullptr, \
                                                                                             dpre, nullptr, part));    \
         BISSD_LAUNCH("dwconv_win_bwd_dx", conv::dwconv_win<T, W, 3, K><<<grid, 128, 0, s>>>(d, dpre, a->weight,        \
                                                                                             nullptr, nullptr, a->dx, nullptr)); \
@@ -919,7 +921,7 @@ static int conv_backward_impl(const bissd_conv_args *a, const conv::ConvDims &d,
         BISSD_LAUNCH("dwconv_silu_bwd_dw", conv::dwconv_silu_bwd_dw<T><<<grid, 128, 0, s>>>(d, a->x, dpre, part));
         BISSD_LAUNCH("dwconv_silu_bwd_dx", conv::dwconv_silu_bwd_dx<T, W><<<grid, 128, 0, s>>>(d, dpre, a->weight, a->dx));
     }
-    const int nparts = d.batch * conv_row_blocks(d.seqlen);
+    const int nparts = d.batch * (win ? (int)grid_dw.y : conv_row_blocks(d.seqlen));
     const long long n = (long long)d.channels * (conv::kMaxK + 1);
     BISSD_LAUNCH("conv_bwd_reduce", conv::conv_bwd_reduce<W><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
         part, nparts, d.channels, d.width, a->dweight, a->dbias));

@@ -21,6 +21,7 @@ namespace conv {
 
 constexpr int kMaxK = 8;
 constexpr int kRows = 64;                        // rows per thread run (and per partial row of dw / dbias)
+constexpr int kRowsDw = 256;                     // the same for the rolling-window dw pass: fewer partial rows to reduce
 
 struct ConvDims {
     int batch, seqlen, channels, width;
@@ -203,9 +204,10 @@ template <class T, class W, int MODE, int K>
 __global__ void __launch_bounds__(128, 3) dwconv_win(ConvDims d, const void *src, const void *weight, const void *bias,
                                                      const void *aux, void *dst, float *part) {
     constexpr int U = 4, PAD = K / 2;                            // the window covers rows l - PAD .. l + PAD
+    constexpr int ROWS = MODE == 2 ? kRowsDw : kRows;
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 8;
     if (c0 >= d.channels) return;
-    const int b = blockIdx.z, l0 = blockIdx.y * kRows, l1 = min(d.seqlen, l0 + kRows);
+    const int b = blockIdx.z, l0 = blockIdx.y * ROWS, l1 = min(d.seqlen, l0 + ROWS);
     const long long ssb = MODE == 3 ? d.osb : d.xsb, ssl = MODE == 3 ? d.osl : d.xsl;      // source strides
     const long long dsb = MODE == 3 ? d.xsb : d.osb, dsl = MODE == 3 ? d.xsl : d.osl;      // destination strides
     float w[K][8], bv[8];                                        // w[o]: weight of window slot o; MODE 2: the dw accumulators

@@ -85,6 +85,9 @@ template <class T> __device__ __forceinline__ void store8(void *base, long long 
         *reinterpret_cast<uint4 *>(static_cast<T *>(base) + off) = pack8n<T>(v);
     }
 }
+template <class T> __device__ __forceinline__ uint4 ldq(const void *base, long long off) {   // 8 packed 16-bit values
+    return __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(base) + off));
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -101,6 +104,32 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_gated_fwd(NormDims d, const 
     const int nsteps = d.hidden / 256, spg = d.group / 256;          // steps per statistics group
     for (long long row = (long long)blockIdx.x * kWarps + warp; row < d.rows; row += (long long)gridDim.x * kWarps) {
         float xv[NS][8], ss[NS], rs[NS];
+        if constexpr (sizeof(T) == 2) {
+            // all loads of the row are issued before the first is used (a load per step followed by its use costs one
+            // memory round trip per step)
+            const bool gate_first = d.has_z && !d.norm_before_gate;
+            uint4 xq[NS], zq[NS];
+#pragma unroll
+            for (int k = 0; k < NS; ++k) {
+                const long long c0 = k * 256 + lane * 8;
+                xq[k] = k < nsteps ? ldq<T>(x, row * d.sx + c0) : make_uint4(0u, 0u, 0u, 0u);
+                zq[k] = (k < nsteps && gate_first) ? ldq<T>(z, row * d.sz + c0) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int k = 0; k < NS; ++k) {
+                ss[k] = 0.f;
+                rs[k] = 0.f;
+                unpack8n<T>(xq[k], xv[k]);
+                if (gate_first) {
+                    float zz[8];
+                    unpack8n<T>(zq[k], zz);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) xv[k][j] *= zz[j] * sigmoidn(zz[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss[k] = fmaf(xv[k][j], xv[k][j], ss[k]);
+            }
+        } else
 #pragma unroll
         for (int k = 0; k < NS; ++k) {
             ss[k] = 0.f;
@@ -169,17 +198,37 @@ __global__ void __launch_bounds__(kThreads, 2) rmsnorm_gated_bwd(NormDims d, con
         // pass 1: per step, the sum of (dy w) xhat; per group its mean
         float dot[NS], mean[NS];
 #pragma unroll
-        for (int k = 0; k < NS; ++k) {
+        for (int h0 = 0; h0 < NS; h0 += 4) {
+        // four steps at a time: their twelve loads are issued before the first is used
+        uint4 xq[4], gq[4], zq[4];
+        if constexpr (sizeof(T) == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const long long c0 = (h0 + q) * 256 + lane * 8;
+                const bool on = h0 + q < nsteps;
+                xq[q] = on ? ldq<T>(x, row * d.sx + c0) : make_uint4(0u, 0u, 0u, 0u);
+                gq[q] = on ? ldq<T>(dout, row * d.so + c0) : make_uint4(0u, 0u, 0u, 0u);
+                zq[q] = (on && d.has_z) ? ldq<T>(z, row * d.sz + c0) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int k = h0; k < h0 + 4; ++k) {
             dot[k] = 0.f;
             mean[k] = 0.f;
             if (k < nsteps) {
                 const int c0 = k * 256 + lane * 8;
                 const float r = rstd[row * d.ngroups + k / spg];
                 float xv[8], gv[8], wv[8], zz[8];
-                load8<T>(x, row * d.sx + c0, xv);
-                load8<T>(dout, row * d.so + c0, gv);
+                if constexpr (sizeof(T) == 2) {
+                    unpack8n<T>(xq[k - h0], xv);
+                    unpack8n<T>(gq[k - h0], gv);
+                    unpack8n<T>(zq[k - h0], zz);
+                } else {
+                    load8<T>(x, row * d.sx + c0, xv);
+                    load8<T>(dout, row * d.so + c0, gv);
+                    if (d.has_z) load8<T>(z, row * d.sz + c0, zz);
+                }
                 load8<W>(weight, c0, wv);
-                if (d.has_z) load8<T>(z, row * d.sz + c0, zz);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float u = xv[j], dy = gv[j];
@@ -192,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 2) rmsnorm_gated_bwd(NormDims d, con
                 }
             }
         }
+        }
         for (int g = 0; g < d.ngroups; ++g) {
             float gs = 0.f;
 #pragma unroll
@@ -200,17 +250,36 @@ __global__ void __launch_bounds__(kThreads, 2) rmsnorm_gated_bwd(NormDims d, con
 #pragma unroll
             for (int k = 0; k < NS; ++k) mean[k] = (k / spg == g) ? m : mean[k];
         }
-        // pass 2: gradients (the operands come from L1 / L2 the second time)
+        // pass 2: gradients (the operands come from L1 / L2 the second time), again four steps at a time
 #pragma unroll
-        for (int k = 0; k < NS; ++k) {
+        for (int h0 = 0; h0 < NS; h0 += 4) {
+        uint4 xq[4], gq[4], zq[4];
+        if constexpr (sizeof(T) == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const long long c0 = (h0 + q) * 256 + lane * 8;
+                const bool on = h0 + q < nsteps;
+                xq[q] = on ? ldq<T>(x, row * d.sx + c0) : make_uint4(0u, 0u, 0u, 0u);
+                gq[q] = on ? ldq<T>(dout, row * d.so + c0) : make_uint4(0u, 0u, 0u, 0u);
+                zq[q] = (on && d.has_z) ? ldq<T>(z, row * d.sz + c0) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int k = h0; k < h0 + 4; ++k) {
             if (k < nsteps) {
                 const int c0 = k * 256 + lane * 8;
                 const float r = rstd[row * d.ngroups + k / spg];
                 float xv[8], gv[8], wv[8], zz[8], ox[8], oz[8], dwv[8];
-                load8<T>(x, row * d.sx + c0, xv);
-                load8<T>(dout, row * d.so + c0, gv);
+                if constexpr (sizeof(T) == 2) {
+                    unpack8n<T>(xq[k - h0], xv);
+                    unpack8n<T>(gq[k - h0], gv);
+                    unpack8n<T>(zq[k - h0], zz);
+                } else {
+                    load8<T>(x, row * d.sx + c0, xv);
+                    load8<T>(dout, row * d.so + c0, gv);
+                    if (d.has_z) load8<T>(z, row * d.sz + c0, zz);
+                }
                 load8<W>(weight, c0, wv);
-                if (d.has_z) load8<T>(z, row * d.sz + c0, zz);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float sl = 1.f, dsl = 0.f;
@@ -239,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, 2) rmsnorm_gated_bwd(NormDims d, con
                 store8<T>(dx, row * d.sx + c0, ox);
                 if (d.has_z) store8<T>(dz, row * d.sz + c0, oz);
             }
+        }
         }
     }
     // the eight warps' rows are added in warp order and written as this CTA's partial row
