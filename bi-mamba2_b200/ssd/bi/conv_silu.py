@@ -4,31 +4,39 @@
 .transpose(1, 2)` (src/ssd/modules.py:164-167) but works channels-last: no transposes, and the result is one
 contiguous (batch, seqlen, channels) tensor whose channel slices (x, B, C) the scan reads in place.
 
-On CUDA tensors in the kernels' range (channels % 8 == 0, odd width <= 8, channel stride 1) the work is done by
-libbissd (`bissd_dwconv_silu_forward/_backward`, csrc/conv_kernels.cuh); otherwise by the PyTorch expression above.
+All work is done by libbissd (`bissd_dwconv_silu_forward/_backward`, csrc/conv_kernels.cuh).  Their range: CUDA
+tensors, fp32 / bf16 / fp16, channels a multiple of 8, odd width up to 7, weight (and bias) in fp32 or the input's dtype.
+There is no eager or CPU path: anything outside that range raises.
 """
 import ctypes
 
 import torch
-import torch.nn.functional as F
 
 from ssd import _cabi
 
 _DT = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
 
 
-def dwconv1d_silu_ref(x, weight, bias=None):
-    """The reference expression; weight (channels, 1, width) or (channels, width)."""
-    w = weight.reshape(weight.shape[0], 1, -1)
-    y = F.conv1d(x.transpose(1, 2), w, bias, padding=w.shape[-1] // 2, groups=w.shape[0])
-    return F.silu(y).transpose(1, 2)
+def _why_not(x, weight, bias):
+    """None when the kernels cover these arguments, else the reason they do not."""
+    C, K = weight.shape[0], weight.shape[-1]
+    if not x.is_cuda or not weight.is_cuda:
+        return "tensors must be on a CUDA device (no CPU implementation is shipped)"
+    if x.dim() != 3 or x.shape[-1] != C:
+        return f"x must be (batch, seqlen, channels) with {C} channels, got {tuple(x.shape)}"
+    if x.dtype not in _DT or weight.dtype not in (torch.float32, x.dtype) or (bias is not None and bias.dtype != weight.dtype):
+        return f"unsupported dtypes: x {x.dtype}, weight {weight.dtype}"
+    if C % 8 != 0:
+        return f"channels ({C}) must be a multiple of 8"
+    if K % 2 != 1 or K > 7:
+        return f"width ({K}) must be odd and at most 7"
+    if x.numel() == 0:
+        return "empty input"
+    return None
 
 
 def _kernel_ok(x, weight, bias):
-    C, K = weight.shape[0], weight.shape[-1]
-    return (x.is_cuda and x.dim() == 3 and x.dtype in _DT and weight.dtype in (torch.float32, x.dtype) and
-            (bias is None or bias.dtype == weight.dtype) and C % 8 == 0 and K % 2 == 1 and K <= 8 and
-            x.shape[-1] == C and x.numel() > 0)
+    return _why_not(x, weight, bias) is None
 
 
 def _strided_ok(t):
@@ -84,7 +92,9 @@ class _DWConvSiLUFn(torch.autograd.Function):
 
 
 def dwconv1d_silu(x, weight, bias=None):
-    """x (batch, seqlen, channels), weight (channels, 1, width) as nn.Conv1d stores it (or (channels, width))."""
-    if _kernel_ok(x, weight, bias):
-        return _DWConvSiLUFn.apply(x, weight, bias)
-    return dwconv1d_silu_ref(x, weight, bias)
+    """x (batch, seqlen, channels), weight (channels, 1, width) as nn.Conv1d stores it (or (channels, width)).
+    Raises for arguments outside the kernels' range (see the module docstring)."""
+    why = _why_not(x, weight, bias)
+    if why is not None:
+        raise RuntimeError(f"dwconv1d_silu: {why}")
+    return _DWConvSiLUFn.apply(x, weight, bias)

@@ -4,27 +4,43 @@ Same class name, constructor and forward signature as the reference's `ssd.bi.la
 (src/ssd/bi/layernorm_gated.py:415-437); the arithmetic follows its `rms_norm_ref` (:18-41): statistics in fp32,
 result cast back to the input dtype.
 
-On a CUDA device the work is done by libbissd's `bissd_rmsnorm_gated_forward/_backward` (csrc/norm_kernels.cuh) when
-the shape is in the kernels' range (hidden a multiple of 256, at most 4096; groups multiples of 256; no bias) -
-`rmsnorm_fn`; everything else, and CPU tensors, go through the same formula written with PyTorch tensor ops
-(`rmsnorm_ref_fn`), which is also what the tests hold the kernels to.
+All work is done by libbissd's `bissd_rmsnorm_gated_forward/_backward` (csrc/norm_kernels.cuh).  Their range: CUDA
+tensors, fp32 / bf16 / fp16, hidden a multiple of 256 and at most 4096, groups that are multiples of 256, no bias (the
+reference's RMSNorm registers none), weight in fp32 or the input's dtype.  There is no eager or CPU path: anything
+outside that range raises.
 """
 import ctypes
 
 import torch
-import torch.nn.functional as F
 
 from ssd import _cabi
 
 _DT = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
 
 
-def _kernel_ok(x, weight, bias, z, group_size):
+def _why_not(x, weight, bias, z, group_size):
+    """None when the kernels cover these arguments, else the reason they do not."""
     hidden = x.shape[-1]
     group = hidden if group_size is None else group_size
-    return (x.is_cuda and bias is None and x.dtype in _DT and weight.dtype in (torch.float32, x.dtype) and
-            hidden % 256 == 0 and hidden <= 4096 and group % 256 == 0 and hidden % group == 0 and
-            (z is None or (z.shape == x.shape and z.dtype == x.dtype)) and x.numel() > 0)
+    if not x.is_cuda or not weight.is_cuda or (z is not None and not z.is_cuda):
+        return "tensors must be on a CUDA device (no CPU implementation is shipped)"
+    if bias is not None:
+        return "a bias is not supported"
+    if x.dtype not in _DT or weight.dtype not in (torch.float32, x.dtype):
+        return f"unsupported dtypes: x {x.dtype}, weight {weight.dtype}"
+    if hidden % 256 != 0 or hidden > 4096:
+        return f"hidden size {hidden} must be a multiple of 256 and at most 4096"
+    if group % 256 != 0 or hidden % group != 0:
+        return f"group size {group} must be a multiple of 256 that divides the hidden size {hidden}"
+    if z is not None and (z.shape != x.shape or z.dtype != x.dtype):
+        return "z must have x's shape and dtype"
+    if x.numel() == 0:
+        return "empty input"
+    return None
+
+
+def _kernel_ok(x, weight, bias, z, group_size):
+    return _why_not(x, weight, bias, z, group_size) is None
 
 
 def _rows(t, hidden):
@@ -91,30 +107,12 @@ class _RMSNormGatedFn(torch.autograd.Function):
 
 
 def rmsnorm_fn(x, weight, bias=None, z=None, eps=1e-6, group_size=None, norm_before_gate=True):
-    """Same signature as the reference's rmsnorm_fn (src/ssd/bi/layernorm_gated.py:391-393)."""
-    if _kernel_ok(x, weight, bias, z, group_size):
-        return _RMSNormGatedFn.apply(x, weight, z, eps, group_size, norm_before_gate)
-    return rmsnorm_ref_fn(x, weight, bias, z=z, eps=eps, group_size=group_size, norm_before_gate=norm_before_gate)
-
-
-def rmsnorm_ref_fn(x, weight, bias=None, z=None, eps=1e-6, group_size=None, norm_before_gate=True):
-    dtype = x.dtype
-    xf = x.float()
-    zf = z.float() if z is not None else None
-    if zf is not None and not norm_before_gate:
-        xf = xf * F.silu(zf)
-    if group_size is None:
-        rstd = torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + eps)
-        out = xf * rstd * weight.float()
-    else:
-        xg = xf.unflatten(-1, (-1, group_size))
-        rstd = torch.rsqrt(xg.square().mean(dim=-1, keepdim=True) + eps)
-        out = (xg * rstd).flatten(-2) * weight.float()
-    if bias is not None:
-        out = out + bias.float()
-    if zf is not None and norm_before_gate:
-        out = out * F.silu(zf)
-    return out.to(dtype)
+    """Same signature as the reference's rmsnorm_fn (src/ssd/bi/layernorm_gated.py:391-393).  Raises for arguments
+    outside the kernels' range (see the module docstring)."""
+    why = _why_not(x, weight, bias, z, group_size)
+    if why is not None:
+        raise RuntimeError(f"rmsnorm_fn: {why}")
+    return _RMSNormGatedFn.apply(x, weight, z, eps, group_size, norm_before_gate)
 
 
 class RMSNorm(torch.nn.Module):

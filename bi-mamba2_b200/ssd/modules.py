@@ -2,8 +2,9 @@
 bidirectional SSD scan -> gated RMSNorm -> out_proj.
 
 Same constructor arguments, parameter names (state_dict keys) and forward semantics as the reference layer
-(src/ssd/modules.py:17-187), so its checkpoints load unchanged; the scan runs on the sm_100a kernels of
-libbissd, the projections on cuBLAS and the convolution on cuDNN as in the reference.
+(src/ssd/modules.py:17-187), so its checkpoints load unchanged.  The scan, the depthwise convolution + SiLU
+(channels-last, no transposes) and the gated RMSNorm run on the sm_100a kernels of libbissd; the two projections are
+plain library GEMMs (cuBLAS through nn.Linear).
 """
 import math
 

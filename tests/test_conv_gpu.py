@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle.bissd_oracle import max_rel_err
+from oracle.layer_oracle import dwconv1d_silu_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -23,7 +24,7 @@ CASES = [
 
 @pytest.mark.parametrize("name,shape,K,dtype,wdtype,has_bias", CASES, ids=[c[0] for c in CASES])
 def test_forward_and_backward_match_reference_expression(name, shape, K, dtype, wdtype, has_bias):
-    from ssd.bi.conv_silu import _kernel_ok, dwconv1d_silu, dwconv1d_silu_ref
+    from ssd.bi.conv_silu import _kernel_ok, dwconv1d_silu
     b, L, C = shape
     g = torch.Generator().manual_seed(sum(name.encode()))
     x = torch.randn(b, L, C, generator=g).to(dtype).cuda()
@@ -34,9 +35,9 @@ def test_forward_and_backward_match_reference_expression(name, shape, K, dtype, 
     leaves = [t.clone().requires_grad_(True) if t is not None else None for t in (x, w, bias)]
     out = dwconv1d_silu(*leaves)
     out.backward(dout)
-    ref_leaves = [t.detach().float().requires_grad_(True) if t is not None else None for t in (x, w, bias)]
-    ref = dwconv1d_silu_ref(*ref_leaves)
-    ref.backward(dout.float())
+    ref_leaves = [t.detach().float().cpu().requires_grad_(True) if t is not None else None for t in (x, w, bias)]
+    ref = dwconv1d_silu_reference(*ref_leaves)
+    ref.backward(dout.float().cpu())
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert out.dtype == dtype and out.shape == x.shape and out.is_contiguous()
     assert max_rel_err(out, ref) < tol
@@ -47,11 +48,22 @@ def test_forward_and_backward_match_reference_expression(name, shape, K, dtype, 
 
 
 def test_strided_input_slice_is_read_in_place_and_results_repeat():
-    from ssd.bi.conv_silu import dwconv1d_silu, dwconv1d_silu_ref
+    from ssd.bi.conv_silu import dwconv1d_silu
     g = torch.Generator().manual_seed(5)
     big = torch.randn(2, 200, 1024 + 512 + 24, generator=g).bfloat16().cuda()
     x = big[..., 1024:1536]                                  # what BiMamba2 does: a channel slice of in_proj's output
     w = (0.3 * torch.randn(512, 1, 7, generator=g)).cuda()
     a, b2 = dwconv1d_silu(x, w), dwconv1d_silu(x, w)
     assert torch.equal(a, b2)
-    assert max_rel_err(a, dwconv1d_silu_ref(x.float(), w)) < 2e-2
+    assert max_rel_err(a, dwconv1d_silu_reference(x.float().cpu(), w.cpu())) < 2e-2
+
+
+def test_arguments_outside_the_kernel_range_raise():
+    """No eager or CPU path is shipped: unsupported shapes and CPU tensors are errors, not silent detours."""
+    from ssd.bi.conv_silu import dwconv1d_silu
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        dwconv1d_silu(torch.randn(1, 16, 12, device="cuda"), torch.randn(12, 1, 3, device="cuda"))
+    with pytest.raises(RuntimeError, match="odd"):
+        dwconv1d_silu(torch.randn(1, 16, 16, device="cuda"), torch.randn(16, 1, 4, device="cuda"))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        dwconv1d_silu(torch.randn(1, 16, 16), torch.randn(16, 1, 3))

@@ -1,31 +1,36 @@
 """The BiMamba2 layer (the operator's caller in the reference, src/ssd/modules.py:17-187): same parameters and
-state_dict keys, forward + backward against a dense restatement of the layer in fp64 built on the oracle's O(L^2)
-definition of the scan."""
+state_dict keys, forward + backward against a restatement of the layer on the CPU built on the oracle's scan (its
+O(L^2) definition in fp64 for the small layer, its chunked evaluator in fp32 at config #4's sequence length and
+width) and on oracle/layer_oracle.py for the convolution and the gated RMSNorm.  The layers are sized so that the
+CUDA norm and convolution kernels run (d_inner a multiple of 256); tolerances are layer-level (several GEMMs in
+16-bit around the scan): 2e-3 fp32, 5e-2 bf16."""
 import pytest
 import torch
 import torch.nn.functional as F
 
-from oracle.bissd_oracle import dense_reference, max_rel_err
+from oracle.bissd_oracle import chunked_reference, dense_reference, max_rel_err
+from oracle.layer_oracle import dwconv1d_silu_reference, rms_norm_gated_reference
 
 pytestmark = pytest.mark.gpu
 
 
-def _dense_layer(m, u):
-    """fp64 restatement of BiMamba2.forward with the module's own parameters (src/ssd/modules.py:118-187)."""
-    d = torch.float64
+def _dense_layer(m, u, d=torch.float64, chunked=False):
+    """Restatement of BiMamba2.forward with the module's own parameters (src/ssd/modules.py:118-187) in dtype d."""
     W = {k: v.detach().to("cpu", d).requires_grad_(True) for k, v in m.named_parameters()}
     zxbcdt = u @ W["in_proj.weight"].t()
     A = -torch.exp(W["A_log"])
     z, xBC, dt = torch.split(zxbcdt, [m.d_inner, m.d_inner + 2 * m.ngroups * m.d_state, m.nheads], dim=-1)
     dt = F.softplus(dt + W["dt_bias"])
-    xBC = F.silu(F.conv1d(xBC.transpose(1, 2), W["conv1d.weight"], W["conv1d.bias"], padding=m.d_conv // 2,
-                          groups=xBC.shape[-1]).transpose(1, 2))
+    xBC = dwconv1d_silu_reference(xBC, W["conv1d.weight"], W["conv1d.bias"])
     x, B, C = torch.split(xBC, [m.d_inner, m.ngroups * m.d_state, m.ngroups * m.d_state], dim=-1)
     b, L = u.shape[:2]
-    y = dense_reference(x.reshape(b, L, m.nheads, m.headdim), dt, A, B.reshape(b, L, m.ngroups, m.d_state),
-                        C.reshape(b, L, m.ngroups, m.d_state), D=W["D"])
-    y = y.reshape(b, L, m.d_inner)
-    y = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + 1e-5) * W["norm.weight"] * F.silu(z)
+    args = (x.reshape(b, L, m.nheads, m.headdim), dt, A, B.reshape(b, L, m.ngroups, m.d_state),
+            C.reshape(b, L, m.ngroups, m.d_state))
+    if chunked:
+        y = chunked_reference(*args, m.chunk_size, D=W["D"], compute_dtype=d)
+    else:
+        y = dense_reference(*args, D=W["D"], compute_dtype=d)
+    y = rms_norm_gated_reference(y.reshape(b, L, m.d_inner), W["norm.weight"], None, z=z, eps=1e-5)
     return y @ W["out_proj.weight"].t(), W
 
 
@@ -40,24 +45,58 @@ def test_state_dict_keys_match_reference_layer():
 def test_layer_forward_backward_against_dense_restatement(dtype, tol):
     from ssd.modules import BiMamba2
     torch.manual_seed(0)
-    m = BiMamba2(64, d_state=64, headdim=64, chunk_size=128, d_conv=7)
+    m = BiMamba2(128, d_state=64, headdim=64, chunk_size=128, d_conv=7)     # d_inner 256: the CUDA norm's range
     with torch.no_grad():
         m.A_log.uniform_(0.0, 2.0)
         m.D.normal_()
-    u = torch.randn(2, 256, 64, dtype=torch.float64)
-    gout = torch.randn(2, 256, 64, dtype=torch.float64)
+    u = torch.randn(2, 256, 128, dtype=torch.float64)
+    gout = torch.randn(2, 256, 128, dtype=torch.float64)
     ref_u = u.clone().requires_grad_(True)
     ref_out, W = _dense_layer(m, ref_u)
     ref_out.backward(gout)
-    mg = BiMamba2(64, d_state=64, headdim=64, chunk_size=128, d_conv=7).to("cuda", dtype)
+    mg = BiMamba2(128, d_state=64, headdim=64, chunk_size=128, d_conv=7).to("cuda", dtype)
     mg.load_state_dict({k: v.to(dtype) for k, v in m.state_dict().items()})
     ug = u.to("cuda", dtype).requires_grad_(True)
+    from ssd import _cabi
+    _cabi.trace_enable(True)
     out = mg(ug)
     out.backward(gout.to("cuda", dtype))
+    torch.cuda.synchronize()
+    ran = set(_cabi.trace_read())
+    _cabi.trace_enable(False)
+    assert {"rmsnorm_gated_fwd", "rmsnorm_gated_bwd"} <= ran and any(k.startswith("dwconv") for k in ran), ran
     assert max_rel_err(out, ref_out) < tol
     assert max_rel_err(ug.grad, ref_u.grad) < tol
     for k, p in mg.named_parameters():
         if k == "fc_D.weight":            # defined but unused, as in the reference: receives no gradient
             assert p.grad is None
+            continue
+        assert max_rel_err(p.grad, W[k].grad) < tol, k
+
+
+def test_config4_layer_slab_against_chunked_restatement():
+    """Config #4's layer at its true width and sequence length, one batch row: d_model 1024, d_state 64, d_conv 7,
+    expand 2, headdim 64 (32 heads), chunk 256, bf16 module and input of shape (1, 4096, 1024).  The restatement runs
+    in fp32 on the CPU from the same bf16-rounded parameters and input."""
+    from ssd.modules import BiMamba2
+    torch.manual_seed(4)
+    dtype = torch.bfloat16
+    mg = BiMamba2(1024, d_state=64, d_conv=7, expand=2, headdim=64, ngroups=1, chunk_size=256).to("cuda", dtype)
+    with torch.no_grad():
+        mg.A_log.uniform_(0.0, 2.0)
+        mg.D.normal_()
+    u = torch.randn(1, 4096, 1024).to(dtype)
+    gout = torch.randn(1, 4096, 1024).to(dtype)
+    ref_u = u.float().requires_grad_(True)
+    ref_out, W = _dense_layer(mg, ref_u, d=torch.float32, chunked=True)
+    ref_out.backward(gout.float())
+    ug = u.cuda().requires_grad_(True)
+    out = mg(ug)
+    out.backward(gout.cuda())
+    tol = 5e-2
+    assert max_rel_err(out, ref_out) < tol
+    assert max_rel_err(ug.grad, ref_u.grad) < tol
+    for k, p in mg.named_parameters():
+        if k == "fc_D.weight":
             continue
         assert max_rel_err(p.grad, W[k].grad) < tol, k

@@ -258,6 +258,102 @@ def test_strided_inputs_like_the_module_produces():
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# (b2) the small two-head problem over eight seeds, for both tensor-core kernel families
+# ---------------------------------------------------------------------------------------------------------------
+def _report(res):
+    lines = [f"seed {s}: " + ", ".join(f"{k} {v:.2e}" for k, v in e.items()) for s, e in res["errors"].items()]
+    return "\n".join(lines)
+
+
+def test_two_head_problem_eight_seeds_tma_family():
+    """Element-wise tensors within 2e-2; the reduced gradients within the conditioning-aware rule of
+    tests/two_head_worker.py.  Runs on the TMA-fed / persistent kernels (the default for this shape)."""
+    import two_head_worker
+    res = two_head_worker.run()
+    print(_report(res))
+    assert "tc_chunk_scan_ws" in res["family"] and "tc_intra_sums" in res["family"], res["family"]
+    assert not res["failures"], res["failures"]
+
+
+def test_two_head_problem_eight_seeds_thread_staged_family():
+    """The same on the thread-staged tcgen05 kernels (the family shapes like headdim 128 / dstate 256 use), selected
+    for this shape by the library's debug switch BISSD_NO_TMA=1 - read once per process, hence the child process."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import two_head_worker
+    env = dict(os.environ, BISSD_NO_TMA="1")
+    p = subprocess.run([sys.executable, two_head_worker.__file__], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("TWO_HEAD_RESULT ")][-1]
+    res = json.loads(line[len("TWO_HEAD_RESULT "):])
+    print(_report(res))
+    assert "tc_chunk_scan" in res["family"] and "tc_chunk_scan_ws" not in res["family"], res["family"]
+    assert not res["failures"], res["failures"]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# (b3) the benchmark configurations at their true sequence length / heads / head and state sizes, one batch row
+# ---------------------------------------------------------------------------------------------------------------
+def _slab_reference(inp, Q, softplus, heads=None, group=None):
+    """fp32 oracle on one batch row; with `heads` (a slice) and `group`, on the heads of one group only."""
+    sel = dict(inp)
+    if heads is not None:
+        for k in ("x", "z", "dout"):
+            if sel[k] is not None:
+                sel[k] = sel[k][:, :, heads]
+        sel["dt"] = sel["dt"][:, :, heads]
+        for k in ("A", "D", "dt_bias"):
+            if sel[k] is not None:
+                sel[k] = sel[k][heads]
+        sel["B"], sel["C"] = sel["B"][:, :, group:group + 1], sel["C"][:, :, group:group + 1]
+    return reference_with_grads(sel["x"], sel["dt"], sel["A"], sel["B"], sel["C"], Q, sel["dout"], D=sel["D"],
+                                z=sel["z"], dt_bias=sel["dt_bias"], dt_softplus=softplus, compute_dtype=torch.float32)
+
+
+def test_config3_shard_slab_matches_oracle():
+    """Config #3 as one rank of eight sees it: 8192 tokens (32 chunks) of one batch row, 32 heads x 64 in 8 groups,
+    dstate 128, chunk 256, bf16, D of shape (nheads, headdim), no z, dt logits ~ N(-5, 1) with softplus and no bias.
+    The GPU runs all heads; the oracle checks the four heads of group 5 (heads of different groups do not interact:
+    out, dx, ddt, dA, dD of a head and dB, dC of its group depend on that group's heads only)."""
+    b, L, H, P, G, N, Q = 1, 8192, 32, 64, 8, 128, 256
+    inp = make_inputs(33, b, L, H, P, G, N, torch.bfloat16, D_hdim=True, has_bias=False)
+    inp["dt"] = inp["dt"] - 1.0
+    got = run_gpu(inp, Q, True)
+    grp, hs = 5, slice(20, 24)
+    ref = _slab_reference(inp, Q, True, heads=hs, group=grp)
+    sub = dict(out=got["out"][:, :, hs], dx=got["dx"][:, :, hs], ddt=got["ddt"][:, :, hs], dA=got["dA"][hs],
+               dB=got["dB"][:, :, grp:grp + 1], dC=got["dC"][:, :, grp:grp + 1], dD=got["dD"][hs])
+    compare(sub, ref, 2e-2, keys=("out", "dx", "ddt", "dA", "dB", "dC", "dD"))
+
+
+def test_config4_scan_slab_matches_oracle():
+    """Config #4's scan as the BiMamba2 layer calls it: 4096 tokens of one batch row, 32 heads x 64, one group,
+    dstate 64, chunk 256, bf16, dt already positive (softplus applied by the caller) and in bf16, D (nheads,), no z,
+    no dt_bias."""
+    b, L, H, P, G, N, Q = 1, 4096, 32, 64, 1, 64, 256
+    inp = make_inputs(44, b, L, H, P, G, N, torch.bfloat16, has_bias=False, softplus=False, dt_dtype=torch.bfloat16)
+    got = run_gpu(inp, Q, False)
+    ref = _slab_reference(inp, Q, False)
+    compare(got, ref, 2e-2)
+
+
+def test_config5_slab_matches_oracle():
+    """Config #5: 1024 tokens of one batch row, 16 heads x 128 in 2 groups, dstate 256, chunk 128, fp16 ~ N(0, 0.5),
+    z, D (nheads, headdim), dt ~ U(0.001, 0.1) used directly, A = -U(0.5, 8)."""
+    b, L, H, P, G, N, Q = 1, 1024, 16, 128, 2, 256, 128
+    inp = make_inputs(55, b, L, H, P, G, N, torch.float16, has_z=True, D_hdim=True, has_bias=False, softplus=False)
+    g = torch.Generator().manual_seed(55)
+    inp["A"] = -(torch.rand(H, generator=g) * 7.5 + 0.5)
+    for k in ("x", "B", "C", "z", "dout"):
+        inp[k] = (inp[k].float() * 0.5).half()
+    got = run_gpu(inp, Q, False)
+    ref = _slab_reference(inp, Q, False)
+    compare(got, ref, 2e-2)
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # (c) properties at full size (benchmark config #2: b=8, L=2048, 24 heads x 64, dstate 128, chunk 256, bf16, z)
 # ---------------------------------------------------------------------------------------------------------------
 def _config2(batch=8):
