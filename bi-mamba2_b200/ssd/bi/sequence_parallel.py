@@ -4,10 +4,11 @@ Rank r owns tokens [r*L/W, (r+1)*L/W).  Each pass runs in two phases of libbissd
 include/bissd.h) with ONE exchange in between:
 
     forward :  LOCAL  -> local final states F_f, F_b (from zero incoming state) and log total decay per (batch, head)
-               all-gather, then every rank chains   final_f(r) = Lambda_r * init_f(r) + F_f(r),  init_f(r+1) = final_f(r)
-               (mirrored right-to-left for the reverse scan)                      -> FINISH with init_f / init_b
+               ONE all-gather of the packed (F_f, F_b, log decay), then every rank chains
+               final_f(r) = Lambda_r * init_f(r) + F_f(r),  init_f(r+1) = final_f(r)  (unrolled into one weighted sum;
+               mirrored right-to-left for the reverse scan)                       -> FINISH with init_f / init_b
     backward:  LOCAL  -> gradients w.r.t. the incoming states for zero gradient of the outgoing ones
-               all-gather, then   dinit_f(r) = dinit_loc_f(r) + Lambda_r * dfinal_f(r),  dfinal_f(r-1) = dinit_f(r)
+               ONE all-gather, then   dinit_f(r) = dinit_loc_f(r) + Lambda_r * dfinal_f(r),  dfinal_f(r-1) = dinit_f(r)
                (mirrored)                                                        -> FINISH with dfinal_f / dfinal_b
 
 The reference has no multi-GPU path; its single-GPU recurrence over chunks (src/ssd/bi/ssd_state_passing.py:27-92) is
@@ -28,34 +29,52 @@ from .ssd_combined import _check_shapes, _check_status, _f32c, _inner_contig, _p
 # ----------------------------------------------------------------------------------------------------------------
 # boundary algebra (pure tensor code: runs on any device, tested on CPU with gloo)
 # ----------------------------------------------------------------------------------------------------------------
+def _chain_weights(log_decay_all, rank):
+    """log_decay_all (W,b,H): each rank's sum of a over its tokens.  Returns (w_left, w_right), both (W,b,H) fp32:
+    w_left[r']  = exp(sum of log decays of the ranks strictly between r' and `rank`) for r' < rank, else 0;
+    w_right[r'] = the same for r' > rank.  Every exponent is a sum of non-positive numbers; the prefix sums are taken
+    in fp64 so that their differences stay exact when one rank's decay is huge and its neighbours' are not."""
+    W = log_decay_all.shape[0]
+    ld = log_decay_all.double()
+    c = torch.cat([torch.zeros_like(ld[:1]), torch.cumsum(ld, dim=0)], dim=0)       # c[k] = sum_{j<k} ld[j]
+    idx = torch.arange(W, device=ld.device)
+    shape = (W,) + (1,) * (ld.dim() - 1)
+    left = (idx < rank).view(shape)
+    right = (idx > rank).view(shape)
+    e_left = c[rank].unsqueeze(0) - c[1:]                                           # span (r', rank)
+    e_right = c[:-1] - c[rank + 1].unsqueeze(0)                                     # span (rank, r')
+    zero = torch.zeros((), dtype=torch.float64, device=ld.device)
+    w_left = torch.where(left, torch.exp(torch.where(left, e_left, zero)), zero)
+    w_right = torch.where(right, torch.exp(torch.where(right, e_right, zero)), zero)
+    return w_left.to(log_decay_all.dtype), w_right.to(log_decay_all.dtype)
+
+
+def chain_forward_stacked(F_f, F_b, log_decay, rank):
+    """F_f, F_b (W,b,H,P,N): every rank's local final states (from zero incoming state); log_decay (W,b,H).
+    Returns (init_f, init_b) for `rank`:  init_f = sum_{r'<rank} (prod_{r'<r''<rank} Lambda_r'') F_f[r'],  init_b the
+    mirror image over r' > rank - the recurrence  S <- Lambda_r S + F_r  of the single-GPU chunk loop
+    (src/ssd/bi/ssd_state_passing.py:60,81) continued across ranks, unrolled into one weighted sum."""
+    w_left, w_right = _chain_weights(log_decay, rank)
+    return (w_left[..., None, None] * F_f).sum(dim=0), (w_right[..., None, None] * F_b).sum(dim=0)
+
+
+def chain_backward_stacked(dinit_loc_f, dinit_loc_b, log_decay, rank):
+    """dinit_loc_* (W,b,H,P,N): every rank's gradient w.r.t. its incoming states computed with zero gradient of its
+    outgoing states.  Returns (dfinal_f, dfinal_b) for `rank`, the gradients of its outgoing states:
+    dfinal_f = sum_{r'>rank} (prod_{rank<r''<r'} Lambda_r'') dinit_loc_f[r'],  dfinal_b the mirror image."""
+    w_left, w_right = _chain_weights(log_decay, rank)
+    return (w_right[..., None, None] * dinit_loc_f).sum(dim=0), (w_left[..., None, None] * dinit_loc_b).sum(dim=0)
+
+
 def chain_forward_boundaries(F_f, F_b, log_decay, rank):
-    """F_f, F_b: lists (one per rank) of (b,H,P,N) local final states; log_decay: list of (b,H) = sum of a over the
-    rank's tokens.  Returns (init_f, init_b) for `rank`."""
-    W = len(F_f)
-    lam = [torch.exp(ld)[..., None, None] for ld in log_decay]
-    init_f = torch.zeros_like(F_f[0])
-    for r in range(rank):                       # left to right: state entering rank r+1
-        init_f = lam[r] * init_f + F_f[r]
-    init_b = torch.zeros_like(F_b[0])
-    for r in range(W - 1, rank, -1):            # right to left
-        init_b = lam[r] * init_b + F_b[r]
-    return init_f, init_b
+    """List form (one entry per rank) of chain_forward_stacked."""
+    return chain_forward_stacked(torch.stack(list(F_f)), torch.stack(list(F_b)), torch.stack(list(log_decay)), rank)
 
 
 def chain_backward_boundaries(dinit_loc_f, dinit_loc_b, log_decay, rank):
-    """dinit_loc_*: lists of (b,H,P,N) gradients w.r.t. each rank's incoming states computed with zero gradient of its
-    outgoing states.  Returns (dfinal_f, dfinal_b) for `rank`: the gradients of its outgoing states."""
-    W = len(dinit_loc_f)
-    lam = [torch.exp(ld)[..., None, None] for ld in log_decay]
-    dfin = torch.zeros_like(dinit_loc_f[0])     # gradient of final_f of the last rank
-    for r in range(W - 1, rank, -1):
-        dfin = dinit_loc_f[r] + lam[r] * dfin   # = dinit_f(r) = dfinal_f(r-1)
-    dfinal_f = dfin
-    dfin = torch.zeros_like(dinit_loc_b[0])     # final_b of rank 0 leaves to the left: no consumer
-    for r in range(0, rank):
-        dfin = dinit_loc_b[r] + lam[r] * dfin   # = dinit_b(r) = dfinal_b(r+1)
-    dfinal_b = dfin
-    return dfinal_f, dfinal_b
+    """List form (one entry per rank) of chain_backward_stacked."""
+    return chain_backward_stacked(torch.stack(list(dinit_loc_f)), torch.stack(list(dinit_loc_b)),
+                                  torch.stack(list(log_decay)), rank)
 
 
 def _all_gather(t, group):
@@ -63,6 +82,58 @@ def _all_gather(t, group):
     out = [torch.empty_like(t) for _ in range(W)]
     dist.all_gather(out, t.contiguous(), group=group)
     return out
+
+
+def gather_packed(tensors, group):
+    """ONE collective for several same-dtype tensors: they are packed into one flat buffer, all-gathered into a
+    (W, total) tensor that lands in local memory, and handed back as (W, *shape) views in the order given."""
+    W = dist.get_world_size(group)
+    flat = torch.cat([t.reshape(-1) for t in tensors])
+    out = torch.empty(W * flat.numel(), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, flat, group=group)       # rank r's buffer lands at [r * n, (r + 1) * n)
+    out = out.view(W, flat.numel())
+    views, o = [], 0
+    for t in tensors:
+        views.append(out[:, o:o + t.numel()].view((W,) + tuple(t.shape)))
+        o += t.numel()
+    return views
+
+
+# Optional CUDA-event brackets around the exchange (collective + chaining) of every pass, for benchmarks.
+_exchange_events = None
+
+
+def record_exchange_events(on):
+    """on=True: start collecting (start, end) event pairs around every boundary exchange; on=False: stop and drop."""
+    global _exchange_events
+    _exchange_events = [] if on else None
+
+
+def exchange_ms():
+    """Sum of the recorded exchange times in ms (synchronises on the recorded events)."""
+    total = 0.0
+    for e0, e1 in _exchange_events or []:
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total
+
+
+class _ExchangeTimer:
+    def __init__(self, device):
+        self.on = _exchange_events is not None and device.type == "cuda"
+        if self.on:
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def __enter__(self):
+        if self.on:
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            self.e1.record()
+            _exchange_events.append((self.e0, self.e1))
+        return False
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -171,8 +242,9 @@ class _SeqParallelFn(torch.autograd.Function):
     def forward(ctx, x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_softplus, dt_limit, group):
         st = local_forward(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_softplus, dt_limit)
         rank = dist.get_rank(group)
-        Ff, Fb, ld = _all_gather(st.final_f, group), _all_gather(st.final_b, group), _all_gather(st.log_decay, group)
-        init_f, init_b = chain_forward_boundaries(Ff, Fb, ld, rank)
+        with _ExchangeTimer(x.device):
+            Ff, Fb, ld = gather_packed([st.final_f, st.final_b, st.log_decay], group)
+            init_f, init_b = chain_forward_stacked(Ff, Fb, ld, rank)
         out = finish_forward(st, init_f, init_b)
         ctx.st, ctx.group, ctx.ld = st, group, ld
         ctx.dtypes = (A.dtype, None if D is None else D.dtype, None if dt_bias is None else dt_bias.dtype)
@@ -183,8 +255,9 @@ class _SeqParallelFn(torch.autograd.Function):
         st, group = ctx.st, ctx.group
         rank = dist.get_rank(group)
         dif, dib = local_backward(st, dout)
-        gf, gb = _all_gather(dif, group), _all_gather(dib, group)
-        dfinal_f, dfinal_b = chain_backward_boundaries(gf, gb, ctx.ld, rank)
+        with _ExchangeTimer(dout.device):
+            gf, gb = gather_packed([dif, dib], group)
+            dfinal_f, dfinal_b = chain_backward_stacked(gf, gb, ctx.ld, rank)
         dx, ddt, dA, dB, dC, dD, dz, dbias = finish_backward(st, dfinal_f, dfinal_b)
         a_dt, d_dt, b_dt = ctx.dtypes
         return (dx, ddt, dA.to(a_dt), dB, dC, None, None if dD is None else dD.to(d_dt), dz,

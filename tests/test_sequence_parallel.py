@@ -1,8 +1,8 @@
 """Sequence sharding: the boundary-state algebra between ranks.
 
 CPU part (world_size-2 gloo processes): every rank evaluates its shard with the oracle standing in for the kernels,
-exchanges boundary states with all_gather, chains them with the functions the GPU driver uses
-(ssd.bi.sequence_parallel.chain_*_boundaries) and must reproduce the unsharded oracle - outputs and gradients.
+exchanges boundary states with one packed all-gather per pass and chains them with the functions the GPU driver
+uses (ssd.bi.sequence_parallel.gather_packed, chain_*_stacked) and must reproduce the unsharded oracle - outputs and gradients.
 
 GPU part (one GPU, ranks emulated one after the other in one process): the phased C-ABI calls
 (BISSD_PHASE_LOCAL / BISSD_PHASE_FINISH) with chained boundaries against the unsharded operator.
@@ -41,7 +41,7 @@ def _worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ssd.bi.sequence_parallel import _all_gather, chain_backward_boundaries, chain_forward_boundaries
+        from ssd.bi.sequence_parallel import chain_backward_stacked, chain_forward_stacked, gather_packed
         x, dt, A, B, C, D, dout = _problem()
         Q, L = 32, x.shape[1]
         sl = slice(rank * L // world, (rank + 1) * L // world)
@@ -49,13 +49,13 @@ def _worker(rank, world, port, ret):
         # forward, LOCAL: finals from zero incoming state + log total decay
         _, Ff, Fb = dense_reference(xs, dts, A, Bs, Cs, D=D, return_final_states=True)
         ld = (dts * A).sum(dim=1)
-        init_f, init_b = chain_forward_boundaries(_all_gather(Ff, None), _all_gather(Fb, None), _all_gather(ld, None), rank)
+        Ff_all, Fb_all, lds = gather_packed([Ff, Fb, ld], None)          # one collective, as the GPU driver does
+        init_f, init_b = chain_forward_stacked(Ff_all, Fb_all, lds, rank)
         out = dense_reference(xs, dts, A, Bs, Cs, D=D, initial_states_f=init_f, initial_states_b=init_b)
         # backward, LOCAL: gradient w.r.t. the incoming states with zero gradient of the outgoing ones
         loc = manual_backward(xs, dts, A, Bs, Cs, Q, gs, D=D, initial_states_f=init_f, initial_states_b=init_b)
-        lds = _all_gather(ld, None)
-        dfinal_f, dfinal_b = chain_backward_boundaries(_all_gather(loc["dinit_f"], None), _all_gather(loc["dinit_b"], None),
-                                                       lds, rank)
+        gf_all, gb_all = gather_packed([loc["dinit_f"], loc["dinit_b"]], None)
+        dfinal_f, dfinal_b = chain_backward_stacked(gf_all, gb_all, lds, rank)
         fin = manual_backward(xs, dts, A, Bs, Cs, Q, gs, D=D, initial_states_f=init_f, initial_states_b=init_b,
                               dfinal_f=dfinal_f, dfinal_b=dfinal_b)
         # parameter gradients are partial sums over ranks
@@ -162,7 +162,7 @@ def _nccl_worker(rank, world, port, ret):
 @pytest.mark.gpu
 def test_sequence_parallel_over_nccl_matches_single_gpu():
     """Real process group: one rank per GPU, boundary states exchanged with NCCL all-gather."""
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)        # 2048 tokens: one 256-token chunk per rank at 8 ranks
     if world < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")
