@@ -534,6 +534,30 @@ def run_ours(args, cfg):
     state["keep"] = [None, None]
     del dbuf, hout, hres, pin
 
+    # ---- the same step replayed from a CUDA graph (one launch per step on the host side): what the kernels alone
+    # take when the host is out of the way.  Reported beside the headline, never instead of it.
+    graph_replay = None
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        main.wait_stream(side)
+        torch.cuda.synchronize()
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+        for _ in range(3):
+            cg.replay()
+        g_ms, _, g_host = timed(cg.replay, args.steps)
+        graph_replay = dict(ms_per_step=g_ms / args.steps, tokens_per_s=tokens_per_step * args.steps / (g_ms * 1e-3),
+                            host_enqueue_ms_per_step=g_host / args.steps)
+        del cg
+    except Exception as e:                                       # capture refused: report why, keep the run
+        graph_replay = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        torch.cuda.synchronize()
+
     strong = None
     seqpar = None
     if world > 1 and cfg is CONFIGS["2"]:
@@ -581,6 +605,7 @@ def run_ours(args, cfg):
                                                   dt_softplus=cfg["softplus"])},
             "roofline": roof, "op_roofline": op_roof, "kernels": kernels,
             "per_rank_ms": per_rank_ms, "host_enqueue_ms_per_step": per_rank_host, "sustained": sustained,
+            "cuda_graph_replay": graph_replay,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ems / esteps, "steps": esteps,

@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -180,10 +181,29 @@ static BwdWs bwd_layout(const Dims &d) {
 static View view_of(const bissd_tensor &t) { return View{t.ptr, t.stride_batch, t.stride_seq, t.stride_head}; }
 static MutView mview_of(const bissd_tensor &t) { return MutView{t.ptr, t.stride_batch, t.stride_seq, t.stride_head}; }
 
+// Raise a kernel's dynamic shared-memory limit.  The attribute is per (function, device) and sticks, so it is set the
+// first time a kernel needs `bytes` on a device and remembered (the driver call costs a microsecond or two per launch
+// otherwise - a tenth of the host time of a whole pass).
+static std::mutex g_smem_mu;
+static std::map<std::pair<const void *, int>, size_t> g_smem_granted;   // (kernel, device) -> bytes already allowed
 template <class K> static int allow_smem(K kernel, size_t bytes) {
     if (bytes <= 48 * 1024) return BISSD_OK;
-    return note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
-                     "cudaFuncSetAttribute");
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    const std::pair<const void *, int> key(reinterpret_cast<const void *>(kernel), dev);
+    if (dev >= 0) {
+        std::lock_guard<std::mutex> lk(g_smem_mu);
+        auto it = g_smem_granted.find(key);
+        if (it != g_smem_granted.end() && it->second >= bytes) return BISSD_OK;
+    }
+    int rc = note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
+                       "cudaFuncSetAttribute");
+    if (rc == BISSD_OK && dev >= 0) {
+        std::lock_guard<std::mutex> lk(g_smem_mu);
+        size_t &g = g_smem_granted[key];
+        g = std::max(g, bytes);
+    }
+    return rc;
 }
 
 // ---- which kernel family ---------------------------------------------------------------------------------
@@ -776,10 +796,14 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
 }
 
 static int check_device() {
+    static std::atomic<int> major_of[64];                        // 0 = not asked yet
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return BISSD_ERR_LAUNCH;
-    int major = 0;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return BISSD_ERR_LAUNCH;
+    int major = (dev >= 0 && dev < 64) ? major_of[dev].load(std::memory_order_relaxed) : 0;
+    if (!major) {
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return BISSD_ERR_LAUNCH;
+        if (dev >= 0 && dev < 64) major_of[dev].store(major, std::memory_order_relaxed);
+    }
     return major == 10 ? BISSD_OK : BISSD_ERR_ARCH;
 }
 
@@ -1111,8 +1135,16 @@ const char *bissd_kernel_path(const bissd_problem *p) {
     return (!force_simt() && tc_shape_ok(*p)) ? "tcgen05" : "simt";
 }
 
+static int static_scratch_if_known(void **out);
+
 int bissd_read_status(const void *workspace, void *stream, int *status_out) {
-    if (!workspace || !status_out) return BISSD_ERR_NULL;
+    if (!status_out) return BISSD_ERR_NULL;
+    if (!workspace) {                                            // the library-owned scratch of the current device
+        void *scratch = nullptr;
+        int rc = static_scratch_if_known(&scratch);
+        if (rc != BISSD_OK) return rc;
+        workspace = scratch;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = note_cuda(cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync");
     if (rc != BISSD_OK) return rc;
@@ -1173,6 +1205,19 @@ static int static_scratch_on_current_device(void **out) {
         if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 255)) return BISSD_ERR_WORKSPACE;
         g_static_addr[dev] = ptr;
     }
+    *out = g_static_addr[dev];
+    return BISSD_OK;
+}
+
+// For bissd_read_status(NULL, ...): the address remembered by an earlier bissd_forward_static_scratch call on this
+// device; no symbol lookup here, so a status read never triggers the set-up.
+static int static_scratch_if_known(void **out) {
+    int dev = -1;
+    int rc = note_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc != BISSD_OK) return rc;
+    if (dev < 0 || dev >= 64) return BISSD_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) return BISSD_ERR_NULL;              // bissd_forward_static_scratch has not run here yet
     *out = g_static_addr[dev];
     return BISSD_OK;
 }

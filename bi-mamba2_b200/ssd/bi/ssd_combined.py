@@ -6,7 +6,8 @@ name `MambaChunkScanCombinedFn` (:555) and the two private entry points the refe
 benchmarks call, `_mamba_chunk_scan_combined_fwd` (:297) and `_mamba_chunk_scan_combined_bwd` (:334).
 
 All arithmetic runs in libbissd.so (hand-written CUDA for sm_100a, C ABI in include/bissd.h) through two
-PyTorch custom ops, `bissd::scan_fwd` and `bissd::scan_bwd`.  There is no Triton and no CPU or eager fallback:
+PyTorch custom ops, `bissd::scan_fwd` and `bissd::scan_bwd` (in eager mode their implementations are called
+directly, skipping the dispatcher).  There is no Triton and no CPU or eager fallback:
 without the library, or on CPU tensors, the operator raises.
 """
 import math
@@ -88,13 +89,21 @@ def kernel_path(x, dt, B, chunk_size, D=None, z=None, dt_bias=None, dt_softplus=
 
 # ----------------------------------------------------------------------------------------------------------------
 # custom ops: thin marshalling around bissd_forward / bissd_backward
+#
+# `_scan_fwd_core` / `_scan_bwd_core` do the marshalling; `bissd::scan_fwd` / `bissd::scan_bwd` are the same functions
+# registered as PyTorch custom ops (with fake kernels) so that torch.compile and the dispatcher see opaque operators.
+# In plain eager mode the autograd function below calls the cores directly: a trip through the custom-op machinery
+# costs about 0.1 ms of host time per call, a quarter of a forward + backward step of the benchmark shape.
 # ----------------------------------------------------------------------------------------------------------------
-@torch.library.custom_op("bissd::scan_fwd", mutates_args=())
-def scan_fwd(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, chunk_size: int,
-             D: Optional[torch.Tensor], z: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
-             init_f: Optional[torch.Tensor], init_b: Optional[torch.Tensor], dt_softplus: bool, dt_min: float,
-             dt_max: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
-                                     torch.Tensor, torch.Tensor, torch.Tensor]:
+def _family(n, shape, fused, **kw):
+    """n equally shaped buffers: views of one allocation when `fused` (every torch.empty costs a few microseconds of
+    host time), separate tensors otherwise (outputs of a custom op may not share storage)."""
+    if fused:
+        return torch.empty((n,) + tuple(shape), **kw).unbind(0)
+    return tuple(torch.empty(shape, **kw) for _ in range(n))
+
+
+def _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt_softplus, dt_min, dt_max, fused):
     """Returns (out, out_x, dt_out, cs_f, cs_b, states_f, states_b, final_f, final_b); out_x is empty without z."""
     import ctypes
     _require_cuda(x, dt, A, B, C, D, z, dt_bias)
@@ -109,12 +118,9 @@ def scan_fwd(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor
     dev = x.device
     out = torch.empty(x.shape, dtype=x.dtype, device=dev)
     out_x = torch.empty(x.shape, dtype=x.dtype, device=dev) if z is not None else torch.empty(0, dtype=x.dtype, device=dev)
-    dt_out = torch.empty(batch, nheads, nchunks, chunk_size, dtype=torch.float32, device=dev)
-    cs_f, cs_b = torch.empty_like(dt_out), torch.empty_like(dt_out)
-    states_f = torch.empty(batch, nchunks, nheads, headdim, dstate, dtype=x.dtype, device=dev)
-    states_b = torch.empty_like(states_f)
-    final_f = torch.empty(batch, nheads, headdim, dstate, dtype=torch.float32, device=dev)
-    final_b = torch.empty_like(final_f)
+    dt_out, cs_f, cs_b = _family(3, (batch, nheads, nchunks, chunk_size), fused, dtype=torch.float32, device=dev)
+    states_f, states_b = _family(2, (batch, nchunks, nheads, headdim, dstate), fused, dtype=x.dtype, device=dev)
+    final_f, final_b = _family(2, (batch, nheads, headdim, dstate), fused, dtype=torch.float32, device=dev)
     ws, nbytes = _workspace(p, dev, "fwd")
     args = _cabi.FwdArgs(p, _tensor4(x), _tensor4(B), _tensor4(C), _tensor4(z),
                          _cabi.Tensor(dt.data_ptr(), dt.stride(0), dt.stride(1), dt.stride(2)),
@@ -126,6 +132,21 @@ def scan_fwd(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor
         _cabi.check(lib.bissd_forward(ctypes.byref(args), ws.data_ptr(), nbytes, stream))
         _check_status(ws, stream)
     return out, out_x, dt_out, cs_f, cs_b, states_f, states_b, final_f, final_b
+
+
+def _scan_fwd_impl(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, chunk_size: int,
+                   D: Optional[torch.Tensor], z: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
+                   init_f: Optional[torch.Tensor], init_b: Optional[torch.Tensor], dt_softplus: bool, dt_min: float,
+                   dt_max: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                                           torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt_softplus, dt_min, dt_max, False)
+
+
+def _scan_fwd_eager(*args):
+    return _scan_fwd_core(*args, True)
+
+
+scan_fwd = torch.library.custom_op("bissd::scan_fwd", _scan_fwd_impl, mutates_args=())
 
 
 @scan_fwd.register_fake
@@ -144,14 +165,8 @@ def _(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt_softplus, dt
             torch.empty(fin, **f32), torch.empty(fin, **f32))
 
 
-@torch.library.custom_op("bissd::scan_bwd", mutates_args=())
-def scan_bwd(dout: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
-             chunk_size: int, D: Optional[torch.Tensor], z: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
-             out_x: Optional[torch.Tensor], dt_out: torch.Tensor, cs_f: torch.Tensor, cs_b: torch.Tensor,
-             states_f: torch.Tensor, states_b: torch.Tensor, dfinal_f: Optional[torch.Tensor],
-             dfinal_b: Optional[torch.Tensor], want_dinit: bool, dt_softplus: bool, dt_min: float,
-             dt_max: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
-                                     torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+def _scan_bwd_core(dout, x, dt, A, B, C, chunk_size, D, z, dt_bias, out_x, dt_out, cs_f, cs_b, states_f, states_b,
+                   dfinal_f, dfinal_b, want_dinit, dt_softplus, dt_min, dt_max, fused):
     """Returns (dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinit_f, dinit_b); absent ones are empty tensors."""
     import ctypes
     _require_cuda(dout, x, dt, A, B, C)
@@ -170,11 +185,15 @@ def scan_bwd(dout: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, A: torch.Ten
     dB = torch.empty(B.shape, dtype=B.dtype, device=dev)
     dC = torch.empty(C.shape, dtype=C.dtype, device=dev)
     ddt = torch.empty(dt.shape, dtype=dt.dtype, device=dev)
-    dA = torch.empty(nheads, **f32)
+    if dt_bias is not None:
+        dA, ddt_bias = _family(2, (nheads,), fused, **f32)
+    else:
+        dA, ddt_bias = torch.empty(nheads, **f32), empty()
     dD = torch.empty(D.shape, **f32) if D is not None else empty()
-    ddt_bias = torch.empty(nheads, **f32) if dt_bias is not None else empty()
-    dinit_f = torch.empty(batch, nheads, headdim, dstate, **f32) if want_dinit else empty()
-    dinit_b = torch.empty_like(dinit_f)
+    if want_dinit:
+        dinit_f, dinit_b = _family(2, (batch, nheads, headdim, dstate), fused, **f32)
+    else:
+        dinit_f, dinit_b = empty(), empty()
     ws, nbytes = _workspace(p, dev, "bwd")
     opt = lambda t, present: _ptr(t) if present else None
     args = _cabi.BwdArgs(p, _tensor4(x), _tensor4(B), _tensor4(C), _tensor4(z), _tensor4(dout),
@@ -189,6 +208,32 @@ def scan_bwd(dout: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, A: torch.Ten
         _cabi.check(lib.bissd_backward(ctypes.byref(args), ws.data_ptr(), nbytes, stream))
         _check_status(ws, stream)
     return dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinit_f, dinit_b
+
+
+def _scan_bwd_impl(dout: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
+                   chunk_size: int, D: Optional[torch.Tensor], z: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
+                   out_x: Optional[torch.Tensor], dt_out: torch.Tensor, cs_f: torch.Tensor, cs_b: torch.Tensor,
+                   states_f: torch.Tensor, states_b: torch.Tensor, dfinal_f: Optional[torch.Tensor],
+                   dfinal_b: Optional[torch.Tensor], want_dinit: bool, dt_softplus: bool, dt_min: float,
+                   dt_max: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                                           torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _scan_bwd_core(dout, x, dt, A, B, C, chunk_size, D, z, dt_bias, out_x, dt_out, cs_f, cs_b, states_f, states_b,
+                          dfinal_f, dfinal_b, want_dinit, dt_softplus, dt_min, dt_max, False)
+
+
+def _scan_bwd_eager(*args):
+    return _scan_bwd_core(*args, True)
+
+
+scan_bwd = torch.library.custom_op("bissd::scan_bwd", _scan_bwd_impl, mutates_args=())
+
+
+def _ops():
+    """(forward, backward) callables: the registered custom ops while torch.compile is tracing, else the plain
+    implementations."""
+    if torch.compiler.is_compiling():
+        return scan_fwd, scan_bwd
+    return _scan_fwd_eager, _scan_bwd_eager
 
 
 @scan_bwd.register_fake
@@ -229,7 +274,7 @@ def _mamba_chunk_scan_combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, d
     """Same 9-tuple as the reference (src/ssd/bi/ssd_combined.py:331):
     out, out_x, dt, dA_cumsum_f, dA_cumsum_b, states_f, states_b, final_states_f, final_states_b."""
     _check_shapes(x, dt, A, B, C, chunk_size, D, z)
-    out, out_x, dt_out, cs_f, cs_b, st_f, st_b, fin_f, fin_b = scan_fwd(
+    out, out_x, dt_out, cs_f, cs_b, st_f, st_b, fin_f, fin_b = _ops()[0](
         x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states_f, initial_states_b, dt_softplus,
         float(dt_limit[0]), float(dt_limit[1]))
     return out, (out_x if z is not None else None), dt_out, cs_f, cs_b, st_f, st_b, fin_f, fin_b
@@ -243,10 +288,11 @@ def _mamba_chunk_scan_combined_bwd(dout, x, dt, A, B, C, out, chunk_size, D=None
     through its recomputed pre-gate value."""
     _check_shapes(x, dt, A, B, C, chunk_size, D, z)
     assert dout.shape == x.shape
-    fw = scan_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, None, None, dt_softplus, float(dt_limit[0]),
-                  float(dt_limit[1]))
+    fwd_op, bwd_op = _ops()
+    fw = fwd_op(x, dt, A, B, C, chunk_size, D, z, dt_bias, None, None, dt_softplus, float(dt_limit[0]),
+                float(dt_limit[1]))
     outz, out_x, dt_out, cs_f, cs_b, st_f, st_b = fw[:7]
-    g = scan_bwd(dout, x, dt, A, B, C, chunk_size, D, z, dt_bias, out_x if z is not None else None, dt_out, cs_f, cs_b,
+    g = bwd_op(dout, x, dt, A, B, C, chunk_size, D, z, dt_bias, out_x if z is not None else None, dt_out, cs_f, cs_b,
                  st_f, st_b, None, None, False, dt_softplus, float(dt_limit[0]), float(dt_limit[1]))
     gdx, gddt, gdA, gdB, gdC, gdD, gdz, gbias = g[:8]
     for given, got in ((dx, gdx), (ddt, gddt), (dB, gdB), (dC, gdC), (dz, gdz)):
@@ -266,7 +312,7 @@ class MambaChunkScanCombinedFn(torch.autograd.Function):
     def forward(ctx, x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, dt_softplus=False,
                 dt_limit=(0.0, float("inf")), return_final_states=False, initial_states_f=None, initial_states_b=None):
         _check_shapes(x, dt, A, B, C, chunk_size, D, z)
-        out, out_x, dt_out, cs_f, cs_b, st_f, st_b, fin_f, fin_b = scan_fwd(
+        out, out_x, dt_out, cs_f, cs_b, st_f, st_b, fin_f, fin_b = _ops()[0](
             x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states_f, initial_states_b, dt_softplus,
             float(dt_limit[0]), float(dt_limit[1]))
         ctx.save_for_backward(out_x if z is not None else None, x, dt, dt_out, cs_f, cs_b, st_f, st_b, A, B, C, D, z,
@@ -287,8 +333,8 @@ class MambaChunkScanCombinedFn(torch.autograd.Function):
         dfin_f = dfin_b = None
         if ctx.return_final_states:
             dfin_f, dfin_b = args[0], args[1]
-        g = scan_bwd(dout, x, dt, A, B, C, ctx.chunk_size, D, z, dt_bias, out_x, dt_out, cs_f, cs_b, st_f, st_b,
-                     dfin_f, dfin_b, ctx.has_init, ctx.dt_softplus, float(ctx.dt_limit[0]), float(ctx.dt_limit[1]))
+        g = _ops()[1](dout, x, dt, A, B, C, ctx.chunk_size, D, z, dt_bias, out_x, dt_out, cs_f, cs_b, st_f, st_b,
+                      dfin_f, dfin_b, ctx.has_init, ctx.dt_softplus, float(ctx.dt_limit[0]), float(ctx.dt_limit[1]))
         dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinit_f, dinit_b = g
         return (dx, ddt, dA.to(A.dtype), dB, dC, None,
                 dD.to(D.dtype) if D is not None else None,

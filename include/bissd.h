@@ -143,7 +143,12 @@ int bissd_forward(const bissd_fwd_args *args, void *workspace, size_t workspace_
  *   - a problem whose bissd_workspace_bytes() forward size exceeds that limit is refused with BISSD_ERR_TOO_LARGE;
  *   - every GPU context that loads the library holds the array until the process exits;
  *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress) and remembers it:
- *     make that first call with the intended device current, and before starting any stream capture;
+ *     make that first call with the intended device current, and before starting any stream capture.  With CUDA's
+ *     lazy module loading that lookup (or the first kernel launch) is also the moment the driver brings the library's
+ *     device image, this array included, onto the device - work a host that must not allocate later wants done at
+ *     start-up, so issue one small call per device then;
+ *   - the kernels' device status word (see bissd_read_status) sits at the start of the array: pass workspace == NULL
+ *     to bissd_read_status to read it after a call;
  *   - all calls on a device share the one array (it keeps the previous call's contents; the status word at its
  *     start is cleared on entry, everything else is rewritten before it is read), so two calls whose GPU work can
  *     overlap - different streams, or threads - race on it: serialise them.
@@ -209,7 +214,8 @@ int bissd_dwconv_silu_backward(const bissd_conv_args *args, void *workspace, siz
 /* Name of the kernel family the library selects for `p` ("tcgen05" or "simt"); for reports and tests. */
 const char *bissd_kernel_path(const bissd_problem *p);
 
-/* Copies the device status word of `workspace` (written by the last pass that used it) to *status_out and
+/* Copies the device status word of `workspace` (written by the last pass that used it; NULL = the library-owned
+ * scratch of the current device, after bissd_forward_static_scratch has run there) to *status_out and
  * WAITS for `stream` - the one call in this library that synchronises.  0 = no device-side wait ran out.  The
  * tensor-core kernels bound every wait on an mbarrier; when one gives up the kernel records it here, frees its
  * tensor memory and returns, and the results of that pass are invalid.  No reference counterpart. */

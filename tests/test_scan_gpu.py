@@ -406,3 +406,23 @@ def test_config2_many_passes_leave_the_status_word_clean():
         cur = run_gpu(inp, 256, True)
     for k in ("out", "dx", "ddt", "dA"):
         assert torch.equal(first[k], cur[k]), k
+
+
+def test_registered_custom_ops_match_the_eager_path():
+    """bissd::scan_fwd / bissd::scan_bwd (what torch.compile and the dispatcher see) run the same marshalling as the
+    direct calls the autograd function makes in eager mode: same results, bit for bit."""
+    m = _op()
+    inp = make_inputs(9, 1, 256, 2, 64, 1, 64, torch.bfloat16, has_z=True)
+    c = {k: (None if v is None else v.cuda()) for k, v in inp.items()}
+    args = (c["x"], c["dt"], c["A"], c["B"], c["C"], 128, c["D"], c["z"], c["dt_bias"], None, None, True, 0.0, float("inf"))
+    a = torch.ops.bissd.scan_fwd(*args)
+    b = m._scan_fwd_eager(*args)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+    out, out_x, dt_out, cs_f, cs_b, st_f, st_b = a[:7]
+    bargs = (c["dout"], c["x"], c["dt"], c["A"], c["B"], c["C"], 128, c["D"], c["z"], c["dt_bias"], out_x, dt_out, cs_f,
+             cs_b, st_f, st_b, None, None, False, True, 0.0, float("inf"))
+    ga = torch.ops.bissd.scan_bwd(*bargs)
+    gb = m._scan_bwd_eager(*bargs)
+    for u, v in zip(ga, gb):
+        assert torch.equal(u, v)

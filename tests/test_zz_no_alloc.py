@@ -3,8 +3,10 @@
 It exists for hosts that may not allocate device memory where they call the operator (a server that hands out
 fixed buffers and bans cudaMalloc after start-up).  Called here through the C ABI with caller-owned inputs and
 outputs only, twice in a row with different inputs - the second call meets the scratch as the first left it - and
-compared with the ordinary entry point `bissd_forward` given a caller-allocated workspace.  The same kernels run
-in both, so the results must agree to the tolerance of the other GPU tests (in practice bit for bit).
+compared with the ordinary entry point `bissd_forward` given a caller-allocated workspace (the same kernels run
+in both, so the results must agree to the tolerance of the other GPU tests - in practice bit for bit) and, so that the
+file stands on its own, with the CPU oracle.  The device status word of the library-owned scratch must read 0 after
+each call, and the second call must not change the device's free memory.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run every other test.
 """
@@ -70,14 +72,27 @@ def test_static_scratch_forward_matches_workspace_forward(dtype, shape, Q):
         ws = torch.empty(need.value, dtype=torch.uint8, device="cuda")
         _cabi.check(lib.bissd_forward(ctypes.byref(ref_args), ws.data_ptr(), need.value, stream))
         new_args, _ = _args(_cabi, inp, Q, new_buf)
+        if call == 1:                                    # the second call must leave the device's free memory alone
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
         _cabi.check(lib.bissd_forward_static_scratch(ctypes.byref(new_args), stream))
         torch.cuda.synchronize()
+        if call == 1:
+            assert torch.cuda.mem_get_info()[0] == free_before, "the no-allocation entry point changed free device memory"
+        status = ctypes.c_int(-1)
+        _cabi.check(lib.bissd_read_status(None, stream, ctypes.byref(status)))   # NULL = the library-owned scratch
+        assert status.value == 0, f"device status word {status.value}: a bounded device-side wait ran out"
         tol = 1e-3 if dtype == torch.float32 else 2e-2
         for k in ref_buf:
             a, r = new_buf[k].float(), ref_buf[k].float()
             assert torch.isfinite(a).all(), (call, k)
             err = (a - r).abs().max().item() / max(r.abs().max().item(), 1e-30)
             assert err <= tol, (call, k, err)
+        from oracle.bissd_oracle import chunked_reference, max_rel_err
+        c = {k: v.cpu() for k, v in inp.items()}
+        want = chunked_reference(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
+                                 dt_softplus=True)
+        assert max_rel_err(new_buf["out"], want) <= tol, call
 
 
 def test_static_scratch_refuses_oversized_problem():
