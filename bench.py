@@ -1,6 +1,6 @@
 """Benchmark of the bidirectional SSD chunk scan, forward + backward (tokens/s).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3shard|4|5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3shard|4|5] [--layer]
 
 One "step" is one forward + backward pass of `bimamba_chunk_scan_combined` over one batch of synthetic input.  The
 default workload is the Mamba2-130M-layer shape the headline metric is quoted on (config "2"): batch 8, seqlen 2048,
@@ -704,6 +704,45 @@ def seq_parallel_leg(args, dev, rank, world, timed, gather_floats, warmup):
                 collective="one NCCL all_gather_into_tensor per pass (packed final states + log decays; state gradients)")
 
 
+def run_layer(args):
+    """One BiMamba2 layer at config #4's size (forward + backward): b16 L4096 d_model 1024, d_state 64, d_conv 7,
+    expand 2, headdim 64, chunk 256, bf16, random init.  Scan, convolution + SiLU and gated RMSNorm on the library's
+    kernels, the two projections on cuBLAS.  Prints one JSON line with the layer time and the library's kernels."""
+    import torch
+    from ssd import _cabi
+    from ssd.modules import BiMamba2
+    batch = args.batch or 16
+    torch.manual_seed(0)
+    layer = BiMamba2(d_model=1024, d_state=64, d_conv=7, expand=2, headdim=64, chunk_size=256).cuda().bfloat16()
+    u = torch.randn(batch, 4096, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn_like(u)
+    for _ in range(max(args.warmup, 3)):
+        layer(u).backward(g)
+    torch.cuda.synchronize()
+    steps = max(3, min(args.steps, 20))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer(u).backward(g)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    _cabi.trace_enable(True)
+    for _ in range(steps):
+        layer(u).backward(g)
+    torch.cuda.synchronize()
+    tr = _cabi.trace_read()
+    _cabi.trace_enable(False)
+    kernels = {k: {"us_per_step": v[0] / steps * 1000.0, "launches_per_step": v[1] / steps}
+               for k, v in sorted(tr.items(), key=lambda kv: -kv[1][0])}
+    print(json.dumps({"metric": "BiMamba2 layer fwd+bwd tokens/s", "value": batch * 4096 / ms * 1e3, "unit": "tokens/s",
+                      "ms_per_step": ms, "steps": steps, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"config#4 BiMamba2 layer: b{batch} L4096 d_model 1024 d_state 64 d_conv 7 "
+                                             "expand 2 headdim 64 chunk 256"},
+                      "library_kernels_us_per_step": sum(k["us_per_step"] for k in kernels.values()),
+                      "kernels": kernels}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -714,9 +753,13 @@ def main():
                     help="workload; the headline metric is quoted on 2 (the default)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (for profiling runs)")
     ap.add_argument("--no-triton", action="store_true", help="skip the Triton reference leg (for profiling runs)")
+    ap.add_argument("--layer", action="store_true",
+                    help="time one BiMamba2 layer at config #4's size instead of the scan (one GPU; not the headline)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiling captures on a reduced case; not a benchmark number)")
     args = ap.parse_args()
+    if args.layer:
+        return run_layer(args)
     cfg = CONFIGS[args.config]
     if args.batch is not None:
         cfg["batch"] = args.batch

@@ -15,6 +15,7 @@
 #include "norm_kernels.cuh"
 #include "tc_intra.cuh"
 #include "tc_intra_sums.cuh"
+#include "tc_intra_grp.cuh"
 #include "tc_kernels.cuh"
 #include "tc_dbc_tma.cuh"
 #include "tc_dcb_tma.cuh"
@@ -130,7 +131,7 @@ struct FwdWs {
     size_t loc, cb, cb16, total;
 };
 struct BwdWs {
-    size_t cb, cbt, cbt16, cbs, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
+    size_t cb, cbt, cbt16, cb16, cbs, gloc, E, E16, g, dTpart, ddt_out, nf, nb, pf, pb, da_f, da_b, u4, dB_part, dC_part, dCB, dDpart, dApart, dbiaspart, total;
     int nblk, nlt, nsplit;
 };
 
@@ -162,6 +163,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
     w.cbs = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB in strips of 16 columns (tc::intra_sums)
     w.cbt16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);        // CB transposed, rounded to bf16 (TMA-fed dx)
+    w.cb16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);         // CB rounded to bf16 (tc::intra_dcb_grp)
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
     w.ddt_out = take(hq * 4);
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
@@ -239,6 +241,11 @@ static int sm_count() {
 
 static bool no_sums() {  // BISSD_NO_SUMS=1: keep the prefix-sweep form of the intra-chunk decay gradient
     static const bool v = [] { const char *e = getenv("BISSD_NO_SUMS"); return e && e[0] == '1'; }();
+    return v;
+}
+
+static bool no_fused() {  // BISSD_NO_FUSED=1: separate dCB and intra-chunk decay-gradient kernels (for A/B comparisons)
+    static const bool v = [] { const char *e = getenv("BISSD_NO_FUSED"); return e && e[0] == '1'; }();
     return v;
 }
 
@@ -517,6 +524,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
     bool have_fp32_cb = true;                                    // fp32 CB (and its transpose) are in the workspace
     bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
+    bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_grp has been written
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
@@ -528,12 +536,16 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const bool ws_path = !no_tma() && !no_ws() && tc::scan_ws_ok(d.P, d.N, d.Q);
             const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
             __nv_bfloat16 *CBt16 = reinterpret_cast<__nv_bfloat16 *>(ws + w.cbt16);
+            __nv_bfloat16 *CB16b = reinterpret_cast<__nv_bfloat16 *>(ws + w.cb16);
             CUtensorMap mCc, mBc;
             if (ws_path && sums_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
+                // the fused dCB / decay-gradient kernel reads the bf16 tile by TMA; the separate intra_sums kernel
+                // reads the fp32 strips
+                fused_cb = !no_fused() && tc::intra_grp_ok(d.P, d.Q);
                 const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
                 BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
                 BISSD_LAUNCH("tc_bmm_cb_tma", launch_pdl(tc::bmm_cb_tma<T>, dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s, 
-                    d, mCc, mBc, nullptr, CBt16, F(w.cbs), status));
+                    d, mCc, mBc, fused_cb ? CB16b : nullptr, CBt16, fused_cb ? nullptr : F(w.cbs), status));
             } else
             BISSD_LAUNCH("tc_bmm_cb", tc::bmm_cb<T><<<dim3(d.b * d.nc * d.G, nlt_tc), tc::kThreads, smem_cb, s>>>(
                 d, Cm, Bm, (sums_path && ws_path) ? nullptr : F(w.cb), ws_path ? nullptr : F(w.cbt), nullptr,
@@ -690,7 +702,35 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             const int ntQ128 = std::min(ntQ, 128);
             const size_t smem_dcb = tc::smem_bytes(ntQ128, 3 * d.Q), smem_in = tc::smem_bytes(ntQ, 4 * d.Q + tc::kTileM * 8);
             bool dcb_done = false;
-            if (!no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
+            bool fused_done = false;
+            if (fused_cb) {
+                // one kernel for dCB and the intra-chunk decay gradients: a CTA per (batch, chunk, group, row tile)
+                CUtensorMap mG, mX, mCB;
+                const unsigned long long dBC4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
+                const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
+                const unsigned long long sC4b[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
+                const unsigned bx4[4] = {64, 1, 128, 1};
+                const unsigned long long dcb_rows = (unsigned long long)d.b * d.nc * d.G * d.Q;
+                if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
+                    map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q) &&
+                    tc::make_map2(&mCB, BISSD_BF16, ws + w.cb16, d.Q, dcb_rows, 64, 128) &&
+                    tc::bmm_bwd_tma_ok(d.N, d.Q) &&
+                    tc::make_map4(&mBb, a.p.x_dtype, a.B.ptr, dBC4, sB4, bx4) && tc::make_map4(&mCb, a.p.x_dtype, a.C.ptr, dBC4, sC4b, bx4) &&
+                    tc::make_map2(&mDm, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, d.Q) &&
+                    tc::make_map2(&mDk, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, 128)) {
+                    const size_t smem_f = tc::intra_grp_smem(d.Q);
+                    BISSD_ALLOW(tc::intra_dcb_grp<T>, smem_f);
+                    BISSD_LAUNCH("tc_intra_dcb_grp", launch_pdl(tc::intra_dcb_grp<T>, dim3(d.b * d.nc * d.G, nlt_tc), tc::kIntraGrpThreads, smem_f, s,
+                        dg, mG, mX, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
+                        static_cast<void *>(F(w.dCB)), status));
+                    fused_done = dcb_done = true;
+                    bmm_tma = true;
+                    use_u4 = true;
+                } else {
+                    return BISSD_ERR_ALIGN;                      // the bf16 tile was written for this kernel only
+                }
+            }
+            if (!dcb_done && !no_tma() && tc::scan_tma_ok(d.P, d.N, d.Q)) {
                 CUtensorMap mG, mX;
                 const unsigned long long dX4[4] = {(unsigned long long)d.P, (unsigned long long)d.H, (unsigned long long)d.L, (unsigned long long)d.b};
                 const unsigned long long sX4[3] = {(unsigned long long)a.x.stride_head * 2, (unsigned long long)a.x.stride_seq * 2, (unsigned long long)a.x.stride_batch * 2};
@@ -718,9 +758,9 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                 BISSD_LAUNCH("tc_dcb", tc::dcb_kernel<T><<<dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kThreads, smem_dcb, s>>>(
                     dg, x, z, gv, a.dt_out, a.cs_f, a.cs_b, F(w.dCB), status));
             }
-            bool intra_done = false;
+            bool intra_done = fused_done;
             const bool sums_path = !no_tma() && !no_sums() && tc::scan_tma_ok(d.P, d.N, d.Q);
-            if (sums_path) {
+            if (sums_path && !intra_done) {
                 CUtensorMap mG, mX;
                 if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
                     map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q)) {

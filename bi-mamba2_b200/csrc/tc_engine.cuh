@@ -406,6 +406,17 @@ __device__ __forceinline__ void umma_issue_stage(uint32_t d_tmem, int n_tile, in
     }
 }
 
+// CTA-wide wait on an mbarrier phase: the first warp polls, the other warps sleep in the CTA barrier that hands its
+// verdict to everyone.  (Measured on the one-shot kernels: no faster than every warp polling - mbarrier.try_wait
+// suspends the pollers - so those keep their own waits; kernels with sixteen warps use this form.)
+// Every thread of the CTA must call it; the result is uniform.  `ok_in`: a thread that has already seen a failure
+// passes false, which skips its wait and makes the common result false.
+__device__ __forceinline__ bool mbar_wait_cta(uint64_t *bar, uint32_t parity, bool ok_in = true) {
+    bool ok = ok_in;
+    if (threadIdx.x < 32) ok = ok && mbar_wait(bar, parity);
+    return __syncthreads_and(ok);
+}
+
 // Wait until every MMA issued so far has completed, so the accumulators can be read with tmem_ld32.
 __device__ __forceinline__ bool umma_drain(Pipe &p) {
     if (threadIdx.x == 0) umma_commit(&p.sh->done_bar);

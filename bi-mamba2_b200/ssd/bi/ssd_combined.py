@@ -354,7 +354,8 @@ def bimamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_b
         A: (nheads)
         B: (batch, seqlen, ngroups, dstate)
         C: (batch, seqlen, ngroups, dstate)
-        chunk_size: int
+        chunk_size: int, 32 ... 256 (the reference accepts any value >= 32; larger chunks are refused here with
+            a libbissd shape error)
         D: (nheads, headdim) or (nheads,)
         z: (batch, seqlen, nheads, headdim)
         dt_bias: (nheads,)

@@ -24,7 +24,7 @@ Two placements are modelled:
     x * (decay * dt) (not B * ...) -> x dtype before the chunk-state product
     C.B^T -> bf16 when it is written, then  bf16(CB) * weight -> x dtype   (two roundings where the reference has one)
     the chunk-level <S, g> terms use the 16-bit saved states
-    the intra-chunk decay terms are row / column sums of  (g.x^T) * CB * weight  rounded to the x dtype
+    the intra-chunk decay terms are row / column sums of  (g.x^T) * bf16(CB) * weight  rounded to bf16
 """
 import torch
 import torch.nn.functional as F
@@ -177,10 +177,11 @@ def rounded_forward_backward(x, dt, A, B, C, chunk_size, dout, D=None, z=None, d
     G2 = torch.einsum("bclhp,bcshp->bhcls", gc, xc)
     dts = dt_out[..., None, :]
     dCB = q((G2 * dts * (Lf + Lb)).view(b, G, R, nc, Q, Q).sum(2).permute(0, 2, 1, 3, 4))
-    Wf = G2 * CB * dts * Lf * (idx[:, None] > idx[None, :])
-    Wb = G2 * CB * dts * Lb * (idx[:, None] < idx[None, :])
+    CBw = qcb(CB) if kern else CB                                         # the kernels read the bf16 copy of C.B^T here too
+    Wf = G2 * CBw * dts * Lf * (idx[:, None] > idx[None, :])
+    Wb = G2 * CBw * dts * Lb * (idx[:, None] < idx[None, :])
     if kern:
-        Wf, Wb = q(Wf), q(Wb)
+        Wf, Wb = qcb(Wf), qcb(Wb)                                         # rounded to bf16 for the column-sum product
     Rf = torch.cumsum(Wf, dim=-1) - Wf
     da_f = (Rf * lower).sum(dim=-2)
     Rb = torch.flip(torch.cumsum(torch.flip(Wb, [-1]), -1), [-1]) - Wb
