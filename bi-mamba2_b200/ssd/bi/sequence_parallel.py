@@ -84,17 +84,33 @@ def _all_gather(t, group):
     return out
 
 
+_gather_buffers = {}
+
+
 def gather_packed(tensors, group):
     """ONE collective for several same-dtype tensors: they are packed into one flat buffer, all-gathered into a
-    (W, total) tensor that lands in local memory, and handed back as (W, *shape) views in the order given."""
+    (W, total) tensor that lands in local memory, and handed back as (W, *shape) views in the order given.
+
+    The send and receive buffers are kept per (device, dtype, size, world size) and reused: a buffer that has been
+    through a NCCL call is held back by the caching allocator until the communication stream has released it, so
+    fresh ones every pass turn into real cudaMalloc / cudaFree calls - two milliseconds per step at config #3's shard
+    size.  The views returned are therefore only valid until the next call with the same sizes: use them at once (the
+    chaining does) and copy what must live longer."""
     W = dist.get_world_size(group)
-    flat = torch.cat([t.reshape(-1) for t in tensors])
-    out = torch.empty(W * flat.numel(), dtype=flat.dtype, device=flat.device)
+    n = sum(t.numel() for t in tensors)
+    ref = tensors[0]
+    key = (ref.device, ref.dtype, n, W)
+    buf = _gather_buffers.get(key)
+    if buf is None:
+        buf = (torch.empty(n, dtype=ref.dtype, device=ref.device), torch.empty(W * n, dtype=ref.dtype, device=ref.device))
+        _gather_buffers[key] = buf
+    flat, out = buf
+    torch.cat([t.reshape(-1) for t in tensors], out=flat)
     dist.all_gather_into_tensor(out, flat, group=group)       # rank r's buffer lands at [r * n, (r + 1) * n)
-    out = out.view(W, flat.numel())
+    rows = out.view(W, n)
     views, o = [], 0
     for t in tensors:
-        views.append(out[:, o:o + t.numel()].view((W,) + tuple(t.shape)))
+        views.append(rows[:, o:o + t.numel()].view((W,) + tuple(t.shape)))
         o += t.numel()
     return views
 
@@ -246,7 +262,11 @@ class _SeqParallelFn(torch.autograd.Function):
             Ff, Fb, ld = gather_packed([st.final_f, st.final_b, st.log_decay], group)
             init_f, init_b = chain_forward_stacked(Ff, Fb, ld, rank)
         out = finish_forward(st, init_f, init_b)
-        ctx.st, ctx.group, ctx.ld = st, group, ld
+        # The shard object lives on the autograd node; it must not hold the output tensor (whose grad_fn is that node):
+        # the cycle would keep every buffer of the pass alive until Python's cycle collector runs, and the caching
+        # allocator would answer each new pass with fresh cudaMalloc calls.
+        st.out = None
+        ctx.st, ctx.group, ctx.ld = st, group, ld.clone()        # ld is a view of a reused receive buffer
         ctx.dtypes = (A.dtype, None if D is None else D.dtype, None if dt_bias is None else dt_bias.dtype)
         return out
 
