@@ -169,7 +169,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
     w.pf = take(hq * 4 * w.nsplit); w.pb = take(hq * 4 * w.nsplit);
     w.da_f = take(hq * 4); w.da_b = take(hq * 4);
-    w.u4 = take(4 * hq * 4);                                         // u_f / u_b of the two row tiles (tc::intra_sums)
+    w.u4 = take(8 * hq * 4);                                         // u_f / u_b per tile (tc::intra_sums: 2 row tiles; tc::intra_dcb_tile: 4)
     w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
     w.dCB = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
@@ -241,6 +241,11 @@ static int sm_count() {
 
 static bool no_sums() {  // BISSD_NO_SUMS=1: keep the prefix-sweep form of the intra-chunk decay gradient
     static const bool v = [] { const char *e = getenv("BISSD_NO_SUMS"); return e && e[0] == '1'; }();
+    return v;
+}
+
+static bool no_tile() {   // BISSD_NO_TILE=1: the 128 x Q, one-CTA-per-SM form of the fused kernel (for A/B comparisons)
+    static const bool v = [] { const char *e = getenv("BISSD_NO_TILE"); return e && e[0] == '1'; }();
     return v;
 }
 
@@ -525,6 +530,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     bool have_fp32_cb = true;                                    // fp32 CB (and its transpose) are in the workspace
     bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
     bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_grp has been written
+    int u4_tiles = 2;                                            // (u_f, u_b) vector pairs per chunk in u4
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
@@ -718,11 +724,21 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     tc::make_map4(&mBb, a.p.x_dtype, a.B.ptr, dBC4, sB4, bx4) && tc::make_map4(&mCb, a.p.x_dtype, a.C.ptr, dBC4, sC4b, bx4) &&
                     tc::make_map2(&mDm, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, d.Q) &&
                     tc::make_map2(&mDk, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, 128)) {
-                    const size_t smem_f = tc::intra_grp_smem(d.Q);
-                    BISSD_ALLOW(tc::intra_dcb_grp<T>, smem_f);
-                    BISSD_LAUNCH("tc_intra_dcb_grp", launch_pdl(tc::intra_dcb_grp<T>, dim3(d.b * d.nc * d.G, nlt_tc), tc::kIntraGrpThreads, smem_f, s,
-                        dg, mG, mX, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
-                        static_cast<void *>(F(w.dCB)), status));
+                    CUtensorMap mX128;
+                    if (!no_tile() && map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128)) {
+                        const size_t smem_f = tc::intra_tile_smem(d.Q);
+                        BISSD_ALLOW(tc::intra_dcb_tile<T>, smem_f);
+                        BISSD_LAUNCH("tc_intra_dcb_tile", launch_pdl(tc::intra_dcb_tile<T>, dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kIntraTileThreads, smem_f, s,
+                            dg, mG, mX128, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
+                            static_cast<void *>(F(w.dCB)), status));
+                        u4_tiles = nlt_tc * nlt_tc;
+                    } else {
+                        const size_t smem_f = tc::intra_grp_smem(d.Q);
+                        BISSD_ALLOW(tc::intra_dcb_grp<T>, smem_f);
+                        BISSD_LAUNCH("tc_intra_dcb_grp", launch_pdl(tc::intra_dcb_grp<T>, dim3(d.b * d.nc * d.G, nlt_tc), tc::kIntraGrpThreads, smem_f, s,
+                            dg, mG, mX, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
+                            static_cast<void *>(F(w.dCB)), status));
+                    }
                     fused_done = dcb_done = true;
                     bmm_tma = true;
                     use_u4 = true;
@@ -827,7 +843,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     BISSD_LAUNCH("cumsum_bwd", launch_pdl(simt::cumsum_bwd, d.b * d.nc * d.H, 256, 0, s, 
         d, a.dt.ptr, a.p.dt_dtype, a.dt.stride_batch, a.dt.stride_seq, a.dt.stride_head, a.A, a.dt_bias, a.dt_out,
         F(w.ddt_out), F(w.nf), F(w.nb), F(w.pf), F(w.pb), use_u4 ? nullptr : F(w.da_f), use_u4 ? nullptr : F(w.da_b),
-        use_u4 ? F(w.u4) : nullptr, F(w.dTpart), pass_nblk, nsplit, a.ddt,
+        use_u4 ? F(w.u4) : nullptr, u4_tiles, F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
     BISSD_LAUNCH("final_reduce", launch_pdl(simt::final_reduce<1024>, d.H, 1024, 0, s, 
         d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,

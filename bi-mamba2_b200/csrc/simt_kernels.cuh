@@ -863,14 +863,15 @@ __global__ void __launch_bounds__(256) cumsum_fwd(Dims d, const void *dt, int dt
 // Takes over the host glue at src/ssd/bi/ssd_combined.py:456-466 and _chunk_cumsum_bwd_kernel
 // (src/ssd/bi/ssd_chunk_state.py:106-170).  dA / ddt_bias partials per (b,c,h) are reduced by final_reduce.
 // The intra-chunk decay gradients come either as da_f / da_b (already dominance sums) or, when u4 is given, as the
-// per-index differences u_f / u_b = column sums - row sums (four arrays: row tile 0 f, b, row tile 1 f, b), which are
+// per-index differences u_f / u_b = column sums - row sums (u4_tiles pairs of arrays: tile 0 f, b, tile 1 f, b, ...), which are
 // added to the terms that are prefix-summed (u_f) and suffix-summed (u_b) exclusively; da_f / da_b are then null.
 __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt_dtype, long long dsb, long long dsl,
                                                       long long dsh, const float *A, const float *dt_bias,
                                                       const float *dt_out, const float *ddt_out, const float *nf,
                                                       const float *nb, const float *pf, const float *pb, const float *da_f,
-                                                      const float *da_b, const float *u4, const float *dTpart, int nblk,
-                                                      int nsplit, void *ddt, float *dApart, float *dbiaspart) {
+                                                      const float *da_b, const float *u4, int u4_tiles,
+                                                      const float *dTpart, int nblk, int nsplit, void *ddt, float *dApart,
+                                                      float *dbiaspart) {
     pdl_begin();
     __shared__ float tot[4][8];
     __shared__ float red[2][8];
@@ -890,9 +891,11 @@ __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt
             w1 += nb[k * split_stride + base + l];
             w2 += pf[k * split_stride + base + l];
         }
-        if (u4) {
-            v1 += u4[base + l] + u4[2 * split_stride + base + l];            // u_f of the two row tiles
-            w1 += u4[split_stride + base + l] + u4[3 * split_stride + base + l];   // u_b
+        if (u4) {                                                         // (u_f, u_b) pairs, one per tile of the chunk
+            for (int t = 0; t < u4_tiles; ++t) {
+                v1 += u4[(2 * t) * split_stride + base + l];
+                w1 += u4[(2 * t + 1) * split_stride + base + l];
+            }
         }
         if (da_f) ex = da_f[base + l] + da_b[base + l];
         if (l == 0)                                                       // dT_b enters at index 0, dT_f at index Q-1

@@ -271,7 +271,7 @@ def test_two_head_problem_eight_seeds_tma_family():
     import two_head_worker
     res = two_head_worker.run()
     print(_report(res))
-    assert "tc_chunk_scan_ws" in res["family"] and "tc_intra_dcb_grp" in res["family"], res["family"]
+    assert "tc_chunk_scan_ws" in res["family"] and "tc_intra_dcb_tile" in res["family"], res["family"]
     assert not res["failures"], res["failures"]
 
 
