@@ -1295,6 +1295,20 @@ int bissd_forward_static_scratch(const bissd_fwd_args *a, void *stream) {
     return bissd_forward(a, scratch, kStaticScratchBytes, stream);
 }
 
+int bissd_chain_boundaries(const float *left, const float *right, const float *log_decay, int64_t rank_stride,
+                           int64_t log_decay_rank_stride, int world, int rank, int64_t batch_heads, int32_t state_elems,
+                           float *out_left, float *out_right, void *stream) {
+    if (!left || !right || !log_decay || !out_left || !out_right) return BISSD_ERR_NULL;
+    if (world < 1 || rank < 0 || rank >= world || batch_heads <= 0 || state_elems <= 0) return BISSD_ERR_SHAPE;
+    int rc = check_device();
+    if (rc != BISSD_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long n = (long long)batch_heads * state_elems;
+    BISSD_LAUNCH("chain_boundaries", simt::chain_boundaries<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
+        left, right, log_decay, rank_stride, log_decay_rank_stride, world, rank, n, state_elems, out_left, out_right));
+    return BISSD_OK;
+}
+
 int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_bytes, void *stream) {
     if (!a) return BISSD_ERR_NULL;
     Dims d;

@@ -1121,5 +1121,35 @@ __global__ void __launch_bounds__(TB) state_passing_bwd4(Dims d, const float *gl
     if (on && dinit) *reinterpret_cast<float4 *>(dinit + (long long)(b * d.H + h) * PN + e) = run;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Boundary chaining for a sequence sharded over `world` ranks (the single-GPU chunk recurrence of
+// src/ssd/bi/ssd_state_passing.py:60,81 continued across ranks, unrolled into weighted sums):
+//     out_left[e]  = sum_{r' < rank} exp(sum_{r' < r'' < rank} ld[r''][bh]) left[r'][e]
+//     out_right[e] = sum_{r' > rank} exp(sum_{rank < r'' < r'} ld[r''][bh]) right[r'][e]
+// with e over (batch*heads) x (headdim*dstate), bh = e / pn, ld[r][bh] = rank r's total log decay (<= 0).  The
+// exponent is accumulated rank by rank (no differences of prefix sums), so fp32 is enough: where it is large its
+// exponential is zero anyway.  Forward pass: left = F_f -> init_f, right = F_b -> init_b; backward pass:
+// left = dinit_b -> dfinal_b, right = dinit_f -> dfinal_f.  All inputs were gathered into local memory beforehand.
+__global__ void __launch_bounds__(256) chain_boundaries(const float *left, const float *right, const float *ld,
+                                                        long long rank_stride, long long ld_rank_stride, int world, int rank,
+                                                        long long n, int pn, float *out_left, float *out_right) {
+    const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (e >= n) return;
+    const long long bh = e / pn;
+    float a = 0.f, cum = 0.f;
+    for (int r = rank - 1; r >= 0; --r) {
+        a = fmaf(__expf(cum), left[r * rank_stride + e], a);
+        cum += ld[r * ld_rank_stride + bh];
+    }
+    out_left[e] = a;
+    a = 0.f;
+    cum = 0.f;
+    for (int r = rank + 1; r < world; ++r) {
+        a = fmaf(__expf(cum), right[r * rank_stride + e], a);
+        cum += ld[r * ld_rank_stride + bh];
+    }
+    out_right[e] = a;
+}
+
 }  // namespace simt
 }  // namespace bissd

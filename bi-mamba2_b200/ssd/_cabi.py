@@ -65,7 +65,7 @@ class ConvArgs(C.Structure):
 
 EXPORTS = ("bissd_abi_version", "bissd_strerror", "bissd_last_cuda_error", "bissd_workspace_bytes", "bissd_forward",
            "bissd_backward", "bissd_kernel_path", "bissd_launch_count", "bissd_trace_enable", "bissd_trace_read", "bissd_selftest_gemm", "bissd_read_status",
-           "bissd_forward_static_scratch", "bissd_rmsnorm_gated_workspace_bytes", "bissd_rmsnorm_gated_forward",
+           "bissd_forward_static_scratch", "bissd_chain_boundaries", "bissd_rmsnorm_gated_workspace_bytes", "bissd_rmsnorm_gated_forward",
            "bissd_rmsnorm_gated_backward", "bissd_dwconv_silu_workspace_bytes", "bissd_dwconv_silu_forward",
            "bissd_dwconv_silu_backward")
 
@@ -120,6 +120,9 @@ def load():
     lib.bissd_dwconv_silu_forward.argtypes = [C.POINTER(ConvArgs), C.c_void_p]
     lib.bissd_dwconv_silu_backward.restype = C.c_int
     lib.bissd_dwconv_silu_backward.argtypes = [C.POINTER(ConvArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.bissd_chain_boundaries.restype = C.c_int
+    lib.bissd_chain_boundaries.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int,
+                                           C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.bissd_read_status.restype = C.c_int
     lib.bissd_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]
     lib.bissd_selftest_gemm.restype = C.c_int

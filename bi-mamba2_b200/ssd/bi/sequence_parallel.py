@@ -66,6 +66,25 @@ def chain_backward_stacked(dinit_loc_f, dinit_loc_b, log_decay, rank):
     return (w_right[..., None, None] * dinit_loc_f).sum(dim=0), (w_left[..., None, None] * dinit_loc_b).sum(dim=0)
 
 
+def chain_on_device(left, right, log_decay, rank):
+    """The two weighted sums of chain_forward_stacked / chain_backward_stacked in ONE libbissd launch
+    (bissd_chain_boundaries) instead of some twenty small tensor kernels.  left, right: (W,b,H,P,N) fp32 CUDA tensors
+    (views of a gathered buffer are fine: only the rank stride may differ from contiguous); log_decay (W,b,H).
+    Returns (sum over ranks < rank of left, sum over ranks > rank of right), each (b,H,P,N)."""
+    W, b, H, P, N = left.shape
+    assert left.dtype == torch.float32 and right.dtype == torch.float32 and log_decay.dtype == torch.float32
+    assert left[0].is_contiguous() and right[0].is_contiguous() and log_decay[0].is_contiguous()
+    assert left.stride(0) == right.stride(0)
+    out_l, out_r = torch.empty(2, b, H, P, N, dtype=torch.float32, device=left.device).unbind(0)
+    lib = _cabi.load()
+    with torch.cuda.device(left.device):
+        stream = torch.cuda.current_stream(left.device).cuda_stream
+        _cabi.check(lib.bissd_chain_boundaries(left.data_ptr(), right.data_ptr(), log_decay.data_ptr(), left.stride(0),
+                                               log_decay.stride(0), W, rank, b * H, P * N, out_l.data_ptr(),
+                                               out_r.data_ptr(), stream))
+    return out_l, out_r
+
+
 def chain_forward_boundaries(F_f, F_b, log_decay, rank):
     """List form (one entry per rank) of chain_forward_stacked."""
     return chain_forward_stacked(torch.stack(list(F_f)), torch.stack(list(F_b)), torch.stack(list(log_decay)), rank)
@@ -260,7 +279,7 @@ class _SeqParallelFn(torch.autograd.Function):
         rank = dist.get_rank(group)
         with _ExchangeTimer(x.device):
             Ff, Fb, ld = gather_packed([st.final_f, st.final_b, st.log_decay], group)
-            init_f, init_b = chain_forward_stacked(Ff, Fb, ld, rank)
+            init_f, init_b = chain_on_device(Ff, Fb, ld, rank)
         out = finish_forward(st, init_f, init_b)
         # The shard object lives on the autograd node; it must not hold the output tensor (whose grad_fn is that node):
         # the cycle would keep every buffer of the pass alive until Python's cycle collector runs, and the caching
@@ -277,7 +296,7 @@ class _SeqParallelFn(torch.autograd.Function):
         dif, dib = local_backward(st, dout)
         with _ExchangeTimer(dout.device):
             gf, gb = gather_packed([dif, dib], group)
-            dfinal_f, dfinal_b = chain_backward_stacked(gf, gb, ctx.ld, rank)
+            dfinal_b, dfinal_f = chain_on_device(gb, gf, ctx.ld, rank)      # left = dinit_b -> dfinal_b, right = dinit_f -> dfinal_f
         dx, ddt, dA, dB, dC, dD, dz, dbias = finish_backward(st, dfinal_f, dfinal_b)
         a_dt, d_dt, b_dt = ctx.dtypes
         return (dx, ddt, dA.to(a_dt), dB, dC, None, None if dD is None else dD.to(d_dt), dz,

@@ -159,6 +159,19 @@ int bissd_forward_static_scratch(const bissd_fwd_args *args, void *stream);
 /* Backward pass. */
 int bissd_backward(const bissd_bwd_args *args, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Boundary chaining between the two phases of a sequence-sharded pass (no reference counterpart: the reference is
+ * single-GPU; this continues its chunk recurrence, src/ssd/bi/ssd_state_passing.py:60,81, across ranks).  Every rank
+ * has gathered all ranks' boundary tensors into LOCAL memory (e.g. with one NCCL all-gather); then
+ *     out_left  = sum over ranks r' < rank  of exp(sum of log_decay of the ranks strictly between) * left[r']
+ *     out_right = sum over ranks r' > rank  of the same weight * right[r']
+ * left / right: rank r' at offset r' * rank_stride (elements), each (batch*heads, state_elems) fp32 contiguous;
+ * log_decay: rank r' at r' * log_decay_rank_stride, (batch*heads) fp32, the rank's sum of Delta*A over its tokens.
+ * Forward pass: left = final_f -> init_f, right = final_b -> init_b.  Backward: left = dinit_b -> dfinal_b,
+ * right = dinit_f -> dfinal_f. */
+int bissd_chain_boundaries(const float *left, const float *right, const float *log_decay, int64_t rank_stride,
+                           int64_t log_decay_rank_stride, int world, int rank, int64_t batch_heads, int32_t state_elems,
+                           float *out_left, float *out_right, void *stream);
+
 /* ---- gated RMSNorm (the layer that follows the scan in BiMamba2) -------------------------------------------------
  * Takes over rmsnorm_fn / _layer_norm_fwd / _layer_norm_bwd of src/ssd/bi/layernorm_gated.py:108-152, :271-340, used by
  * ssd.modules.BiMamba2 at src/ssd/modules.py:114,184:

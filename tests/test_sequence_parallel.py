@@ -176,3 +176,23 @@ def test_sequence_parallel_over_nccl_matches_single_gpu():
         assert p.exitcode == 0
     for r in range(world):
         assert all(v < 2e-2 for v in ret[r].values()), (r, dict(ret[r]))
+
+
+@pytest.mark.gpu
+def test_chain_kernel_matches_tensor_formulation():
+    """bissd_chain_boundaries (one launch) against the torch formulation the CPU tests pin, forward and backward roles,
+    including ranks whose decay underflows."""
+    from ssd.bi import sequence_parallel as sp
+    g = torch.Generator().manual_seed(2)
+    W, b, H, P, N = 5, 2, 3, 8, 16
+    left = torch.randn(W, b, H, P, N, generator=g).cuda()
+    right = torch.randn(W, b, H, P, N, generator=g).cuda()
+    ld = (-torch.rand(W, b, H, generator=g) * 3.0)
+    ld[2, 0, 1] = -2000.0
+    ld = ld.cuda()
+    for rank in range(W):
+        got_l, got_r = sp.chain_on_device(left, right, ld, rank)
+        want_l, want_r = sp.chain_forward_stacked(left, right, ld, rank)
+        assert max_rel_err(got_l, want_l) < 1e-5 and max_rel_err(got_r, want_r) < 1e-5, rank
+        want_df, want_db = sp.chain_backward_stacked(right, left, ld, rank)   # (dinit_f, dinit_b) = (right, left)
+        assert max_rel_err(got_r, want_df) < 1e-5 and max_rel_err(got_l, want_db) < 1e-5, rank
