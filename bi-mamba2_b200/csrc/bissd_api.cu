@@ -163,7 +163,7 @@ static BwdWs bwd_layout(const Dims &d) {
     w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
     w.cbs = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB in strips of 16 columns (tc::intra_sums)
     w.cbt16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);        // CB transposed, rounded to bf16 (TMA-fed dx)
-    w.cb16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);         // CB rounded to bf16 (tc::intra_dcb_grp)
+    w.cb16 = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 2);         // CB rounded to bf16 (tc::intra_dcb_tile)
     w.dTpart = take((size_t)2 * d.b * d.H * d.nc * w.nblk * 4);
     w.ddt_out = take(hq * 4);
     w.nf = take(hq * 4 * w.nsplit); w.nb = take(hq * 4 * w.nsplit);
@@ -241,11 +241,6 @@ static int sm_count() {
 
 static bool no_sums() {  // BISSD_NO_SUMS=1: keep the prefix-sweep form of the intra-chunk decay gradient
     static const bool v = [] { const char *e = getenv("BISSD_NO_SUMS"); return e && e[0] == '1'; }();
-    return v;
-}
-
-static bool no_tile() {   // BISSD_NO_TILE=1: the 128 x Q, one-CTA-per-SM form of the fused kernel (for A/B comparisons)
-    static const bool v = [] { const char *e = getenv("BISSD_NO_TILE"); return e && e[0] == '1'; }();
     return v;
 }
 
@@ -529,7 +524,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     int nlt = w.nlt, nsplit = 1, part_heads = d.H;
     bool have_fp32_cb = true;                                    // fp32 CB (and its transpose) are in the workspace
     bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
-    bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_grp has been written
+    bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_tile has been written
     int u4_tiles = 2;                                            // (u_f, u_b) vector pairs per chunk in u4
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     if constexpr (TcKernels<T>::available) {
@@ -547,7 +542,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             if (ws_path && sums_path && tc::bmm_cb_tma_ok(d.N, d.Q) && make_cb_maps(a, d, &mCc, &mBc)) {
                 // the fused dCB / decay-gradient kernel reads the bf16 tile by TMA; the separate intra_sums kernel
                 // reads the fp32 strips
-                fused_cb = !no_fused() && tc::intra_grp_ok(d.P, d.Q);
+                fused_cb = !no_fused() && tc::intra_tile_ok(d.P, d.Q);
                 const size_t smem_ct = tc::bmm_cb_tma_smem(d.N);
                 BISSD_ALLOW(tc::bmm_cb_tma<T>, smem_ct);
                 BISSD_LAUNCH("tc_bmm_cb_tma", launch_pdl(tc::bmm_cb_tma<T>, dim3(d.b * d.nc * d.G, d.Q / 128, d.Q / 128), tc::kThreads, smem_ct, s, 
@@ -711,34 +706,25 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             bool fused_done = false;
             if (fused_cb) {
                 // one kernel for dCB and the intra-chunk decay gradients: a CTA per (batch, chunk, group, row tile)
-                CUtensorMap mG, mX, mCB;
+                CUtensorMap mG, mX128, mCB;
                 const unsigned long long dBC4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
                 const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
                 const unsigned long long sC4b[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
                 const unsigned bx4[4] = {64, 1, 128, 1};
                 const unsigned long long dcb_rows = (unsigned long long)d.b * d.nc * d.G * d.Q;
                 if (map_bshd(&mG, a.p.x_dtype, gv.ptr, gv.sb, gv.sl, gv.sh, d.P, d.H, d.L, d.b, 128) &&
-                    map_bshd(&mX, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, d.Q) &&
+                    map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128) &&
                     tc::make_map2(&mCB, BISSD_BF16, ws + w.cb16, d.Q, dcb_rows, 64, 128) &&
                     tc::bmm_bwd_tma_ok(d.N, d.Q) &&
                     tc::make_map4(&mBb, a.p.x_dtype, a.B.ptr, dBC4, sB4, bx4) && tc::make_map4(&mCb, a.p.x_dtype, a.C.ptr, dBC4, sC4b, bx4) &&
                     tc::make_map2(&mDm, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, d.Q) &&
                     tc::make_map2(&mDk, a.p.x_dtype, F(w.dCB), d.Q, dcb_rows, 64, 128)) {
-                    CUtensorMap mX128;
-                    if (!no_tile() && map_bshd(&mX128, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128)) {
-                        const size_t smem_f = tc::intra_tile_smem(d.Q);
-                        BISSD_ALLOW(tc::intra_dcb_tile<T>, smem_f);
-                        BISSD_LAUNCH("tc_intra_dcb_tile", launch_pdl(tc::intra_dcb_tile<T>, dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kIntraTileThreads, smem_f, s,
-                            dg, mG, mX128, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
-                            static_cast<void *>(F(w.dCB)), status));
-                        u4_tiles = nlt_tc * nlt_tc;
-                    } else {
-                        const size_t smem_f = tc::intra_grp_smem(d.Q);
-                        BISSD_ALLOW(tc::intra_dcb_grp<T>, smem_f);
-                        BISSD_LAUNCH("tc_intra_dcb_grp", launch_pdl(tc::intra_dcb_grp<T>, dim3(d.b * d.nc * d.G, nlt_tc), tc::kIntraGrpThreads, smem_f, s,
-                            dg, mG, mX, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
-                            static_cast<void *>(F(w.dCB)), status));
-                    }
+                    const size_t smem_f = tc::intra_tile_smem(d.Q);
+                    BISSD_ALLOW(tc::intra_dcb_tile<T>, smem_f);
+                    BISSD_LAUNCH("tc_intra_dcb_tile", launch_pdl(tc::intra_dcb_tile<T>, dim3(d.b * d.nc * d.G, nlt_tc, nlt_tc), tc::kIntraTileThreads, smem_f, s,
+                        dg, mG, mX128, mCB, a.dt_out, a.cs_f, a.cs_b, F(w.u4), (long long)d.b * d.H * d.nc * d.Q,
+                        static_cast<void *>(F(w.dCB)), status));
+                    u4_tiles = nlt_tc * nlt_tc;
                     fused_done = dcb_done = true;
                     bmm_tma = true;
                     use_u4 = true;

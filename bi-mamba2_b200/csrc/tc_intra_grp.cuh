@@ -7,318 +7,34 @@
 //     u_f[j] = (column sum - row sum) of the part of V_h below the diagonal, u_b[j] the same above it - the
 //     differences of the two dominance sums the decay gradient needs (derivation in tc_intra_sums.cuh; cumsum_bwd
 //     scans them).
-// One CTA per (batch, chunk, group, 128-row tile): the 16-bit C.B^T rows of the tile stay in shared memory; for each
-// head g [128 x P] and x [Q x P] arrive by TMA, one tcgen05 chain gives G2 [128 x Q] in tensor memory, the 16 warps
-// weight it (factorised row x column factors away from the diagonal, one ex2 per element only in the strips the
-// diagonal crosses), add it to the dCB tile they keep in registers, and write V as bf16 into shared memory; a second
-// chain with a lower-triangular ones matrix, D[m,s] = sum_{l<=m} V[l,s], yields the column totals (row 127) and their
-// split at the diagonal (D[m, l0+m]).  Row sums are taken over the values as rounded for that chain, so that row and
-// column sums telescope exactly.  The loads of head h+1 are in flight while head h is weighted.
+// One CTA per (batch, chunk, group) and 128 x 128 tile of (l, s), 256 threads, two CTAs per SM: the bf16 C.B^T tile
+// stays in shared memory; for each head g [128 x P] and x [128 x P] arrive by TMA, one tcgen05 chain gives G2 in
+// tensor memory, the warps weight it (factorised row x column factors away from the diagonal, one ex2 per element only
+// in the strips the diagonal crosses), add it to the dCB tile they keep in registers, and write V as bf16 into shared
+// memory - over g and x, which are dead once G2 exists; a second chain with a lower-triangular ones matrix,
+// D[m,s] = sum_{l<=m} V[l,s], yields the column totals (row 127) and, in tiles on the diagonal, their split at the
+// diagonal (D[m,m]).  Row sums are taken over the values as rounded for that chain, so that row and column sums
+// telescope exactly.  While one CTA weights a head the other one's loads and products are in flight.  A tile writes two
+// Q-long vectors (forward / reverse part): + column sums at its columns, - row sums at its rows, zero elsewhere;
+// cumsum_bwd adds the vectors of a chunk's tiles.  Tiles off the diagonal hold one direction only and no mixed strip.
 //
-// Shapes: headdim 64, chunk 128 or 256, 16-bit inputs.  512 threads: warp w owns rows 32 (w & 3) .. and the column
-// quarter w >> 2.
+// Tried and measured at the benchmark shape (this form: 175 us; the two separate kernels it replaces: 138 + 66 us):
+// a 128 x Q tile per CTA with sixteen warps and the loads of the next head in flight (183 us); the 128 x 128 tile
+// with one CTA per SM and every stage of the chain double-buffered (232 us - the kernel is bound by instruction
+// issue, about twenty instructions per element and head, not by the chain's latencies).
+//
+// Shapes: headdim 64, chunk 128 or 256, 16-bit inputs.
 #pragma once
 #include "tc_scan_tma.cuh"
 
 namespace bissd {
 namespace tc {
 
-constexpr int kIntraGrpThreads = 512;
-
 struct IntraGrpShared {
     uint64_t bar_cb, bar_in, bar_m1, bar_m2;
     uint32_t tmem_base;
 };
 
-inline size_t intra_grp_smem(int Q) {
-    // C.B^T rows, g, x, triangular ones, V, two sets of decay tables
-    return 1024 + (size_t)(Q / 64) * 16384 + 16384 + (size_t)Q * 128 + 32768 + 2 * (size_t)(Q / 64) * 8192 + 2 * 6 * (size_t)Q * 4;
-}
-inline bool intra_grp_ok(int P, int Q) { return P == 64 && (Q == 128 || Q == 256) && intra_grp_smem(Q) + 6144 <= 227 * 1024; }
-
-// grid (b*nc*G, Q/128)
-template <class T>
-__global__ void __launch_bounds__(kIntraGrpThreads, 1)
-intra_dcb_grp(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmX,
-              const __grid_constant__ CUtensorMap tmCB, const float *dt_out, const float *cs_f, const float *cs_b,
-              float *u4, long long hq, void *dCB16, int *status) {
-    pdl_begin();
-    extern __shared__ uint8_t dyn[];
-    __shared__ IntraGrpShared sh;
-    __shared__ float rsum[4][2][kTileM];                          // [column quarter][direction][row]
-    __shared__ float dg[kTileM];                                  // D[m, l0 + m]
-    __shared__ float tot[256];                                    // D[127, s]
-    const int Q = d.Q, R = d.R, nsq = Q / 64, qw = Q / 4;         // qw: columns per warp
-    uint8_t *base_sm = smem_align1024(dyn);
-    uint8_t *smCB = base_sm;                                      // nsq slabs [128 x 64] bf16, K-major
-    uint8_t *smG = smCB + nsq * 16384;                            // [128 x 64], K-major
-    uint8_t *smX = smG + 16384;                                   // [Q x 64], K-major
-    uint8_t *smTri = smX + Q * 128;                               // two slabs [128 x 64] bf16, K-major
-    uint8_t *smV = smTri + 32768;                                 // two K slabs of 64 rows, each [64 x Q] bf16 MN-major
-    float *tabs = reinterpret_cast<float *>(smV + 2 * nsq * 8192);   // [2][6][Q]: f2, b2, tf, tb, colF, colB
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
-    const int l0 = blockIdx.y * kTileM;
-    const int quad = warp & 3, cq = warp >> 2;
-    const int r = quad * 32 + lane, l = l0 + r;
-    const int lim = min(Q, d.L - c * Q);
-    const bool row_on = l < lim;
-    const int wl_min = l0 + quad * 32, wl_max = wl_min + 31;      // rows handled by this warp
-    if (warp == 0) tmem_alloc(&sh.tmem_base, 512);
-    auto load_head = [&](int hr) {                                // one thread: g and x of head hr
-        const int h = g * R + hr;
-        mbar_expect_tx(&sh.bar_in, (uint32_t)(16384 + Q * 128));
-        tma_load4(smG, &tmG, 0, h, c * Q + l0, b, &sh.bar_in);
-        tma_load4(smX, &tmX, 0, h, c * Q, b, &sh.bar_in);
-    };
-    if (tid == 32) {                                              // barriers and first loads by the same thread
-        mbar_init(&sh.bar_cb, 1);
-        mbar_init(&sh.bar_in, 1);
-        mbar_init(&sh.bar_m1, 1);
-        mbar_init(&sh.bar_m2, 1);
-        fence_mbar_init();
-        mbar_expect_tx(&sh.bar_cb, (uint32_t)(nsq * 16384));
-        const int row = ((b * d.nc + c) * d.G + g) * Q + l0;
-        for (int k = 0; k < nsq; ++k) tma_load2(smCB + k * 16384, &tmCB, k * 64, row, &sh.bar_cb);
-        load_head(0);
-    }
-    // table entry tid of head hr: inputs into registers (fetch_tab), table written later (write_tab)
-    float pcf = 0.f, pcb = 0.f, pdt = 1.f, pcfr = 0.f, pcbr = 0.f;
-    auto fetch_tab = [&](int hr) {
-        const int h = g * R + hr;
-        const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
-        if (tid < Q) {
-            pcf = cs_f[base + tid];
-            pcb = cs_b[base + tid];
-            pdt = dt_out[base + tid];
-            pcfr = cs_f[base + (tid | 15)];                       // reference columns of the factorised form
-            pcbr = cs_b[base + (tid & ~15)];
-        }
-    };
-    auto write_tab = [&](int hr) {
-        float *t = tabs + (hr & 1) * 6 * Q;
-        if (tid < Q) {
-            const float cf = pcf * 1.4426950408889634f, cb_ = pcb * 1.4426950408889634f;
-            const float lg = __log2f(pdt);                        // -inf on the zero-padded tail: those columns vanish
-            t[tid] = cf;
-            t[Q + tid] = cb_;
-            t[2 * Q + tid] = cf - lg;
-            t[3 * Q + tid] = cb_ - lg;
-            t[4 * Q + tid] = ex2_approx(pcfr * 1.4426950408889634f - (cf - lg));
-            t[5 * Q + tid] = ex2_approx(pcbr * 1.4426950408889634f - (cb_ - lg));
-        }
-    };
-    // the lower-triangular ones matrix A[m,k] = [k <= m] of the column-sum product (two K slabs of 64)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int q = tid + i * kIntraGrpThreads;
-        const int slab = q >> 10, m = (q & 1023) >> 3, cch = q & 7, k0 = slab * 64 + cch * 8;
-        uint32_t wv[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            wv[e] = ((k0 + 2 * e <= m) ? 0x3F80u : 0u) | ((k0 + 2 * e + 1 <= m) ? 0x3F800000u : 0u);
-        *reinterpret_cast<uint4 *>(smTri + slab * 16384 + m * 128 + ((cch ^ (m & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-    }
-    fetch_tab(0);
-    write_tab(0);
-    if (R > 1) fetch_tab(1);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh.tmem_base;
-    const uint32_t tG2 = tmem, tD2 = tmem + 256;
-    auto issue_g2 = [&](int hr) -> bool {                         // thread 0: G2 of head hr
-        if (!mbar_wait(&sh.bar_in, hr & 1)) return false;
-        tc_fence_after();
-        const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, Q);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            umma(tG2, smem_desc(smem_u32(smG) + kk * 32, 16, 1024), smem_desc(smem_u32(smX) + kk * 32, 16, 1024), idesc,
-                 kk > 0 ? 1u : 0u);
-        umma_commit(&sh.bar_m1);
-        return true;
-    };
-    bool ok = true;
-    if (tid == 0) ok = issue_g2(0) && mbar_wait(&sh.bar_cb, 0);
-    float acc[64];                                                // this thread's piece of the dCB tile: row l, qw columns
-#pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    const uint32_t tl = tmem_lane_base(tmem);
-    const int cbeg = cq * qw;
-    uint8_t *vtile = smV + (r >> 6) * nsq * 8192;
-    const int kl = r & 63;
-    auto store_v8 = [&](int jc, uint4 v) {                        // columns 8 jc .. 8 jc + 7 of row l
-        *reinterpret_cast<uint4 *>(vtile + (jc >> 3) * 8192 + (kl >> 3) * 1024 + (kl & 7) * 128 +
-                                   (((jc & 7) ^ (kl & 7)) << 4)) = v;
-    };
-#pragma unroll 1
-    for (int hr = 0; hr < R; ++hr) {
-        if (hr + 1 < R) {
-            write_tab(hr + 1);
-            if (hr + 2 < R) fetch_tab(hr + 2);
-        }
-        ok = mbar_wait_cta(&sh.bar_m1, hr & 1, ok);               // G2 of head hr is in tensor memory (tables visible too)
-        tc_fence_after();
-        if (tid == 0 && ok && hr + 1 < R) load_head(hr + 1);      // g and x of this head have been consumed
-        float rf = 0.f, rb = 0.f;
-        if (ok) {
-            const float *t = tabs + (hr & 1) * 6 * Q;
-            const float *sf = t, *sb = t + Q, *tf = t + 2 * Q, *tb = t + 3 * Q, *colF = t + 4 * Q, *colB = t + 5 * Q;
-            const float fl = sf[min(l, Q - 1)], bl = sb[min(l, Q - 1)];
-#pragma unroll
-            for (int st = 0; st < 4; ++st) {                      // strips of 16 columns (two when the chunk is 128)
-                if (st * 16 >= qw) break;
-                const int c0 = cbeg + st * 16;
-                float v[16], cbv[16], w[16];
-                tmem_ld16(tl + c0, v);
-                {
-                    const uint8_t *rowp = smCB + (c0 >> 6) * 16384 + r * 128;
-                    const int ch = (c0 & 63) >> 3;
-                    float lo[8], hi[8];
-                    unpack8<__nv_bfloat16>(*reinterpret_cast<const uint4 *>(rowp + ((ch ^ (r & 7)) << 4)), lo);
-                    unpack8<__nv_bfloat16>(*reinterpret_cast<const uint4 *>(rowp + (((ch + 1) ^ (r & 7)) << 4)), hi);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        cbv[j] = lo[j];
-                        cbv[8 + j] = hi[j];
-                    }
-                }
-                const int side = (c0 + 15 < wl_min) ? 0 : (c0 > wl_max) ? 1 : 2;   // left of every diagonal / right / mixed
-                if (side != 2) {
-                    const float *col = (side ? colB : colF) + c0;
-                    const float rfac = row_on ? ex2_approx(side ? bl - sb[c0] : fl - sf[c0 + 15]) : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4) {
-                        const float4 cf4 = *reinterpret_cast<const float4 *>(col + j);
-                        const float t0 = v[j] * cf4.x * rfac, t1 = v[j + 1] * cf4.y * rfac, t2 = v[j + 2] * cf4.z * rfac,
-                                    t3 = v[j + 3] * cf4.w * rfac;
-                        acc[st * 16 + j] += t0;
-                        acc[st * 16 + j + 1] += t1;
-                        acc[st * 16 + j + 2] += t2;
-                        acc[st * 16 + j + 3] += t3;
-                        w[j] = t0 * cbv[j];
-                        w[j + 1] = t1 * cbv[j + 1];
-                        w[j + 2] = t2 * cbv[j + 2];
-                        w[j + 3] = t3 * cbv[j + 3];
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int s = c0 + j;
-                        float a = (s <= l) ? fl - tf[s] : bl - tb[s];
-                        if (s == l) a += 1.f;                     // the diagonal counts once per direction in dCB
-                        const float tj = row_on ? v[j] * ex2_approx(a) : 0.f;
-                        acc[st * 16 + j] += tj;
-                        w[j] = (s == l) ? 0.f : tj * cbv[j];      // ... and not at all in the decay gradient
-                    }
-                }
-                const uint4 q0 = make_uint4(pack2<__nv_bfloat16>(w[0], w[1]), pack2<__nv_bfloat16>(w[2], w[3]),
-                                            pack2<__nv_bfloat16>(w[4], w[5]), pack2<__nv_bfloat16>(w[6], w[7]));
-                const uint4 q1 = make_uint4(pack2<__nv_bfloat16>(w[8], w[9]), pack2<__nv_bfloat16>(w[10], w[11]),
-                                            pack2<__nv_bfloat16>(w[12], w[13]), pack2<__nv_bfloat16>(w[14], w[15]));
-                store_v8(c0 >> 3, q0);
-                store_v8((c0 >> 3) + 1, q1);
-                float rq[16];
-                unpack8<__nv_bfloat16>(q0, *reinterpret_cast<float(*)[8]>(&rq[0]));
-                unpack8<__nv_bfloat16>(q1, *reinterpret_cast<float(*)[8]>(&rq[8]));
-                if (side == 0) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) rf += rq[j];
-                } else if (side == 1) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) rb += rq[j];
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        rf += (c0 + j < l) ? rq[j] : 0.f;
-                        rb += (c0 + j > l) ? rq[j] : 0.f;
-                    }
-                }
-            }
-        }
-        rsum[cq][0][r] = rf;
-        rsum[cq][1][r] = rb;
-        fence_async_smem();
-        tc_fence_before();
-        ok = __syncthreads_and(ok);                               // V complete, G2 fully read
-        if (tid == 0 && ok) {
-            tc_fence_after();
-            umma_issue_stage<false, true>(tD2, Q, 1, smTri, smV, 0u);
-            umma_issue_stage<false, true>(tD2, Q, 1, smTri + 16384, smV + nsq * 8192, 1u);
-            umma_commit(&sh.bar_m2);
-            if (hr + 1 < R) ok = issue_g2(hr + 1);                // next head's product queues behind the column sums
-        }
-        ok = mbar_wait_cta(&sh.bar_m2, hr & 1, ok);
-        tc_fence_after();
-        if (ok) {
-            if (cq == (l0 + quad * 32) / qw) {                    // the diagonal element of this thread's row
-                float v[32];
-                tmem_ld32(tl + 256 + l0 + quad * 32, v);
-                float x = 0.f;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) x = (lane == j) ? v[j] : x;
-                dg[r] = x;
-            }
-            if (quad == 3) {                                      // lane 31 of these warps holds row 127
-                for (int c0 = cbeg; c0 < cbeg + qw; c0 += 32) {
-                    float v[32];
-                    tmem_ld32(tl + 256 + c0, v);
-                    if (lane == 31) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) tot[c0 + j] = v[j];
-                    }
-                }
-            }
-        }
-        tc_fence_before();
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (tid < Q) {
-            const int h = g * R + hr;
-            const long long base = ((long long)(b * d.H + h) * d.nc + c) * Q;
-            const int s = tid, m = s - l0;
-            const bool in = m >= 0 && m < kTileM;
-            const float T_ = tot[s];
-            const float above = in ? dg[m] : 0.f;                 // sum over rows l < s of column s
-            const float Cf = in ? T_ - above : (s < l0 ? T_ : 0.f);
-            const float Cb = in ? above : (s >= l0 + kTileM ? T_ : 0.f);
-            const float Rf = in ? (rsum[0][0][m] + rsum[1][0][m]) + (rsum[2][0][m] + rsum[3][0][m]) : 0.f;
-            const float Rb = in ? (rsum[0][1][m] + rsum[1][1][m]) + (rsum[2][1][m] + rsum[3][1][m]) : 0.f;
-            u4[(blockIdx.y * 2 + 0) * hq + base + s] = Cf - Rf;
-            u4[(blockIdx.y * 2 + 1) * hq + base + s] = Cb - Rb;
-            if (gridDim.y == 1) {
-                u4[2 * hq + base + s] = 0.f;
-                u4[3 * hq + base + s] = 0.f;
-            }
-        }
-        // rsum / dg / tot are next written after two more CTA-wide barriers (G2 wait, V barrier): no extra sync needed
-    }
-    if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
-    if (ok && l < Q) {                                            // the rounded dCB tile; zero outside the sequence
-        T *out = static_cast<T *>(dCB16) + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + cbeg;
-#pragma unroll
-        for (int j0 = 0; j0 < 64; j0 += 8) {
-            if (j0 >= qw) break;
-            float o[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = (l < lim && cbeg + j0 + i < lim) ? acc[j0 + i] : 0.f;
-            *reinterpret_cast<uint4 *>(out + j0) = pack8<T>(o);
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-
-// ---------------------------------------------------------------------------------------------------------------
-// The same work on 128 x 128 tiles of (l, s): grid (b*nc*G, Q/128 row tiles, Q/128 column tiles), 256 threads, two
-// CTAs per SM - while one CTA weights a head the other one's loads and products are in flight, which a single
-// resident CTA can only get from its own sixteen warps.  Shared memory per CTA is kept under half an SM's by letting
-// V take the place of g and x (dead once G2 is in tensor memory) and by a single set of decay tables.  A tile writes
-// two Q-long vectors (forward / reverse part): + column sums at its columns, - row sums at its rows, zero elsewhere;
-// cumsum_bwd adds the vectors of a chunk's tiles.  Tiles off the diagonal hold one direction only and no mixed strip.
 constexpr int kIntraTileThreads = 256;
 inline size_t intra_tile_smem(int Q) { return 1024 + 32768 + 32768 + 32768 + 6 * (size_t)Q * 4; }
 inline bool intra_tile_ok(int P, int Q) { return P == 64 && (Q == 128 || Q == 256); }
