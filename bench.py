@@ -124,9 +124,9 @@ def kernel_model(name, cfg, batch=None):
         "cumsum_fwd": (0, DTB + 3 * HQ),
         "chunk_state": (state_f, X + BC + 3 * HQ + 2 * ST32),
         "state_passing_fwd": (0, 2 * ST32 + 2 * ST16),
-        # launched twice per step under one name: the forward writes one 16-bit copy, the backward a transposed
-        # 16-bit copy and an fp32 strip-major one - the mean of the two launches
-        "bmm_cb": (tg * 2 * Q * Q * N, 2 * BC + CB16 + CB32 // 2),
+        # launched twice per step under one name: the forward writes one 16-bit copy, the backward that copy and its
+        # transpose - the mean of the two launches
+        "bmm_cb": (tg * 2 * Q * Q * N, 2 * BC + CB16 + CB16 // 2),
         "chunk_scan": (state_f + intra_f, X * (2 + 2 * zf) + BC + CB16 + 2 * ST16 + 3 * HQ),
         "gate_bwd": (0, 5 * X),
         "dstates": (state_f, X + BC + 2 * HQ + 2 * ST32),
@@ -136,6 +136,9 @@ def kernel_model(name, cfg, batch=None):
         "dbc_accum": (2 * state_f, 2 * X + 4 * ST16 + 3 * HQ + 4 * BC),
         "dcb": (intra_f, 2 * X + 3 * HQ + CB16),
         "intra_sums": (intra_f, 2 * X + 3 * HQ + CB32 + 4 * HQ),
+        # dCB and the intra-chunk decay gradients from one g.x^T product per head: reads g, x, the bf16 C.B^T tile and
+        # the three per-position vectors; writes the 16-bit dCB and eight per-position vectors
+        "intra_dcb_tile": (intra_f, 2 * X + 2 * CB16 + 11 * HQ),
         "bmm_bwd": (tg * 4 * Q * Q * N, CB16 + 2 * BC + 4 * BC + 2 * BC),
         "cumsum_bwd": (0, 2 * DTB + 10 * HQ),
         "final_reduce": (0, 4 * b * nc * H * (2 + 8 * P)),
@@ -162,6 +165,9 @@ def _source_hash(*files):
 # kernel's source file(s) at capture time; when the source has changed since, `traffic` prints as null instead of a
 # stale figure.  {kernel: (bytes per launch at batch 2, source files, hash)}
 NCU_TRAFFIC_B2 = {
+    "tc_intra_dcb_tile": (28.53e6, ("tc_intra_grp.cuh",), "8edeeff43c51430b"),
+    "tc_dx_ws": (42.54e6, ("tc_scan_ws.cuh",), "5d856adde6413d4a"),
+    "tc_chunk_scan_ws": (43.61e6, ("tc_scan_ws.cuh",), "5d856adde6413d4a"),
 }
 
 
