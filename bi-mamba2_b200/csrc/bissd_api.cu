@@ -527,6 +527,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_tile has been written
     int u4_tiles = 2;                                            // (u_f, u_b) vector pairs per chunk in u4
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
+    bool dd_compact = false;                                     // per-head D from the persistent dx kernel: dd_slots scalars, no channel axis
     if constexpr (TcKernels<T>::available) {
         if (tcp) {
             nlt = nlt_tc;
@@ -599,6 +600,10 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
 #undef BISSD_DX_WS
                     dx_done = true;
                     dd_slots = nlt_tc * 4;
+                    if (d.has_D && !d.D_hdim) {
+                        dd_slots = nlt_tc * 8;                       // one scalar per epilogue warp and tile
+                        dd_compact = true;
+                    }
                 }
             }
             if (!dx_done) {
@@ -832,7 +837,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         use_u4 ? F(w.u4) : nullptr, u4_tiles, F(w.dTpart), pass_nblk, nsplit, a.ddt,
         F(w.dApart), F(w.dbiaspart)));
     BISSD_LAUNCH("final_reduce", launch_pdl(simt::final_reduce<1024>, d.H, 1024, 0, s, 
-        d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, a.dA, d.has_bias ? a.ddt_bias : nullptr,
+        d, F(w.dApart), F(w.dbiaspart), d.has_D ? F(w.dDpart) : nullptr, dd_slots ? dd_slots : nlt, dd_compact ? 1 : 0, a.dA, d.has_bias ? a.ddt_bias : nullptr,
         d.has_D ? a.dD : nullptr));
     return BISSD_OK;
 }

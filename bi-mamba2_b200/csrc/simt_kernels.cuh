@@ -942,9 +942,11 @@ __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt
 
 // ---------------------------------------------------------------------------------------------------------
 // Fixed-order reduction of the per-block partials into dA (H), ddt_bias (H) and dD (H or H*P).  grid (H), NT threads.
+// `compact` (per-head D only): dDpart holds nlt scalars per (batch, chunk, head) instead of nlt rows of P channel sums.
 template <int NT>
 __global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, const float *dbiaspart,
-                                                   const float *dDpart, int nlt, float *dA, float *ddt_bias, float *dD) {
+                                                   const float *dDpart, int nlt, int compact, float *dA, float *ddt_bias,
+                                                   float *dD) {
     pdl_begin();
     __shared__ float red[NT];
     const int h = blockIdx.x;
@@ -970,7 +972,21 @@ __global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, 
     }
     if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = red[0];
     __syncthreads();
-    if (dD && dDpart) {
+    if (dD && dDpart && compact) {
+        float sd = 0.f;                                          // fixed order: strided per thread, then the tree below
+        const int n = nbc * nlt;
+        for (int i = threadIdx.x; i < n; i += NT) {
+            const int bc = i / nlt, t = i - bc * nlt;
+            sd += dDpart[((long long)bc * d.H + h) * nlt + t];
+        }
+        red[threadIdx.x] = sd;
+        __syncthreads();
+        for (int o = NT / 2; o > 0; o >>= 1) {
+            if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) dD[h] = red[0];
+    } else if (dD && dDpart) {
         // rows of the partial buffer are split over NT / P thread groups, then the groups are added in a fixed order
         const int rows = nbc * nlt;
         const int ngrp = d.P <= NT ? NT / d.P : 1;

@@ -311,7 +311,8 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
         tc_fence_after();
         const float wf = live ? __expf(e1) : 0.f, wb = live ? __expf(e2) : 0.f;
         const uint32_t acc = tl + buf * 3 * P + ch;
-        float rs = 0.f, rsf = 0.f, rsb = 0.f;
+        float rs = 0.f, rsf = 0.f, rsb = 0.f, gxs = 0.f;
+        const bool d_cols = d.has_D && d.D_hdim;                 // per-(head, channel) D: column sums of g x are needed
         const long long dslot = ((long long)(it.b * d.nc + it.c) * d.H + it.h) * (nrt * 4) + it.rt * 4 + quarter;
         uint4 held = zero8();
 #pragma unroll
@@ -345,7 +346,11 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
             } else {
                 held = pack8<T>(o);
             }
-            if (d.has_D) {                                       // column sums of g x over this warp's 32 rows
+            if (d.has_D && !d_cols) {                            // per-head D: only the total of g x matters
+#pragma unroll
+                for (int j = 0; j < 8; ++j) gxs += gx[j];
+            }
+            if (d_cols) {                                        // column sums of g x over this warp's 32 rows
                 ws_fold<8>(gx, lane);
                 ws_fold<4>(gx, lane);
                 ws_fold<2>(gx, lane);
@@ -354,6 +359,11 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
                 if (lane < 8) a.dDpart[dslot * P + ch + c0 + lane] = v;
             }
+        }
+        if (d.has_D && !d_cols) {                                // one partial per warp and tile, in a compact array
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) gxs += __shfl_xor_sync(0xffffffffu, gxs, o);
+            if (lane == 0) a.dDpart[dslot * 2 + half] = gxs;
         }
         if (half == 1) {
             rowred[slot][0][r] = rs;
