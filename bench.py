@@ -542,27 +542,30 @@ def run_ours(args, cfg):
 
     # ---- the same step replayed from a CUDA graph (one launch per step on the host side): what the kernels alone
     # take when the host is out of the way.  Reported beside the headline, never instead of it.
-    graph_replay = None
-    try:
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
+    def graph_leg(fn, tokens):
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    fn()
+            main.wait_stream(side)
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                fn()
             for _ in range(3):
-                step()
-        main.wait_stream(side)
-        torch.cuda.synchronize()
-        cg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(cg):
-            step()
-        for _ in range(3):
-            cg.replay()
-        g_ms, _, g_host = timed(cg.replay, args.steps)
-        graph_replay = dict(ms_per_step=g_ms / args.steps, tokens_per_s=tokens_per_step * args.steps / (g_ms * 1e-3),
-                            host_enqueue_ms_per_step=g_host / args.steps)
-        del cg
-    except Exception as e:                                       # capture refused: report why, keep the run
-        graph_replay = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
-        torch.cuda.synchronize()
+                cg.replay()
+            g_ms, _, g_host = timed(cg.replay, args.steps)
+            res = dict(ms_per_step=g_ms / args.steps, tokens_per_s=tokens * args.steps / (g_ms * 1e-3),
+                       host_enqueue_ms_per_step=g_host / args.steps)
+            del cg
+            return res
+        except Exception as e:                                   # capture refused: report why, keep the run
+            torch.cuda.synchronize()
+            return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+    graph_replay = graph_leg(step, tokens_per_step)
 
     strong = None
     seqpar = None
@@ -578,12 +581,17 @@ def run_ours(args, cfg):
                 sstep()
             s_ms, s_my, s_host = timed(sstep, args.steps)
             s_tps = cfg["batch"] * cfg["seqlen"] * args.steps / (s_ms * 1e-3)
+            s_graph = graph_leg(sstep, cfg["batch"] * cfg["seqlen"])
+            if "tokens_per_s" in s_graph:
+                s_graph["efficiency"] = s_graph["tokens_per_s"] / value
             strong = dict(tokens_per_s=s_tps, ms_per_step=s_ms / args.steps, rows_per_rank=rows,
-                          global_batch=cfg["batch"], efficiency=s_tps / value,
+                          global_batch=cfg["batch"], efficiency=s_tps / value, cuda_graph_replay=s_graph,
                           per_rank_ms=gather_floats(s_my / args.steps),
                           host_enqueue_ms_per_step=gather_floats(s_host / args.steps),
                           note="efficiency = tokens/s(N GPUs, global batch 8) / (N x tokens/s(1 GPU, batch 8)), the "
-                               "1-GPU figure being value / N of this run's weak leg (every rank ran batch 8 alone)")
+                               "1-GPU figure being value / N of this run's weak leg (every rank ran batch 8 alone); "
+                               "cuda_graph_replay = the same split step replayed from a CUDA graph (with few rows per "
+                               "rank the eager step is bound by the host's enqueue time, see host_enqueue_ms_per_step)")
             del sstep, mine, full
         seqpar = seq_parallel_leg(args, dev, rank, world, timed, gather_floats, warmup)
 

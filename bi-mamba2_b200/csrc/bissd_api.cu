@@ -412,10 +412,11 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                     if (tc::make_map4(&mC, a.p.x_dtype, a.C.ptr, dC, sC, bC) && tc::make_map4(&mX, a.p.x_dtype, a.x.ptr, dX, sX, bX) &&
                         tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
                         tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P)) {
-                        const size_t smem_t = tc::scan_tma_smem(d.P, d.N, d.Q);
+                        const int rounds = tc::scan_tma_rounds(d.P, d.N, d.Q);
+                        const size_t smem_t = tc::scan_tma_smem(d.P, d.N, d.Q, rounds);
                         BISSD_ALLOW(tc::chunk_scan_tma<T>, smem_t);
                         BISSD_LAUNCH("tc_chunk_scan_tma", tc::chunk_scan_tma<T><<<dim3(bch, ceil_div(d.Q, tc::kTileM)), tc::kThreads, smem_t, s>>>(
-                            d, mC, mSf, mSb, mX, x, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, mview_of(a.out), mview_of(a.out_x), status));
+                            d, mC, mSf, mSb, mX, x, z, a.D, a.dt_out, a.cs_f, a.cs_b, CB, mview_of(a.out), mview_of(a.out_x), rounds, status));
                         tma_done = true;
                     }
                 }
@@ -623,11 +624,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                 if (tc::make_map4(&mB, a.p.x_dtype, a.B.ptr, dB4, sB4, bB4) && tc::make_map4(&mG, a.p.x_dtype, gv.ptr, dG4, sG4, bG4) &&
                     tc::make_map2(&mEf, a.p.x_dtype, e16, d.N, rows, 64, d.P) &&
                     tc::make_map2(&mEb, a.p.x_dtype, e16 + rows * d.N * 2, d.N, rows, 64, d.P)) {
-                    const size_t smem_t = tc::dx_tma_smem(d.P, d.N, d.Q);
+                    const int rounds = tc::scan_tma_rounds(d.P, d.N, d.Q);
+                    const size_t smem_t = tc::dx_tma_smem(d.P, d.N, d.Q, rounds);
                     BISSD_ALLOW(tc::dx_tma<T>, smem_t);
                     BISSD_LAUNCH("tc_dx_tma", tc::dx_tma<T><<<dim3(bch, nlt_tc), tc::kThreads, smem_t, s>>>(
                         d, mB, mEf, mEb, mG, x, gv, a.D, a.dt_out, a.cs_f, a.cs_b, F(w.cbt), a.dx, F(w.ddt_out), F(w.nf), F(w.nb),
-                        F(w.dDpart), status));
+                        F(w.dDpart), rounds, status));
                     dx_done = true;
                 }
             }

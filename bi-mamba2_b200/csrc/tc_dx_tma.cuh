@@ -40,8 +40,9 @@ __global__ void __launch_bounds__(256) gate_bwd(Dims d, View dout, View z, View 
     *reinterpret_cast<uint4 *>(static_cast<T *>(dz) + o) = pack8<T>(dzv);
 }
 
-inline size_t dx_tma_smem(int P, int N, int Q) {
-    return 1024 + (size_t)(N / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 + (size_t)(P / 64) * Q * 128 + 2 * Q * 4;
+inline size_t dx_tma_smem(int P, int N, int Q, int rounds = 1) {   // rounds: see scan_tma_rounds
+    const size_t nsr = (size_t)(N / 64) / rounds;
+    return 1024 + nsr * 16384 + 2 * nsr * P * 128 + (size_t)(P / 64) * Q * 128 + 2 * Q * 4;
 }
 
 // grid (b*nc*H, Q/128).  g: contiguous (b,L,H,P) gated output gradient (dout itself when there is no z).
@@ -50,18 +51,18 @@ __global__ void __launch_bounds__(kThreads, 2)
 dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmEf,
        const __grid_constant__ CUtensorMap tmEb, const __grid_constant__ CUtensorMap tmG, View x, View g, const float *D,
        const float *dt_out, const float *cs_f, const float *cs_b, const float *CBt, void *dx, float *ddt_out, float *nf,
-       float *nb, float *dDpart, int *status) {
+       float *nb, float *dDpart, int rounds, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ ScanShared sh;
     __shared__ float rowred[3][kTileM];
     __shared__ float colred[4][128];
     const int P = d.P, N = d.N, Q = d.Q;
-    const int nsl = N / 64, npb = P / 64;
+    const int nsr = N / 64 / rounds, npb = P / 64;            // slabs of 64 dstate columns resident at a time
     uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smB = base_sm;
-    uint8_t *smEf = smB + nsl * 16384;
-    uint8_t *smEb = smEf + nsl * P * 128;
-    uint8_t *smG = smEb + nsl * P * 128;
+    uint8_t *smEf = smB + nsr * 16384;
+    uint8_t *smEb = smEf + nsr * P * 128;
+    uint8_t *smG = smEb + nsr * P * 128;
     float *f2 = reinterpret_cast<float *>(smG + npb * Q * 128), *b2 = f2 + Q;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
@@ -75,6 +76,7 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
         mbar_init(&sh.bar_cs, 1);
         mbar_init(&sh.bar_x, 1);
         mbar_init(&sh.bar_st, 1);
+        mbar_init(&sh.bar_mid, 1);
         mbar_init(&sh.free_bar[0], 1);
         mbar_init(&sh.free_bar[1], 1);
         mbar_init(&sh.done_bar, 1);
@@ -86,13 +88,17 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     const int tile = (b * d.nc + c) * d.H + h;
-    if (tid == 0) {
-        mbar_expect_tx(&sh.bar_cs, (uint32_t)(nsl * 16384 + 2 * nsl * P * 128));
-        for (int j = 0; j < nsl; ++j) {
-            tma_load4(smB + j * 16384, &tmB, j * 64, grp, c * Q + l0, b, &sh.bar_cs);
-            tma_load2(smEf + j * P * 128, &tmEf, j * 64, tile * P, &sh.bar_cs);
-            tma_load2(smEb + j * P * 128, &tmEb, j * 64, tile * P, &sh.bar_cs);
+    auto load_round = [&](int rd) {                             // thread 0: one dstate share of B and both state gradients
+        mbar_expect_tx(&sh.bar_cs, (uint32_t)(nsr * 16384 + 2 * nsr * P * 128));
+        for (int j = 0; j < nsr; ++j) {
+            const int n0 = (rd * nsr + j) * 64;
+            tma_load4(smB + j * 16384, &tmB, n0, grp, c * Q + l0, b, &sh.bar_cs);
+            tma_load2(smEf + j * P * 128, &tmEf, n0, tile * P, &sh.bar_cs);
+            tma_load2(smEb + j * P * 128, &tmEb, n0, tile * P, &sh.bar_cs);
         }
+    };
+    if (tid == 0) {
+        load_round(0);
         mbar_expect_tx(&sh.bar_x, (uint32_t)(npb * Q * 128));
         for (int j = 0; j < npb; ++j) tma_load4(smG + j * Q * 128, &tmG, j * 64, h, c * Q, b, &sh.bar_x);
     }
@@ -149,19 +155,28 @@ dx_tma(Dims d, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ 
     if (kStageK < Q) load_raw(kStageK);
     bool ok = true;
     if (tid == 0) {
-        if (mbar_wait(&sh.bar_cs, 0)) {
+        const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, P);
+        for (int rd = 0; rd < rounds; ++rd) {                   // bar_cs completes once per round, bar_st with the last one only
+            if (rd > 0) {                                       // the MMAs of the round before have read the tiles
+                if (!mbar_wait(&sh.bar_mid, (rd - 1) & 1)) {
+                    sh.fail = 1;
+                    break;
+                }
+                load_round(rd);
+            }
+            if (!mbar_wait(&sh.bar_cs, rd & 1)) {
+                sh.fail = 1;
+                break;
+            }
             tc_fence_after();
-            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, P);
             for (int dir = 0; dir < 2; ++dir)
-                for (int j = 0; j < nsl; ++j)
+                for (int j = 0; j < nsr; ++j)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         umma(tmem + dir * P, smem_desc(smem_u32(smB + j * 16384) + kk * 32, 16, 1024),
                              smem_desc(smem_u32((dir ? smEb : smEf) + j * P * 128) + kk * 32, 16, 1024), idesc,
-                             (j > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&sh.bar_st);
-        } else {
-            sh.fail = 1;
+                             (rd > 0 || j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(rd + 1 < rounds ? &sh.bar_mid : &sh.bar_st);
         }
     }
     uint32_t it = 0;

@@ -60,13 +60,16 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
     float *tab = reinterpret_cast<float *>(smTri + 32768);        // [6][Q]: f2, b2, tf, tb, colF, colB
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = blockIdx.x % d.G, c = (blockIdx.x / d.G) % d.nc, b = blockIdx.x / (d.G * d.nc);
-    const int l0 = blockIdx.y * kTileM, s0 = blockIdx.z * kTileM;
+    // Launch order (x, then y, then z) puts the tiles on the diagonal first: they carry the dearer strips, and the
+    // second CTA an SM receives is then mostly one off the diagonal.
+    const int ty = blockIdx.y ^ blockIdx.z, tz = blockIdx.y;
+    const int l0 = ty * kTileM, s0 = tz * kTileM;
     const int quad = warp & 3, chalf = warp >> 2;
     const int r = quad * 32 + lane, l = l0 + r;
     const int lim = min(Q, d.L - c * Q);
     const bool row_on = l < lim;
     const int wl_min = l0 + quad * 32, wl_max = wl_min + 31;      // rows handled by this warp
-    const int tile = blockIdx.y * gridDim.z + blockIdx.z;
+    const int tile = ty * gridDim.z + tz;
     if (warp == 0) tmem_alloc(&sh.tmem_base, 256);
     auto load_head = [&](int hr) {                                // one thread: g and x of head hr
         const int h = g * R + hr;
@@ -145,7 +148,7 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
     const uint32_t tl = tmem_lane_base(tmem);
-    const int cbeg = chalf * 64;                                  // first of this thread's columns, within the tile
+    const int cbeg = chalf * 64;                                  // first column of this warp's share of the read-out of row 127
     uint8_t *vtile = smV + (r >> 6) * 16384;
     const int kl = r & 63;
     auto store_v8 = [&](int jc, uint4 v) {                        // tile columns 8 jc .. 8 jc + 7 of row l
@@ -161,8 +164,9 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
             const float *sf = tab, *sb = tab + Q, *tf = tab + 2 * Q, *tb = tab + 3 * Q, *colF = tab + 4 * Q, *colB = tab + 5 * Q;
             const float fl = sf[min(l, Q - 1)], bl = sb[min(l, Q - 1)];
 #pragma unroll
-            for (int st = 0; st < 4; ++st) {                      // strips of 16 columns
-                const int ct = cbeg + st * 16, c0 = s0 + ct;      // within the tile / within the chunk
+            for (int st = 0; st < 4; ++st) {                      // strips of 16 columns, dealt alternately to the two
+                // warps of a row quarter: in a tile on the diagonal each then holds one of the two strips the diagonal crosses
+                const int ct = (st * 2 + chalf) * 16, c0 = s0 + ct;   // within the tile / within the chunk
                 float v[16], cbv[16], w[16];
                 tmem_ld16(tl + ct, v);
                 {
@@ -250,7 +254,7 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
         tc_fence_after();
         if (tid == 0 && ok && hr + 1 < R) load_head(hr + 1);
         if (ok) {
-            if (blockIdx.y == blockIdx.z && chalf == (quad >> 1)) {   // the diagonal element of this thread's row
+            if (ty == tz && chalf == (quad >> 1)) {   // the diagonal element of this thread's row
                 float v[32];
                 tmem_ld32(tl + 128 + quad * 32, v);
                 float x = 0.f;
@@ -282,11 +286,11 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
             float uf = 0.f, ub = 0.f;
             if (incol) {
                 const float T_ = tot[mc];
-                if (blockIdx.y == blockIdx.z) {
+                if (ty == tz) {
                     const float above = dg[mc];                   // rows l < s of column s
                     uf += T_ - above;
                     ub += above;
-                } else if (blockIdx.y > blockIdx.z) {
+                } else if (ty > tz) {
                     uf += T_;                                     // every row of the tile lies below its columns
                 } else {
                     ub += T_;
@@ -302,13 +306,14 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
     }
     if (!ok && tid == 0) atomicExch(status, kErrMmaTimeout);
     if (ok && l < Q) {                                            // the rounded dCB tile; zero outside the sequence
-        T *out = static_cast<T *>(dCB16) + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0 + cbeg;
+        T *out = static_cast<T *>(dCB16) + ((long long)(b * d.nc + c) * d.G + g) * Q * Q + (long long)l * Q + s0;
 #pragma unroll
         for (int j0 = 0; j0 < 64; j0 += 8) {
+            const int col = ((j0 >> 4) * 2 + chalf) * 16 + (j0 & 8);   // acc[16 st + j] is tile column 16 (2 st + chalf) + j
             float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = (l < lim && s0 + cbeg + j0 + i < lim) ? acc[j0 + i] : 0.f;
-            *reinterpret_cast<uint4 *>(out + j0) = pack8<T>(o);
+            for (int i = 0; i < 8; ++i) o[i] = (l < lim && s0 + col + i < lim) ? acc[j0 + i] : 0.f;
+            *reinterpret_cast<uint4 *>(out + col) = pack8<T>(o);
         }
     }
     tc_fence_before();

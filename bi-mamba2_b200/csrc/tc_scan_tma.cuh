@@ -17,35 +17,45 @@ namespace bissd {
 namespace tc {
 
 struct ScanShared {
-    uint64_t bar_cs, bar_x, bar_st, free_bar[2], done_bar;
+    uint64_t bar_cs, bar_x, bar_st, bar_mid, free_bar[2], done_bar;   // bar_mid: every round of the state products but the last
     uint32_t tmem_base;
     int fail;
 };
 
-inline size_t scan_tma_smem(int P, int N, int Q) {
-    return 1024 + (size_t)(N / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 + (size_t)(P / 64) * Q * 128 + 4 * Q * 4;
+// The operands of the two state products (C or B rows and both state tiles) take dstate/64 slabs each.  Where all of
+// them do not fit beside x (headdim 128 with dstate 256), they come in `rounds` = 2 halves of dstate, the second
+// loaded into the same buffers once the MMAs of the first have read them.
+inline size_t scan_tma_smem(int P, int N, int Q, int rounds = 1) {
+    const size_t nsr = (size_t)(N / 64) / rounds;
+    return 1024 + nsr * 16384 + 2 * nsr * P * 128 + (size_t)(P / 64) * Q * 128 + 4 * Q * 4;
 }
-inline bool scan_tma_ok(int P, int N, int Q) {
-    if (P % 64 || N % 64 || (Q != 128 && Q != 256) || P > 128 || N > 256) return false;
-    if ((size_t)(N / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 < 32768) return false;   // room for the two M stages
-    return scan_tma_smem(P, N, Q) <= 200 * 1024;
+inline int scan_tma_rounds(int P, int N, int Q) {                // 0: shape not supported
+    if (P % 64 || N % 64 || (Q != 128 && Q != 256) || P > 128 || N > 256) return 0;
+    for (int rounds = 1; rounds <= 2; ++rounds) {
+        if ((N / 64) % rounds) continue;
+        const size_t nsr = (size_t)(N / 64) / rounds;
+        if (nsr * 16384 + 2 * nsr * P * 128 < 32768) continue;       // room for the two M stages
+        if (scan_tma_smem(P, N, Q, rounds) <= 200 * 1024) return rounds;
+    }
+    return 0;
 }
+inline bool scan_tma_ok(int P, int N, int Q) { return scan_tma_rounds(P, N, Q) > 0; }
 
 template <class T>
 __global__ void __launch_bounds__(kThreads, 2)
 chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmSf,
                const __grid_constant__ CUtensorMap tmSb, const __grid_constant__ CUtensorMap tmX, View x, View z,
                const float *D, const float *dt_out, const float *cs_f, const float *cs_b, const float *CB, MutView out,
-               MutView out_x, int *status) {
+               MutView out_x, int rounds, int *status) {
     extern __shared__ uint8_t dyn[];
     __shared__ ScanShared sh;
     const int P = d.P, N = d.N, Q = d.Q;
-    const int nsl = N / 64, npb = P / 64;
+    const int nsr = N / 64 / rounds, npb = P / 64;            // slabs of 64 dstate columns resident at a time
     uint8_t *base_sm = smem_align1024(dyn);
-    uint8_t *smC = base_sm;                                   // nsl slabs [128 x 64]
-    uint8_t *smSf = smC + nsl * 16384;                        // nsl slabs [P x 64]
-    uint8_t *smSb = smSf + nsl * P * 128;
-    uint8_t *smX = smSb + nsl * P * 128;                      // npb blocks [Q x 64]
+    uint8_t *smC = base_sm;                                   // nsr slabs [128 x 64]
+    uint8_t *smSf = smC + nsr * 16384;                        // nsr slabs [P x 64]
+    uint8_t *smSb = smSf + nsr * P * 128;
+    uint8_t *smX = smSb + nsr * P * 128;                      // npb blocks [Q x 64]
     float *f2 = reinterpret_cast<float *>(smX + npb * Q * 128), *b2 = f2 + Q, *tf = b2 + Q, *tb = tf + Q;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % d.H, c = (blockIdx.x / d.H) % d.nc, b = blockIdx.x / (d.H * d.nc);
@@ -59,6 +69,7 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
         mbar_init(&sh.bar_cs, 1);
         mbar_init(&sh.bar_x, 1);
         mbar_init(&sh.bar_st, 1);
+        mbar_init(&sh.bar_mid, 1);
         mbar_init(&sh.free_bar[0], 1);
         mbar_init(&sh.free_bar[1], 1);
         mbar_init(&sh.done_bar, 1);
@@ -70,13 +81,17 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     const int tile = (b * d.nc + c) * d.H + h;
-    if (tid == 0) {
-        mbar_expect_tx(&sh.bar_cs, (uint32_t)(nsl * 16384 + 2 * nsl * P * 128));
-        for (int j = 0; j < nsl; ++j) {
-            tma_load4(smC + j * 16384, &tmC, j * 64, g, c * Q + l0, b, &sh.bar_cs);
-            tma_load2(smSf + j * P * 128, &tmSf, j * 64, tile * P, &sh.bar_cs);
-            tma_load2(smSb + j * P * 128, &tmSb, j * 64, tile * P, &sh.bar_cs);
+    auto load_round = [&](int rd) {                             // thread 0: one dstate share of C and both states
+        mbar_expect_tx(&sh.bar_cs, (uint32_t)(nsr * 16384 + 2 * nsr * P * 128));
+        for (int j = 0; j < nsr; ++j) {
+            const int n0 = (rd * nsr + j) * 64;
+            tma_load4(smC + j * 16384, &tmC, n0, g, c * Q + l0, b, &sh.bar_cs);
+            tma_load2(smSf + j * P * 128, &tmSf, n0, tile * P, &sh.bar_cs);
+            tma_load2(smSb + j * P * 128, &tmSb, n0, tile * P, &sh.bar_cs);
         }
+    };
+    if (tid == 0) {
+        load_round(0);
         mbar_expect_tx(&sh.bar_x, (uint32_t)(npb * Q * 128));
         for (int j = 0; j < npb; ++j) tma_load4(smX + j * Q * 128, &tmX, j * 64, h, c * Q, b, &sh.bar_x);
     }
@@ -137,19 +152,28 @@ chunk_scan_tma(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_con
     if (kStageK < Q) load_raw(kStageK);
     bool ok = true;
     if (tid == 0) {                                             // the two state products, straight from the TMA tiles
-        if (mbar_wait(&sh.bar_cs, 0)) {
+        const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, P);
+        for (int rd = 0; rd < rounds; ++rd) {                   // bar_cs completes once per round, bar_st with the last one only
+            if (rd > 0) {                                       // the MMAs of the round before have read the tiles
+                if (!mbar_wait(&sh.bar_mid, (rd - 1) & 1)) {
+                    sh.fail = 1;
+                    break;
+                }
+                load_round(rd);
+            }
+            if (!mbar_wait(&sh.bar_cs, rd & 1)) {
+                sh.fail = 1;
+                break;
+            }
             tc_fence_after();
-            const uint32_t idesc = instr_desc(AbFmt<T>::v, false, false, P);
             for (int dir = 0; dir < 2; ++dir)
-                for (int j = 0; j < nsl; ++j)
+                for (int j = 0; j < nsr; ++j)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         umma(tmem + dir * P, smem_desc(smem_u32(smC + j * 16384) + kk * 32, 16, 1024),
                              smem_desc(smem_u32((dir ? smSb : smSf) + j * P * 128) + kk * 32, 16, 1024), idesc,
-                             (j > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&sh.bar_st);
-        } else {
-            sh.fail = 1;
+                             (rd > 0 || j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(rd + 1 < rounds ? &sh.bar_mid : &sh.bar_st);
         }
     }
     uint32_t it = 0;

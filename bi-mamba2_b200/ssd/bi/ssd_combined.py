@@ -57,12 +57,18 @@ def _problem(x, dt, B, chunk_size, D, z, dt_bias, dt_softplus, dt_min, dt_max):
                          float(dt_min), float(dt_max))
 
 
+_ws_bytes = {}                                    # problem fields -> (forward bytes, backward bytes)
+
+
 def _workspace(problem, device, which):
-    lib = _cabi.load()
-    import ctypes
-    f, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
-    _cabi.check(lib.bissd_workspace_bytes(ctypes.byref(problem), ctypes.byref(f), ctypes.byref(b)))
-    nbytes = f.value if which == "fwd" else b.value
+    key = tuple(getattr(problem, name) for name, _ in problem._fields_)
+    sizes = _ws_bytes.get(key)
+    if sizes is None:
+        import ctypes
+        f, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
+        _cabi.check(_cabi.load().bissd_workspace_bytes(ctypes.byref(problem), ctypes.byref(f), ctypes.byref(b)))
+        sizes = _ws_bytes[key] = (f.value, b.value)
+    nbytes = sizes[0] if which == "fwd" else sizes[1]
     return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
 
 
@@ -73,7 +79,11 @@ def _require_cuda(*tensors):
 
 
 def _f32c(t):
-    return None if t is None else t.detach().to(torch.float32).contiguous()
+    if t is None:
+        return None
+    if t.dtype is torch.float32 and t.is_contiguous():
+        return t                                  # only its address is taken: no detach / cast / copy needed
+    return t.detach().to(torch.float32).contiguous()
 
 
 def _inner_contig(t):
