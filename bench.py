@@ -749,11 +749,38 @@ def run_layer(args):
     _cabi.trace_enable(False)
     kernels = {k: {"us_per_step": v[0] / steps * 1000.0, "launches_per_step": v[1] / steps}
                for k, v in sorted(tr.items(), key=lambda kv: -kv[1][0])}
+
+    def held_between_passes(m):
+        """Bytes a layer keeps allocated between its forward and its backward pass (beyond input and parameters)."""
+        torch.cuda.synchronize()
+        base = torch.cuda.memory_allocated()
+        out = m(u)
+        torch.cuda.synchronize()
+        held = torch.cuda.memory_allocated() - base
+        out.backward(g)
+        return held
+
+    # the same layer through the single-node path that recomputes instead of saving (use_mem_eff_path=True)
+    fused = BiMamba2(d_model=1024, d_state=64, d_conv=7, expand=2, headdim=64, chunk_size=256,
+                     use_mem_eff_path=True).cuda().bfloat16()
+    fused.load_state_dict(layer.state_dict())
+    for _ in range(3):
+        fused(u).backward(g)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fused(u).backward(g)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_fused = e0.elapsed_time(e1) / steps
+    mem = {"step_by_step_bytes": held_between_passes(layer), "mem_eff_bytes": held_between_passes(fused)}
     print(json.dumps({"metric": "BiMamba2 layer fwd+bwd tokens/s", "value": batch * 4096 / ms * 1e3, "unit": "tokens/s",
                       "ms_per_step": ms, "steps": steps, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": f"config#4 BiMamba2 layer: b{batch} L4096 d_model 1024 d_state 64 d_conv 7 "
                                              "expand 2 headdim 64 chunk 256"},
                       "library_kernels_us_per_step": sum(k["us_per_step"] for k in kernels.values()),
+                      "mem_eff_path": {"ms_per_step": ms_fused, "tokens_per_s": batch * 4096 / ms_fused * 1e3,
+                                       "held_between_passes": mem},
                       "kernels": kernels}), flush=True)
 
 

@@ -57,37 +57,51 @@ def _args(x, weight, bias, out=None, dout=None, dx=None, dw=None, db=None):
     return a
 
 
+def conv_forward(x, w2, bias):
+    """silu(depthwise conv) of x (batch, seqlen, channels; rows may be strided, see _strided_ok) into a new contiguous
+    tensor.  w2: (channels, width) contiguous."""
+    lib = _cabi.load()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    a = _args(x, w2, bias, out=out)
+    with torch.cuda.device(x.device):
+        _cabi.check(lib.bissd_dwconv_silu_forward(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def conv_backward(x, w2, bias, dout, dx):
+    """Gradients of conv_forward: writes dx (same strides as x) and returns (dweight (channels, width), dbias or None).
+    dout: contiguous (batch, seqlen, channels)."""
+    lib = _cabi.load()
+    assert dx.stride() == x.stride() and dout.is_contiguous()
+    dw = torch.empty_like(w2)
+    db = torch.empty_like(bias) if bias is not None else None
+    a = _args(x, w2, bias, dout=dout, dx=dx, dw=dw, db=db)
+    need = ctypes.c_size_t()
+    _cabi.check(lib.bissd_dwconv_silu_workspace_bytes(ctypes.byref(a), ctypes.byref(need)))
+    ws = torch.empty(need.value, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(lib.bissd_dwconv_silu_backward(ctypes.byref(a), ws.data_ptr(), need.value,
+                                                   torch.cuda.current_stream().cuda_stream))
+    return dw, db
+
+
 class _DWConvSiLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
-        lib = _cabi.load()
         if not _strided_ok(x):
             x = x.contiguous()
         w2 = weight.reshape(weight.shape[0], -1).contiguous()
-        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        a = _args(x, w2, bias, out=out)
-        with torch.cuda.device(x.device):
-            _cabi.check(lib.bissd_dwconv_silu_forward(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+        out = conv_forward(x, w2, bias)
         ctx.save_for_backward(x, w2, bias)
         ctx.wshape = weight.shape
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        lib = _cabi.load()
         x, w2, bias = ctx.saved_tensors
-        dout = dout.contiguous()
         xc = x if x.is_contiguous() else x.contiguous()          # dx is written with x's strides: use a contiguous pair
         dx = torch.empty_like(xc)
-        dw = torch.empty_like(w2)
-        db = torch.empty_like(bias) if bias is not None else None
-        a = _args(xc, w2, bias, dout=dout, dx=dx, dw=dw, db=db)
-        need = ctypes.c_size_t()
-        _cabi.check(lib.bissd_dwconv_silu_workspace_bytes(ctypes.byref(a), ctypes.byref(need)))
-        ws = torch.empty(need.value, dtype=torch.uint8, device=x.device)
-        with torch.cuda.device(x.device):
-            _cabi.check(lib.bissd_dwconv_silu_backward(ctypes.byref(a), ws.data_ptr(), need.value,
-                                                       torch.cuda.current_stream().cuda_stream))
+        dw, db = conv_backward(xc, w2, bias, dout.contiguous(), dx)
         return dx, dw.reshape(ctx.wshape), db
 
 

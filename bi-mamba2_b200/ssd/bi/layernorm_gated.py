@@ -65,44 +65,61 @@ def _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, out=None
     return a
 
 
+def norm_forward(x2, z2, weight, eps, group_size, norm_before_gate, rstd=None):
+    """x2, z2: (rows, hidden) with unit inner stride (rows may be strided).  Returns (out (rows, hidden) contiguous,
+    rstd (rows, hidden / group) fp32)."""
+    lib = _cabi.load()
+    rows, hidden = x2.shape
+    group = hidden if group_size is None else group_size
+    out = torch.empty((rows, hidden), dtype=x2.dtype, device=x2.device)
+    if rstd is None:
+        rstd = torch.empty((rows, hidden // group), dtype=torch.float32, device=x2.device)
+    a = _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, out=out)
+    with torch.cuda.device(x2.device):
+        _cabi.check(lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+    return out, rstd
+
+
+def norm_backward(x2, z2, weight, rstd, eps, group_size, norm_before_gate, dout2, dx, dz):
+    """Gradients of norm_forward: writes dx (row stride of x2) and dz (row stride of z2; None without z), returns the
+    weight gradient.  dout2: (rows, hidden) with unit inner stride."""
+    lib = _cabi.load()
+    assert dx.stride(0) == x2.stride(0) and (z2 is None or dz.stride(0) == z2.stride(0))
+    dw = torch.empty_like(weight)
+    a = _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, dout=dout2, dx=dx, dz=dz, dw=dw)
+    need = ctypes.c_size_t()
+    _cabi.check(lib.bissd_rmsnorm_gated_workspace_bytes(ctypes.byref(a), ctypes.byref(need)))
+    ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=x2.device)
+    with torch.cuda.device(x2.device):
+        _cabi.check(lib.bissd_rmsnorm_gated_backward(ctypes.byref(a), ws.data_ptr(), need.value,
+                                                     torch.cuda.current_stream().cuda_stream))
+    return dw
+
+
 class _RMSNormGatedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, z, eps, group_size, norm_before_gate):
-        lib = _cabi.load()
         hidden = x.shape[-1]
         x2 = _rows(x, hidden)
         z2 = _rows(z, hidden) if z is not None else None
         weight = weight.contiguous()
-        group = hidden if group_size is None else group_size
-        out = torch.empty((x2.shape[0], hidden), dtype=x.dtype, device=x.device)
-        rstd = torch.empty((x2.shape[0], hidden // group), dtype=torch.float32, device=x.device)
-        a = _norm_args(x2, z2, weight, rstd, eps, group_size, norm_before_gate, out=out)
-        with torch.cuda.device(x.device):
-            _cabi.check(lib.bissd_rmsnorm_gated_forward(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+        out, rstd = norm_forward(x2, z2, weight, eps, group_size, norm_before_gate)
         ctx.save_for_backward(x2, weight, z2, rstd)
         ctx.cfg = (eps, group_size, norm_before_gate, x.shape)
         return out.reshape(x.shape)
 
     @staticmethod
     def backward(ctx, dout):
-        lib = _cabi.load()
         x2, weight, z2, rstd = ctx.saved_tensors
         eps, group_size, norm_before_gate, shape = ctx.cfg
         hidden = x2.shape[1]
         d2 = _rows(dout, hidden)
         dx = torch.empty((x2.shape[0], hidden), dtype=x2.dtype, device=x2.device)
         dz = torch.empty_like(dx) if z2 is not None else None
-        dw = torch.empty_like(weight)
         # dx / dz are written with x's / z's row strides
         xs = x2 if x2.stride(0) == hidden else x2.contiguous()
         zs = z2 if z2 is None or z2.stride(0) == hidden else z2.contiguous()
-        a = _norm_args(xs, zs, weight, rstd, eps, group_size, norm_before_gate, dout=d2, dx=dx, dz=dz, dw=dw)
-        need = ctypes.c_size_t()
-        _cabi.check(lib.bissd_rmsnorm_gated_workspace_bytes(ctypes.byref(a), ctypes.byref(need)))
-        ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=x2.device)
-        with torch.cuda.device(x2.device):
-            _cabi.check(lib.bissd_rmsnorm_gated_backward(ctypes.byref(a), ws.data_ptr(), need.value,
-                                                         torch.cuda.current_stream().cuda_stream))
+        dw = norm_backward(xs, zs, weight, rstd, eps, group_size, norm_before_gate, d2, dx, dz)
         return dx.reshape(shape), dw, (dz.reshape(shape) if dz is not None else None), None, None, None
 
 

@@ -113,8 +113,11 @@ def _family(n, shape, fused, **kw):
     return tuple(torch.empty(shape, **kw) for _ in range(n))
 
 
-def _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt_softplus, dt_min, dt_max, fused):
-    """Returns (out, out_x, dt_out, cs_f, cs_b, states_f, states_b, final_f, final_b); out_x is empty without z."""
+def _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt_softplus, dt_min, dt_max, fused,
+                   phases=None, out=None):
+    """Returns (out, out_x, dt_out, cs_f, cs_b, states_f, states_b, final_f, final_b); out_x is empty without z.
+    phases: a BISSD_PHASE_* mask (default all); with PHASE_LOCAL alone only dt_out, the cumulative sums, the entering
+    states and the final states are computed and `out` (any tensor of x's shape, never written) must be given."""
     import ctypes
     _require_cuda(x, dt, A, B, C, D, z, dt_bias)
     lib = _cabi.load()
@@ -126,8 +129,13 @@ def _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt
     nchunks = math.ceil(seqlen / chunk_size)
     p = _problem(x, dt, B, chunk_size, D, z, dt_bias, dt_softplus, dt_min, dt_max)
     dev = x.device
-    out = torch.empty(x.shape, dtype=x.dtype, device=dev)
-    out_x = torch.empty(x.shape, dtype=x.dtype, device=dev) if z is not None else torch.empty(0, dtype=x.dtype, device=dev)
+    phases = _cabi.PHASE_ALL if phases is None else phases
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=dev)
+    if z is not None and (phases & _cabi.PHASE_FINISH):
+        out_x = torch.empty(x.shape, dtype=x.dtype, device=dev)
+    else:
+        out_x = torch.empty(0, dtype=x.dtype, device=dev) if z is None else out
     dt_out, cs_f, cs_b = _family(3, (batch, nheads, nchunks, chunk_size), fused, dtype=torch.float32, device=dev)
     states_f, states_b = _family(2, (batch, nchunks, nheads, headdim, dstate), fused, dtype=x.dtype, device=dev)
     final_f, final_b = _family(2, (batch, nheads, headdim, dstate), fused, dtype=torch.float32, device=dev)
@@ -136,7 +144,7 @@ def _scan_fwd_core(x, dt, A, B, C, chunk_size, D, z, dt_bias, init_f, init_b, dt
                          _cabi.Tensor(dt.data_ptr(), dt.stride(0), dt.stride(1), dt.stride(2)),
                          _ptr(A32), _ptr(D32), _ptr(bias32), _tensor4(out), _tensor4(out_x if z is not None else None),
                          _ptr(dt_out), _ptr(cs_f), _ptr(cs_b), _ptr(states_f), _ptr(states_b), _ptr(final_f),
-                         _ptr(final_b), _ptr(init_f), _ptr(init_b), _cabi.PHASE_ALL)
+                         _ptr(final_b), _ptr(init_f), _ptr(init_b), phases)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _cabi.check(lib.bissd_forward(ctypes.byref(args), ws.data_ptr(), nbytes, stream))

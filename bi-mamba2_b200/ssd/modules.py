@@ -4,7 +4,9 @@ bidirectional SSD scan -> gated RMSNorm -> out_proj.
 Same constructor arguments, parameter names (state_dict keys) and forward semantics as the reference layer
 (src/ssd/modules.py:17-187), so its checkpoints load unchanged.  The scan, the depthwise convolution + SiLU
 (channels-last, no transposes) and the gated RMSNorm run on the sm_100a kernels of libbissd; the two projections are
-plain library GEMMs (cuBLAS through nn.Linear).
+plain library GEMMs (cuBLAS through nn.Linear).  `use_mem_eff_path=True` runs everything after in_proj as one autograd
+node that saves only the projection's output and the scan's output and recomputes the rest in the backward pass
+(ssd/bi/split_conv1d_scan.py).
 """
 import math
 
@@ -14,6 +16,7 @@ import torch.nn.functional as F
 
 from ssd.bi.conv_silu import dwconv1d_silu
 from ssd.bi.layernorm_gated import RMSNorm as RMSNormGated
+from ssd.bi.split_conv1d_scan import bimamba_split_conv1d_scan_combined
 from ssd.bi.ssd_combined import bimamba_chunk_scan_combined
 
 
@@ -38,8 +41,7 @@ class BiMamba2(nn.Module):
         self.learnable_init_states = learnable_init_states
         self.activation = activation
         self.chunk_size = chunk_size
-        self.use_mem_eff_path = use_mem_eff_path
-        assert not self.use_mem_eff_path, "Mem Eff Path is not implemented yet."
+        self.use_mem_eff_path = use_mem_eff_path        # one autograd node with recomputation, see forward()
         self.layer_idx = layer_idx
 
         # order of the projection's output channels: [z, x, B, C, dt]
@@ -73,6 +75,15 @@ class BiMamba2(nn.Module):
         zxbcdt = self.in_proj(u)
         A = -torch.exp(self.A_log.float())
         dt_limit_kwargs = {} if self.dt_limit == (0.0, float("inf")) else dict(dt_limit=self.dt_limit)
+        if self.use_mem_eff_path:
+            # the path the reference leaves commented out (src/ssd/modules.py:129-150): everything after in_proj as one
+            # autograd node that recomputes the convolution, the scan's saved quantities and the norm's output
+            return bimamba_split_conv1d_scan_combined(
+                zxbcdt, self.conv1d.weight, self.conv1d.bias, self.dt_bias, A, self.D, self.chunk_size,
+                dt_limit=self.dt_limit, rmsnorm_weight=self.norm.weight, rmsnorm_eps=self.norm.eps,
+                outproj_weight=self.out_proj.weight, outproj_bias=self.out_proj.bias, headdim=self.headdim,
+                ngroups=self.ngroups, norm_before_gate=self.norm.norm_before_gate,
+                rmsnorm_group_size=self.d_inner if self.norm.group_size is None else self.norm.group_size)
         z, xBC, dt = torch.split(
             zxbcdt, [self.d_inner, self.d_inner + 2 * self.ngroups * self.d_state, self.nheads], dim=-1)
         assert self.activation in ["silu", "swish"]

@@ -107,6 +107,19 @@ def test_operator_refuses_cpu_tensors(lib):
                                     torch.randn(1, 64, 1, 8), 32)
 
 
+def test_fused_layer_function_refuses_cpu_tensors_and_odd_widths(lib):
+    import torch
+    from ssd.bi.split_conv1d_scan import bimamba_split_conv1d_scan_combined
+    H, P, G, N = 8, 16, 1, 16
+    dim = H * P
+    args = lambda extra=0: (torch.randn(1, 64, 2 * dim + 2 * G * N + H + extra), torch.randn(dim + 2 * G * N, 1, 3), None,
+                            torch.zeros(H), -torch.ones(H), torch.ones(H, P), 32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        bimamba_split_conv1d_scan_combined(*args())
+    with pytest.raises(ValueError, match="channels"):                             # extra non-SSM channels are not taken
+        bimamba_split_conv1d_scan_combined(*args(extra=8))
+
+
 def test_norm_entry_points_validate_before_any_launch(lib):
     a = _cabi.NormArgs(rows=4, hidden=200, group_size=0, x_dtype=0, w_dtype=0, norm_before_gate=1, eps=1e-5,
                        stride_x=200, stride_z=200, stride_out=200, x=256, weight=256, out=256, rstd=256)

@@ -100,3 +100,114 @@ def test_config4_layer_slab_against_chunked_restatement():
         if k == "fc_D.weight":
             continue
         assert max_rel_err(p.grad, W[k].grad) < tol, k
+
+
+# ---- the fused, memory-efficient path (the reference's commented-out use_mem_eff_path, src/ssd/modules.py:129-150) ----
+
+def _pair(dtype, d_model=128, **kw):
+    """Two layers with the same parameters: the step-by-step path and the single-node path."""
+    from ssd.modules import BiMamba2
+    torch.manual_seed(1)
+    a = BiMamba2(d_model, use_mem_eff_path=False, **kw).to("cuda", dtype)
+    with torch.no_grad():
+        a.A_log.uniform_(0.0, 2.0)
+        a.D.normal_()
+    b = BiMamba2(d_model, use_mem_eff_path=True, **kw).to("cuda", dtype)
+    b.load_state_dict(a.state_dict())
+    return a, b
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mem_eff_path_equals_step_by_step_path(dtype):
+    """Same kernels in the same order: the outputs are bit-equal and so are the gradients the library computes; the
+    output projection's weight gradient comes from a differently shaped GEMM and is held to a rounding tolerance."""
+    a, b = _pair(dtype, d_state=64, headdim=64, chunk_size=128, d_conv=7)
+    u = torch.randn(2, 384, 128, device="cuda", dtype=dtype)
+    gout = torch.randn_like(u)
+    ua, ub = u.clone().requires_grad_(True), u.clone().requires_grad_(True)
+    oa, ob = a(ua), b(ub)
+    assert torch.equal(oa, ob)
+    oa.backward(gout)
+    ob.backward(gout)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert max_rel_err(ub.grad, ua.grad) <= tol
+    for (k, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        if k == "fc_D.weight":
+            assert pb.grad is None
+            continue
+        assert pb.grad is not None and pb.grad.shape == pa.grad.shape, k
+        assert max_rel_err(pb.grad, pa.grad) <= tol, k
+    for k in ("conv1d.weight", "conv1d.bias", "A_log", "D", "dt_bias", "norm.weight"):   # straight from the library
+        assert torch.equal(dict(b.named_parameters())[k].grad, dict(a.named_parameters())[k].grad), k
+
+
+def test_mem_eff_path_against_dense_restatement():
+    from ssd.modules import BiMamba2
+    torch.manual_seed(0)
+    m = BiMamba2(128, d_state=64, headdim=64, chunk_size=128, d_conv=7)
+    with torch.no_grad():
+        m.A_log.uniform_(0.0, 2.0)
+        m.D.normal_()
+    u = torch.randn(2, 256, 128, dtype=torch.float64)
+    gout = torch.randn(2, 256, 128, dtype=torch.float64)
+    ref_u = u.clone().requires_grad_(True)
+    ref_out, W = _dense_layer(m, ref_u)
+    ref_out.backward(gout)
+    mg = BiMamba2(128, d_state=64, headdim=64, chunk_size=128, d_conv=7, use_mem_eff_path=True).to("cuda", torch.float32)
+    mg.load_state_dict(m.state_dict())
+    ug = u.to("cuda", torch.float32).requires_grad_(True)
+    out = mg(ug)
+    out.backward(gout.to("cuda", torch.float32))
+    tol = 2e-3
+    assert max_rel_err(out, ref_out) < tol
+    assert max_rel_err(ug.grad, ref_u.grad) < tol
+    for k, p in mg.named_parameters():
+        if k != "fc_D.weight":
+            assert max_rel_err(p.grad, W[k].grad) < tol, k
+
+
+def test_mem_eff_path_holds_less_memory_between_the_passes():
+    a, b = _pair(torch.bfloat16, d_model=512, d_state=64, headdim=64, chunk_size=256, d_conv=7)
+    u = torch.randn(4, 2048, 512, device="cuda", dtype=torch.bfloat16)
+    held = []
+    for m in (a, b):
+        torch.cuda.synchronize()
+        base = torch.cuda.memory_allocated()
+        out = m(u.clone().requires_grad_(True))
+        torch.cuda.synchronize()
+        held.append(torch.cuda.memory_allocated() - base)
+        out.sum().backward()
+        del out
+    assert held[1] < 0.75 * held[0], held
+
+
+def test_split_conv1d_scan_function_without_norm_and_projection():
+    """The function form with the gate inside the scan and no projections, against the same steps taken one by one."""
+    from ssd.bi.conv_silu import dwconv1d_silu
+    from ssd.bi.split_conv1d_scan import bimamba_split_conv1d_scan_combined, mamba_split_conv1d_scan_combined
+    from ssd.bi.ssd_combined import bimamba_chunk_scan_combined
+    assert mamba_split_conv1d_scan_combined is bimamba_split_conv1d_scan_combined
+    torch.manual_seed(2)
+    b, L, H, P, G, N, K, Q = 2, 256, 8, 32, 2, 32, 5, 64
+    dim, dt_ = H * P, torch.bfloat16
+    zxbcdt = torch.randn(b, L, 2 * dim + 2 * G * N + H, device="cuda", dtype=dt_)
+    cw = (torch.randn(dim + 2 * G * N, 1, K, device="cuda") * 0.3)
+    cb = torch.randn(dim + 2 * G * N, device="cuda") * 0.1
+    dt_bias = torch.rand(H, device="cuda") - 4.0
+    A = -torch.exp(torch.rand(H, device="cuda") * 2.0)
+    D = torch.randn(H, P, device="cuda")
+    leaves = [t.clone().requires_grad_(True) for t in (zxbcdt, cw, cb, dt_bias, A, D)]
+    ref_leaves = [t.clone().requires_grad_(True) for t in (zxbcdt, cw, cb, dt_bias, A, D)]
+    out = bimamba_split_conv1d_scan_combined(*leaves, Q, ngroups=G)
+    z, xBC, dt = torch.split(ref_leaves[0], [dim, dim + 2 * G * N, H], dim=-1)
+    xBC = dwconv1d_silu(xBC, ref_leaves[1], ref_leaves[2])
+    x, Bm, Cm = torch.split(xBC, [dim, G * N, G * N], dim=-1)
+    ref = bimamba_chunk_scan_combined(x.unflatten(-1, (H, P)), dt, ref_leaves[4], Bm.unflatten(-1, (G, N)),
+                                      Cm.unflatten(-1, (G, N)), Q, D=ref_leaves[5], z=z.unflatten(-1, (H, P)),
+                                      dt_bias=ref_leaves[3], dt_softplus=True).reshape(b, L, dim)
+    assert torch.equal(out, ref)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref.backward(g)
+    for got, want, name in zip(leaves, ref_leaves, ("zxbcdt", "conv_w", "conv_b", "dt_bias", "A", "D")):
+        assert max_rel_err(got.grad, want.grad) <= 1e-6, name
