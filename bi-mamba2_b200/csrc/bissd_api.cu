@@ -146,7 +146,10 @@ static FwdWs fwd_layout(const Dims &d) {
     return w;
 }
 
-static BwdWs bwd_layout(const Dims &d) {
+// tc: sized for the tensor-core family (16-bit inputs that meet its alignment rules): the passed state gradients are
+// kept in the input dtype only, and the "states" parts of dB / dC arrive summed over the heads of a group.  The
+// CUDA-core family needs the fp32 copy and one partial per head.
+static BwdWs bwd_layout(const Dims &d, bool tc) {
     BwdWs w;
     size_t o = kWsHeader;
     const size_t st = (size_t)d.b * d.nc * d.H * d.P * d.N;
@@ -157,7 +160,7 @@ static BwdWs bwd_layout(const Dims &d) {
     auto take = [&](size_t bytes) { size_t at = o; o = align256(o + bytes); return at; };
     w.cb = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
     w.gloc = take(2 * st * 4);
-    w.E = take(2 * st * 4);
+    w.E = take(tc ? 0 : 2 * st * 4);                                 // fp32 passed state gradients (CUDA-core family)
     w.E16 = take(2 * st * 2);                                        // passed state gradients in the input dtype
     w.g = take((size_t)d.b * d.L * d.H * d.P * 2);                   // gated output gradient dout * silu(z)
     w.cbt = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);          // CB transposed
@@ -170,8 +173,8 @@ static BwdWs bwd_layout(const Dims &d) {
     w.pf = take(hq * 4 * w.nsplit); w.pb = take(hq * 4 * w.nsplit);
     w.da_f = take(hq * 4); w.da_b = take(hq * 4);
     w.u4 = take(8 * hq * 4);                                         // u_f / u_b per tile (tc::intra_sums: 2 row tiles; tc::intra_dcb_tile: 4)
-    w.dB_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
-    w.dC_part = take((size_t)d.b * d.nc * d.Q * d.H * d.N * 4);
+    w.dB_part = take((size_t)d.b * d.nc * d.Q * (tc ? d.G : d.H) * d.N * 4);
+    w.dC_part = take((size_t)d.b * d.nc * d.Q * (tc ? d.G : d.H) * d.N * 4);
     w.dCB = take((size_t)d.b * d.nc * d.G * d.Q * d.Q * 4);
     w.dDpart = take((size_t)d.b * d.nc * d.H * std::max(w.nlt, 8) * d.P * 4);   // up to 8 partial rows per (b,c,h)
     w.dApart = take((size_t)d.b * d.nc * d.H * 4);
@@ -443,7 +446,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
 
 template <class T>
 static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaStream_t s, bool tcp) {
-    const BwdWs w = bwd_layout(d);
+    const BwdWs w = bwd_layout(d, tcp);
     int *status = reinterpret_cast<int *>(ws);
     auto F = [&](size_t off) { return reinterpret_cast<float *>(ws + off); };
     const View x = view_of(a.x), Bm = view_of(a.B), Cm = view_of(a.C), z = view_of(a.z), dout = view_of(a.dout),
@@ -1029,7 +1032,7 @@ int bissd_workspace_bytes(const bissd_problem *p, size_t *fwd_bytes, size_t *bwd
     int rc = make_dims(*p, &d);
     if (rc != BISSD_OK) return rc;
     if (fwd_bytes) *fwd_bytes = fwd_layout(d).total;
-    if (bwd_bytes) *bwd_bytes = bwd_layout(d).total;
+    if (bwd_bytes) *bwd_bytes = bwd_layout(d, !force_simt() && tc_shape_ok(*p)).total;
     return BISSD_OK;
 }
 
@@ -1320,14 +1323,16 @@ int bissd_backward(const bissd_bwd_args *a, void *workspace, size_t workspace_by
     if (a->p.has_z && (!a->z.ptr || !a->dz || !a->out_x.ptr)) return BISSD_ERR_NULL;   // the gate runs in the LOCAL phase
     if (a->p.has_D && !a->D) return BISSD_ERR_NULL;
     if (a->p.has_dt_bias && !a->dt_bias) return BISSD_ERR_NULL;
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < bwd_layout(d).total)
+    // 16-bit tensors that miss the tensor-core family's alignment rules run on the CUDA-core family, which needs the
+    // larger workspace that bissd_workspace_bytes reports for the same sizes with fp32 inputs
+    const bool tcp = !force_simt() && tc_shape_ok(a->p) && aligned16(a->x) && aligned16(a->B) && aligned16(a->C) &&
+                     aligned16(a->z) && aligned16(a->dout) && aligned16(a->out_x);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < bwd_layout(d, tcp).total)
         return BISSD_ERR_WORKSPACE;
     rc = check_device();
     if (rc != BISSD_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     char *ws = static_cast<char *>(workspace);
-    const bool tcp = !force_simt() && tc_shape_ok(a->p) && aligned16(a->x) && aligned16(a->B) && aligned16(a->C) &&
-                     aligned16(a->z) && aligned16(a->dout) && aligned16(a->out_x);
     switch (a->p.x_dtype) {
         case BISSD_F32: return backward_impl<float>(*a, d, ws, s, false);
         case BISSD_BF16: return backward_impl<__nv_bfloat16>(*a, d, ws, s, tcp);

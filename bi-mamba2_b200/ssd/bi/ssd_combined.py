@@ -87,7 +87,15 @@ def _f32c(t):
 
 
 def _inner_contig(t):
-    return t if t is None or t.stride(-1) == 1 else t.contiguous()
+    """t as the library reads it in place: unit inner stride and, for 16-bit tensors, 16-byte aligned rows (what the
+    tensor-core kernels and the workspace size reported for them assume); anything else is copied."""
+    if t is None:
+        return t
+    if t.stride(-1) != 1:
+        return t.contiguous()
+    if t.element_size() == 2 and (t.data_ptr() % 16 or any(st % 8 for st in t.stride()[:-1])):
+        return t.contiguous()
+    return t
 
 
 def kernel_path(x, dt, B, chunk_size, D=None, z=None, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):

@@ -129,7 +129,12 @@ const char *bissd_strerror(int status);
 const char *bissd_last_cuda_error(void);
 
 /* Bytes of scratch each pass needs for `p` (either pointer may be NULL).  The reference allocates the same
- * kind of temporaries with torch.empty inside every wrapper (e.g. ssd_chunk_state.py:775-776). */
+ * kind of temporaries with torch.empty inside every wrapper (e.g. ssd_chunk_state.py:775-776).
+ * For 16-bit problems the backward size is that of the tensor-core kernels, which take x, B, C, z, dout and out_x
+ * with 16-byte aligned pointers and batch / sequence / head strides that are multiples of 8 elements.  Tensors that
+ * miss this are still accepted - the CUDA-core kernels run them - but those need the (larger) backward size this
+ * function reports for the same sizes with x_dtype = BISSD_F32; with less, bissd_backward returns
+ * BISSD_ERR_WORKSPACE. */
 int bissd_workspace_bytes(const bissd_problem *p, size_t *fwd_bytes, size_t *bwd_bytes);
 
 /* Forward pass.  workspace must be 256-byte aligned. */

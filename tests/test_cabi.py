@@ -87,6 +87,27 @@ def test_workspace_bytes_and_validation(lib):
     assert lib.bissd_workspace_bytes(None, None, None) == -1
 
 
+def test_backward_workspace_is_sized_by_kernel_family(lib):
+    """16-bit problems report the tensor-core kernels' backward scratch (no fp32 copy of the passed state gradients,
+    dB / dC parts per group); 16-bit tensors that miss the alignment rules need the CUDA-core size and are refused
+    with less - before anything touches a device."""
+    cfg2 = dict(batch=8, seqlen=2048, nheads=24, headdim=64, ngroups=1, dstate=128, chunk_size=256, has_z=1, has_dt_bias=1)
+    tc, simt = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem(x_dtype=1, dt_dtype=1, **cfg2)), None, ctypes.byref(tc)) == 0
+    assert lib.bissd_workspace_bytes(ctypes.byref(_problem(x_dtype=0, dt_dtype=0, **cfg2)), None, ctypes.byref(simt)) == 0
+    assert tc.value < 350e6 < simt.value, (tc.value, simt.value)
+    a = _cabi.BwdArgs()
+    a.p = _problem(x_dtype=1, dt_dtype=1, **cfg2)
+    a.phases = 3
+    t = lambda addr: _cabi.Tensor(addr, 2048 * 24 * 64, 24 * 64, 64)
+    a.x, a.B, a.C, a.z, a.dout, a.out_x = t(4096 + 2), t(4096), t(4096), t(4096), t(4096), t(4096)   # x 2 bytes off
+    a.dt = _cabi.Tensor(4096, 2048 * 24, 24, 1)
+    for f in ("A", "D", "dt_bias", "dt_out", "cs_f", "cs_b", "states_f", "states_b", "dx", "dz", "dB", "dC", "ddt", "dA",
+              "dD", "ddt_bias"):
+        setattr(a, f, 4096)
+    assert lib.bissd_backward(ctypes.byref(a), 4096, tc.value, None) == -5     # BISSD_ERR_WORKSPACE
+
+
 def test_forward_rejects_bad_arguments_before_any_launch(lib):
     args = _cabi.FwdArgs()
     args.p = _problem()
