@@ -407,7 +407,7 @@ __device__ __forceinline__ void umma_issue_stage(uint32_t d_tmem, int n_tile, in
 }
 
 // CTA-wide wait on an mbarrier phase: the first warp polls, the other warps sleep in the CTA barrier that hands its
-// verdict to everyone.  (Measured on the one-shot kernels: no faster than every warp polling - mbarrier.try_wait
+// outcome to everyone.  (Measured on the one-shot kernels: no faster than every warp polling - mbarrier.try_wait
 // suspends the pollers - so those keep their own waits; kernels with sixteen warps use this form.)
 // Every thread of the CTA must call it; the result is uniform.  `ok_in`: a thread that has already seen a failure
 // passes false, which skips its wait and makes the common result false.

@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ from the REFERENCE implementation itself.
 
-Run once, in a container that has the reference checkout (default /root/reference) - it is not needed at
+Run once, in a container that has the reference checkout (see --reference) - it is not needed at
 test time.  Usage:  python tests/golden/make_golden.py [--reference /path/to/Bi-Mamba2]
 
 Two sources, both the reference's own code:

@@ -1,7 +1,7 @@
 """Generate tests/golden/rmsnorm_ref_*.npz from the REFERENCE's own `rms_norm_ref`
 (src/ssd/bi/layernorm_gated.py:18-41; pure PyTorch, runs on CPU).
 
-Run once where the reference checkout is present (default /root/reference); it is not needed at test time.
+Run once where the reference checkout is present (see --reference); it is not needed at test time.
     python tests/golden/make_golden_norm.py [--reference /path/to/Bi-Mamba2]
 
 Each file stores the inputs (x, z, weight, dout - values exactly representable in the case's dtype), the switches,
