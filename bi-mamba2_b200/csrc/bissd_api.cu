@@ -362,7 +362,7 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                     d, Cm, Bm, ws_path ? nullptr : CB, nullptr, ws_path ? CB16 : nullptr, nullptr, nullptr, status));
                 bool tma_done = false;
                 if (ws_path) {
-                    CUtensorMap mC, mCB, mSf, mSb, mX;
+                    CUtensorMap mC, mCB, mSf, mSb, mX, mR;
                     const unsigned long long dC[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
                     const unsigned long long sC[3] = {(unsigned long long)a.C.stride_head * 2, (unsigned long long)a.C.stride_seq * 2, (unsigned long long)a.C.stride_batch * 2};
                     const unsigned bC[4] = {64, 1, 128, 1};
@@ -372,6 +372,10 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                                 tc::make_map2(&mCB, BISSD_BF16, CB16, d.Q, (unsigned long long)d.b * d.nc * d.G * d.Q, 64, 128) &&
                                 tc::make_map2(&mSf, a.p.x_dtype, a.states_f, d.N, rows, 64, d.P) &&
                                 tc::make_map2(&mSb, a.p.x_dtype, a.states_b, d.N, rows, 64, d.P);
+                    // the epilogue's z rows by TMA (a [128 rows x 64] tile per step); without z the map is not used
+                    const bool z_rows = maps && d.has_z &&
+                                        map_bshd(&mR, a.p.x_dtype, a.z.ptr, a.z.stride_batch, a.z.stride_seq, a.z.stride_head, d.P, d.H, d.L, d.b, 128);
+                    if (maps && !z_rows) mR = mX;
                     if (maps) {
                         const size_t smem_t = tc::scan_ws_smem(d.P, d.N, d.Q);
                         const int tiles = bch * (d.Q / tc::kTileM);
@@ -386,11 +390,12 @@ static int forward_impl(const bissd_fwd_args &a, const Dims &d, char *ws, cudaSt
                         wa.x = x; wa.z = z; wa.D = a.D; wa.dt_out = a.dt_out; wa.cs_f = a.cs_f; wa.cs_b = a.cs_b;
                         wa.out = mview_of(a.out); wa.out_x = mview_of(a.out_x);
                         wa.wide_z = wide_z; wa.wide_o = wide_o;
+                        wa.rows_by_tma = z_rows ? 1 : 0;
 #define BISSD_SCAN_WS(NSL, NS)                                                                                          \
     do {                                                                                                                \
         BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 0>), smem_t);                                                            \
         BISSD_LAUNCH("tc_chunk_scan_ws", launch_pdl(tc::ws_kernel<T, NSL, NS, 0>, grid, tc::kWsThreads, smem_t, s,              \
-            d, mC, mCB, mSf, mSb, mX, wa, status));                                                                     \
+            d, mC, mCB, mSf, mSb, mX, mR, wa, status));                                                                 \
     } while (0)
                         if (d.N == 128 && d.Q == 256) BISSD_SCAN_WS(2, 4);
                         else if (d.N == 64 && d.Q == 256) BISSD_SCAN_WS(1, 4);
@@ -566,7 +571,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
             };
             bool dx_done = false;
             if (ws_path) {
-                CUtensorMap mB, mCBt, mEf, mEb, mG;
+                CUtensorMap mB, mCBt, mEf, mEb, mG, mR;
                 const unsigned long long dB4[4] = {(unsigned long long)d.N, (unsigned long long)d.G, (unsigned long long)d.L, (unsigned long long)d.b};
                 const unsigned long long sB4[3] = {(unsigned long long)a.B.stride_head * 2, (unsigned long long)a.B.stride_seq * 2, (unsigned long long)a.B.stride_batch * 2};
                 const unsigned bB4[4] = {64, 1, 128, 1};
@@ -577,6 +582,9 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                                   tc::make_map2(&mCBt, BISSD_BF16, CBt16, d.Q, (unsigned long long)d.b * d.nc * d.G * d.Q, 64, 128) &&
                                   tc::make_map2(&mEf, a.p.x_dtype, e16, d.N, rows, 64, d.P) &&
                                   tc::make_map2(&mEb, a.p.x_dtype, e16 + rows * d.N * 2, d.N, rows, 64, d.P);
+                // the epilogue's x rows by TMA (a [128 rows x 64] tile per step)
+                const bool x_rows = maps && map_bshd(&mR, a.p.x_dtype, a.x.ptr, a.x.stride_batch, a.x.stride_seq, a.x.stride_head, d.P, d.H, d.L, d.b, 128);
+                if (maps && !x_rows) mR = mG;
                 if (maps) {
                     auto wide = [](const void *ptr, long long sb, long long sl, long long sh) {
                         return ptr && reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && sb % 16 == 0 && sl % 16 == 0 && sh % 16 == 0;
@@ -589,13 +597,14 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     wa.wide_x = wide(x.ptr, x.sb, x.sl, x.sh);
                     wa.wide_z = wide(gv.ptr, gv.sb, gv.sl, gv.sh);
                     wa.wide_o = wide(a.dx, 16, 16, 16) && (d.H * d.P) % 16 == 0;
+                    wa.rows_by_tma = x_rows ? 1 : 0;
                     const size_t smem_t = tc::scan_ws_smem(d.P, d.N, d.Q);
                     const int grid = std::min(sm_count(), bch * nlt_tc);
 #define BISSD_DX_WS(NSL, NS)                                                                                            \
     do {                                                                                                                \
         BISSD_ALLOW((tc::ws_kernel<T, NSL, NS, 1>), smem_t);                                                            \
         BISSD_LAUNCH("tc_dx_ws", launch_pdl(tc::ws_kernel<T, NSL, NS, 1>, grid, tc::kWsThreads, smem_t, s,                      \
-            d, mB, mCBt, mEf, mEb, mG, wa, status));                                                                    \
+            d, mB, mCBt, mEf, mEb, mG, mR, wa, status));                                                                \
     } while (0)
                     if (d.N == 128 && d.Q == 256) BISSD_DX_WS(2, 4);
                     else if (d.N == 64 && d.Q == 256) BISSD_DX_WS(1, 4);

@@ -15,6 +15,12 @@
 //                       warps w and w+4 share 32 rows and take 32 columns each
 //   warps 10-17         build the masked-decay tile M 64 columns at a time into a ring of stages
 //
+// The rows the epilogue reads beside the accumulators - z (MODE 0) or x (MODE 1), a [128 x 64] tile per step - come
+// by TMA into one more buffer, requested by a lane of the first epilogue warp a tile ahead: as per-lane loads (32 row
+// pieces, 32 different lines per instruction) they cost the backward kernel 12 us at the benchmark shape.  g, which the
+// backward epilogue needs too, still comes by per-lane loads: there is no room for a second buffer, and reading it out
+// of the MMA's operand pieces (same rows, same layout) ties the loader to the epilogue and measured slower.
+//
 // Accumulators are double-buffered in TMEM (2 x 3P columns), so the epilogue of tile i overlaps the MMAs of tile i+1
 // and the M build of tile i+1/i+2.  The entering states of tile i+1 are requested as soon as the state products of
 // tile i have completed; x of tile i+1 arrives in 64-row pieces, each requested once the MMAs that read the same
@@ -39,7 +45,11 @@ namespace tc {
 constexpr int kWsBuilderWarps = 8, kWsEpiWarps = 8;
 constexpr int kWsFirstEpi = 2, kWsFirstBuilder = kWsFirstEpi + kWsEpiWarps;
 constexpr int kWsThreads = 32 * (kWsFirstBuilder + kWsBuilderWarps);
-constexpr int kWsMStages = 3;
+constexpr int kWsMaxMStages = 3;
+// Ring of built M stages: three where shared memory allows (dstate 64), two beside the row tile at dstate 128 (two
+// and three measured the same there: scan 112 / 114, dx 139 / 141 us).
+__host__ __device__ constexpr int ws_m_stages(int nsl) { return nsl == 1 ? 3 : 2; }
+constexpr int kWsRowBytes = kTileM * 128;                       // the epilogue's rows of one tile: [128 x 64] 16-bit
 
 struct WsShared {
     uint64_t grp_full, grp_done, st_full, st_done, tab_bar, fin_bar;
@@ -49,15 +59,16 @@ struct WsShared {
     // to release it).  With one barrier per slot it is at most zero phases ahead.
     uint64_t red_bar[4][3];
     uint64_t x_full[4], x_free[4];
-    uint64_t m_full[kWsMStages], m_free[kWsMStages];
+    uint64_t m_full[kWsMaxMStages], m_free[kWsMaxMStages];
     uint64_t acc_full[2], acc_free[2];
+    uint64_t r_full, r_free;     // the epilogue's row tile (z or x) has landed / every epilogue warp has taken its rows
     uint32_t tmem_base;
     int fail;
 };
 
 inline size_t scan_ws_smem(int P, int N, int Q) {
     return 1024 + (size_t)(N / 64) * 16384 + (size_t)(Q / 64) * 16384 + 2 * (size_t)(N / 64) * P * 128 + (size_t)Q * 128 +
-           (size_t)kWsMStages * kAStageBytes + 2 * 6 * (size_t)Q * 4;
+           (size_t)ws_m_stages(N / 64) * kAStageBytes + kWsRowBytes + 2 * 6 * (size_t)Q * 4;
 }
 inline bool scan_ws_ok(int P, int N, int Q) {
     if (P != 64 || (N != 64 && N != 128) || (Q != 128 && Q != 256)) return false;
@@ -158,7 +169,7 @@ __device__ __forceinline__ uint4 ws_scale8<__half>(const uint4 &raw, float rf, c
 // All stages of one tile whose rows start at l0.  Deliberately a compact runtime loop (the code of all four roles has
 // to stay resident in the instruction caches): per stage wait for the ring slot, then for each of the four 32-row
 // blocks pick - uniformly over the CTA - the factorised form below / above the diagonal or the per-element form.
-template <class T>
+template <class T, int NST>
 __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM, const float *tabp, int ns, int l0, int bt,
                                               int lane, float dfold, WsRing &ring, uint64_t *m_full, uint64_t *m_free,
                                               volatile int *fail) {
@@ -168,7 +179,7 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
 #pragma unroll 1
     for (int s = 0; s < ns; ++s) {
         const int s0 = s * 64, sc = s0 + cc * 8;
-        if (ring.used >= kWsMStages &&
+        if (ring.used >= NST &&
             !ws_wait_warp(&m_free[ring.mb], ((ring.par >> ring.mb) & 1) ^ 1, fail, 33))
             return false;
         const uint8_t *slab = smCB + s * 16384;
@@ -226,7 +237,7 @@ __device__ __forceinline__ bool ws_build_tile(const uint8_t *smCB, uint8_t *smM,
         __syncwarp();
         if (lane == 0) mbar_arrive(&m_full[ring.mb]);
         ring.par ^= 1u << ring.mb;
-        ring.mb = (ring.mb + 1 == kWsMStages) ? 0 : ring.mb + 1;
+        ring.mb = (ring.mb + 1 == NST) ? 0 : ring.mb + 1;
         ++ring.used;
     }
     return true;
@@ -240,6 +251,7 @@ struct WsArgs {
     MutView out, out_x;      // MODE 0: out, out_x; MODE 1: out = dx
     float *ddt_out, *nf, *nb, *dDpart;   // MODE 1
     int wide_z, wide_x, wide_o;          // 32-byte accesses allowed on z / x / the outputs
+    int rows_by_tma;                     // the epilogue's z (MODE 0) / x (MODE 1) rows arrive through tmR
 };
 
 // One step of the transpose-reduce over a warp: every lane holds N values (one per column); lanes whose bit N/2 is
@@ -257,6 +269,43 @@ __device__ __forceinline__ void ws_fold(float (&v)[32], int lane) {
     }
 }
 
+// The epilogue's row tile ([128 rows x 64 columns] of z or x, K-major with the 128-byte swizzle) comes by TMA instead of
+// 32 per-lane row pieces per load instruction.  One lane of the first epilogue warp requests the tile of the next
+// step as soon as all eight epilogue warps have copied their rows of the current one into registers.
+struct WsRows {
+    const CUtensorMap *map;
+    uint8_t *buf;
+    int issued;
+    __device__ __forceinline__ void request(WsShared &sh, const Dims &d, const WsIter &w, int Q) {
+        mbar_expect_tx(&sh.r_full, (uint32_t)kWsRowBytes);
+        tma_load4(buf, map, 0, w.h, w.c * Q + w.rt * kTileM, w.b, &sh.r_full);
+        ++issued;
+    }
+};
+// this lane's 32 columns (columns ch .. ch + 31 of row r) of the landed tile
+__device__ __forceinline__ void ws_take_rows(const uint8_t *buf, int r, int ch, uint4 (&out)[4]) {
+    const uint8_t *rowp = buf + r * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) out[q] = *reinterpret_cast<const uint4 *>(rowp + ((((ch >> 3) + q) ^ (r & 7)) << 4));
+}
+// Every epilogue warp, at the top of tile i: wait for the tile's rows, copy them, hand the buffer back; the issuing lane
+// then waits for all warps and requests the rows of tile i + 1 (`next` is that tile).  False if a wait ran out.
+__device__ __forceinline__ bool ws_rows_step(WsShared &sh, WsRows &rw, const Dims &d, int Q, int i, int nt, const WsIter &next,
+                                             bool issuer, int r, int ch, int lane, uint4 (&out)[4], volatile int *fail) {
+    if (!ws_wait_warp(&sh.r_full, i & 1, fail, 23)) return false;
+    ws_take_rows(rw.buf, r, ch, out);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh.r_free);
+    if (issuer && lane == 0 && i + 1 < nt) {
+        if (ws_wait(&sh.r_free, i & 1, fail, 24)) {
+            fence_async_smem();                                 // the warps' reads precede the next TMA write
+            rw.request(sh, d, next, Q);
+        }
+    }
+    __syncwarp();
+    return true;
+}
+
 // MODE 1 epilogue (one warp: rows 32*quarter.., columns ch..ch+31 of every tile of this CTA):
 //   a = wf (B.E_f^T) + wb (B.E_b^T) + Mt.g;  dx = a Delta + D g;  ddt_out = sum_p a x;  nf / nb = Delta wf|wb sum_p
 //   (B.E^T) x;  dD partial = column sums of g x.  Row sums are completed across the two column halves through shared
@@ -264,7 +313,7 @@ __device__ __forceinline__ void ws_fold(float (&v)[32], int lane) {
 template <class T, int NS>
 __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, WsShared &sh, float (*rowred)[3][kTileM],
                                                uint32_t tl, int quarter, int ch, int lane, WsIter it, int nt, int nrt,
-                                               volatile int *fail) {
+                                               volatile int *fail, WsRows &rw, bool issuer) {
     constexpr int P = 64, Q = NS * 64;
     const View x = a.x, g = a.z;
     const int half = ch >> 5, r = quarter * 32 + lane;
@@ -284,10 +333,16 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
         const T *gp = static_cast<const T *>(g.ptr) + w.b * g.sb + (long long)(w.c * Q + l) * g.sl + w.h * g.sh + ch;
         if (!live) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) xr[q] = gr[q] = zero8();
+            for (int q = 0; q < 4; ++q) gr[q] = zero8();
+            if (!a.rows_by_tma) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) xr[q] = zero8();
+            }
         } else {
-            load16(xp, a.wide_x, xr[0], xr[1]);
-            load16(xp + 16, a.wide_x, xr[2], xr[3]);
+            if (!a.rows_by_tma) {
+                load16(xp, a.wide_x, xr[0], xr[1]);
+                load16(xp + 16, a.wide_x, xr[2], xr[3]);
+            }
             load16(gp, a.wide_z, gr[0], gr[1]);
             load16(gp + 16, a.wide_z, gr[2], gr[3]);
         }
@@ -295,6 +350,11 @@ __device__ __forceinline__ void ws_epilogue_dx(const Dims &d, const WsArgs &a, W
     if (nt > 0) load_rows(it);
     for (int i = 0; i < nt; ++i) {
         const int buf = i & 1, slot = i % 3;
+        if (a.rows_by_tma) {                                     // x rows of this tile from the TMA-fed buffer
+            WsIter nx = it;
+            nx.next(d, nrt);
+            if (!ws_rows_step(sh, rw, d, Q, i, nt, nx, issuer, r, ch, lane, xr, fail)) break;
+        }
         const int lim = min(Q, d.L - it.c * Q);
         const int l = it.rt * kTileM + r;
         const long long base = ((long long)(it.b * d.H + it.h) * d.nc + it.c) * Q;
@@ -390,7 +450,7 @@ template <class T, int NSL, int NS, int MODE>
 __global__ void __launch_bounds__(kWsThreads, 1)
 ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCB,
           const __grid_constant__ CUtensorMap tmSf, const __grid_constant__ CUtensorMap tmSb,
-          const __grid_constant__ CUtensorMap tmX, const WsArgs a, int *status) {
+          const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmR, const WsArgs a, int *status) {
     pdl_begin();
     extern __shared__ uint8_t dyn[];
     __shared__ WsShared sh;
@@ -405,8 +465,10 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
     uint8_t *smCB = smC + NSL * 16384;                        // NS slabs [128 x 64] bf16, K-major
     uint8_t *smS = smCB + NS * 16384;                         // per K slab: S_f [P x 64] then S_b [P x 64]
     uint8_t *smX = smS + 2 * NSL * P * 128;                   // [Q x 64], MN-major, in NS pieces of 64 rows
-    uint8_t *smM = smX + Q * 128;                             // kWsMStages stages [128 x 64]
-    float *tab = reinterpret_cast<float *>(smM + kWsMStages * kAStageBytes);   // 2 x (f2, b2, tf, tb, colF, colB)[Q]
+    constexpr int NST = ws_m_stages(NSL);
+    uint8_t *smM = smX + Q * 128;                             // NST stages [128 x 64]
+    uint8_t *smR = smM + NST * kAStageBytes;           // the epilogue's row tile (tmR): z (MODE 0) or x (MODE 1)
+    float *tab = reinterpret_cast<float *>(smR + kWsRowBytes);    // 2 x (f2, b2, tf, tb, colF, colB)[Q]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int *fail = &sh.fail;
 
@@ -428,7 +490,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             mbar_init(&sh.x_full[i], 1);
             mbar_init(&sh.x_free[i], 1);
         }
-        for (int i = 0; i < kWsMStages; ++i) {
+        for (int i = 0; i < NST; ++i) {
             mbar_init(&sh.m_full[i], kWsBuilderWarps);
             mbar_init(&sh.m_free[i], 1);
         }
@@ -436,6 +498,8 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
             mbar_init(&sh.acc_full[i], 1);
             mbar_init(&sh.acc_free[i], kWsEpiWarps);
         }
+        mbar_init(&sh.r_full, 1);
+        mbar_init(&sh.r_free, kWsEpiWarps);
         sh.fail = 0;
         fence_mbar_init();
     }
@@ -488,7 +552,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                         umma_commit(&sh.m_free[mb]);
                         umma_commit(&sh.x_free[s]);
                         m_par ^= 1u << mb;
-                        mb = (mb + 1 == kWsMStages) ? 0 : mb + 1;
+                        mb = (mb + 1 == NST) ? 0 : mb + 1;
                     }
                 }
                 if (!ok) break;
@@ -558,8 +622,12 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
         WsIter it;
         it.init(d, nrt, t0);
         bool ok = true;
+        WsRows rw{&tmR, smR, 0};
+        const bool issuer = warp == kWsFirstEpi;
+        const bool rows = a.rows_by_tma != 0;
+        if (rows && issuer && lane == 0 && nt > 0) rw.request(sh, d, it, Q);
         if constexpr (MODE == 1) {
-            ws_epilogue_dx<T, NS>(d, a, sh, rowred, tl, quarter, ch, lane, it, nt, nrt, fail);
+            ws_epilogue_dx<T, NS>(d, a, sh, rowred, tl, quarter, ch, lane, it, nt, nrt, fail, rw, issuer);
         } else {
         uint4 zr[4];
         auto load_z = [&](const WsIter &w) {
@@ -577,9 +645,15 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 for (int q = 0; q < 4; ++q) zr[q] = __ldg(reinterpret_cast<const uint4 *>(zp + q * 8));
             }
         };
-        if (nt > 0) load_z(it);
+        if (nt > 0 && !rows) load_z(it);
         for (int i = 0; i < nt && ok; ++i) {
             const int buf = i & 1;
+            if (rows) {                                          // z rows of this tile from the TMA-fed buffer
+                WsIter nx = it;
+                nx.next(d, nrt);
+                ok = ws_rows_step(sh, rw, d, Q, i, nt, nx, issuer, quarter * 32 + lane, ch, lane, zr, fail);
+                if (!ok) break;
+            }
             const int lim = min(Q, d.L - it.c * Q);
             const int l = it.rt * kTileM + quarter * 32 + lane;
             const long long base = ((long long)(it.b * d.H + it.h) * d.nc + it.c) * Q;
@@ -642,9 +716,11 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 if (live) stg16(po + c0, pack8<T>(o0), pack8<T>(o1), wide_o);
             }
             it.next(d, nrt);
-            if (i + 1 < nt) load_z(it);                          // a whole tile ahead of its use
+            if (i + 1 < nt && !rows) load_z(it);                 // a whole tile ahead of its use
         }
         }
+        if (rows && issuer && lane == 0 && sh.fail && rw.issued)  // leave no load in flight
+            mbar_wait(&sh.r_full, (rw.issued - 1) & 1);
     } else {
         // ------------------------------------------------------------------------------------------ M builders
         const int bt = tid - 32 * kWsFirstBuilder;               // 0 .. 255
@@ -713,7 +789,7 @@ ws_kernel(Dims d, const __grid_constant__ CUtensorMap tmC, const __grid_constant
                 if (!ok) break;
             }
             const float *tb_ = tab + (i & 1) * 6 * Q;
-            ok = ws_build_tile<T>(smCB, smM, tb_, NS, rt * kTileM, bt, lane, dfold, ring, sh.m_full, sh.m_free, fail);
+            ok = ws_build_tile<T, NST>(smCB, smM, tb_, NS, rt * kTileM, bt, lane, dfold, ring, sh.m_full, sh.m_free, fail);
             if (!ok) break;
             if (i + 1 < nt) {
                 write_tab((i + 1) & 1);
