@@ -9,8 +9,9 @@
 //     scans them).
 // One CTA per (batch, chunk, group) and 128 x 128 tile of (l, s), 256 threads, two CTAs per SM: the bf16 C.B^T tile
 // stays in shared memory; for each head g [128 x P] and x [128 x P] arrive by TMA, one tcgen05 chain gives G2 in
-// tensor memory, the warps weight it (factorised row x column factors away from the diagonal, one ex2 per element only
-// in the strips the diagonal crosses), add it to the dCB tile they keep in registers, and write V as bf16 into shared
+// tensor memory, the warps weight it (row x column factors everywhere; in a 16-column strip the diagonal crosses the
+// factors are taken around the strip's own end columns and chosen per element, and only a strip whose decay across its
+// 16 columns would leave fp32's range pays one ex2 per element), add it to the dCB tile they keep in registers, and write V as bf16 into shared
 // memory - over g and x, which are dead once G2 exists; a second chain with a lower-triangular ones matrix,
 // D[m,s] = sum_{l<=m} V[l,s], yields the column totals (row 127) and, in tiles on the diagonal, their split at the
 // diagonal (D[m,m]).  Row sums are taken over the values as rounded for that chain, so that row and column sums
@@ -18,7 +19,8 @@
 // Q-long vectors (forward / reverse part): + column sums at its columns, - row sums at its rows, zero elsewhere;
 // cumsum_bwd adds the vectors of a chunk's tiles.  Tiles off the diagonal hold one direction only and no mixed strip.
 //
-// Tried and measured at the benchmark shape (this form: 175 us; the two separate kernels it replaces: 138 + 66 us):
+// Tried and measured at the benchmark shape (this form: 175 us, 155 us since the strips were dealt alternately and
+// the diagonal strips factorised; the two separate kernels it replaces: 138 + 66 us):
 // a 128 x Q tile per CTA with sixteen warps and the loads of the next head in flight (183 us); the 128 x 128 tile
 // with one CTA per SM and every stage of the chain double-buffered (232 us - the kernel is bound by instruction
 // issue, about twenty instructions per element and head, not by the chain's latencies).
@@ -36,6 +38,7 @@ struct IntraGrpShared {
 };
 
 constexpr int kIntraTileThreads = 256;
+constexpr float kMixedSpan = 60.f;                              // log2 of the largest decay across 16 columns the fast form takes
 inline size_t intra_tile_smem(int Q) { return 1024 + 32768 + 32768 + 32768 + 6 * (size_t)Q * 4; }
 inline bool intra_tile_ok(int P, int Q) { return P == 64 && (Q == 128 || Q == 256); }
 
@@ -198,6 +201,24 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
                         w[j + 1] = t1 * cbv[j + 1];
                         w[j + 2] = t2 * cbv[j + 2];
                         w[j + 3] = t3 * cbv[j + 3];
+                    }
+                } else if (sf[c0] - sf[c0 + 15] <= kMixedSpan && sb[c0 + 15] - sb[c0] <= kMixedSpan) {
+                    // The strip the diagonal crosses, factorised as well: the forward weights around the strip's last
+                    // column, the reverse ones around its first (the column factors of the tables), a row factor each.
+                    // A row inside the strip then has a row factor above one - bounded by the decay across the 16
+                    // columns, which the test above keeps within fp32's range; the side a row does not use may
+                    // overflow and is never selected.
+                    const float rF = row_on ? ex2_approx(fl - sf[c0 + 15]) : 0.f;
+                    const float rB = row_on ? ex2_approx(bl - sb[c0]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int s = c0 + j;
+                        const float wf = colF[s] * rF, wb = colB[s] * rB;
+                        float wt = (s < l) ? wf : wb;
+                        if (s == l) wt = wf + wf;                 // the diagonal counts once per direction in dCB
+                        const float tj = row_on ? v[j] * wt : 0.f;
+                        acc[st * 16 + j] += tj;
+                        w[j] = (s == l) ? 0.f : tj * cbv[j];      // ... and not at all in the decay gradient
                     }
                 } else {
 #pragma unroll

@@ -139,6 +139,21 @@ def test_matches_oracle(name, shape, dtype, kw):
     compare(got, ref, TOL[dtype])
 
 
+def test_strong_decay_both_forms_of_the_diagonal_strips():
+    """Steps of order one: per head the decay across 16 positions runs from about 2^20 to far beyond fp32's range, so
+    the fused dCB / decay-gradient kernel takes its factorised form of the strips on the diagonal for some heads and
+    the per-element form for the others, and the persistent kernels see exponents of several hundred."""
+    b, L, H, P, G, N, Q = 1, 512, 8, 64, 1, 128, 256
+    inp = make_inputs(11, b, L, H, P, G, N, torch.bfloat16, has_z=True, softplus=False, has_bias=False)
+    g = torch.Generator().manual_seed(12)
+    inp["dt"] = torch.rand(b, L, H, generator=g) + 0.5                       # 0.5 .. 1.5, used as given
+    inp["A"] = -torch.tensor([1.0, 1.5, 2.0, 3.0, 4.0, 8.0, 12.0, 16.0])
+    got = run_gpu(inp, Q, False)
+    ref = reference_with_grads(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], Q, inp["dout"], D=inp["D"], z=inp["z"],
+                               dt_bias=None, dt_softplus=False)
+    compare(got, ref, TOL[torch.bfloat16])
+
+
 def test_dense_definition_config1():
     """Config #1 of the benchmark description against the O(L^2) definition (no chunking at all)."""
     b, L, H, P, G, N, Q = 1, 256, 4, 32, 1, 16, 64
