@@ -52,7 +52,7 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
     __shared__ IntraGrpShared sh;
     __shared__ float rsum[2][2][kTileM];                          // [column half][direction][row]
     __shared__ float dg[kTileM];                                  // D[m, m] of a diagonal tile
-    __shared__ float tot[kTileM];                                 // D[127, s]
+    __shared__ __align__(16) float tot[kTileM];                   // D[127, s]
     const int Q = d.Q, R = d.R;
     uint8_t *base_sm = smem_align1024(dyn);
     uint8_t *smCB = base_sm;                                      // two slabs [128 x 64] bf16, K-major
@@ -162,6 +162,11 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
     for (int hr = 0; hr < R; ++hr) {
         ok = mbar_wait_cta(&sh.bar_m1, hr & 1, ok);               // G2 of head hr is in tensor memory
         tc_fence_after();
+        if (hr == 0 && ok && ty == tz && chalf == ((r >> 4) & 1)) {
+            // V has no diagonal: the one thread that reads C.B^T[r, r] (its strip r / 16) clears it in the resident tile
+            *reinterpret_cast<__nv_bfloat16 *>(smCB + (r >> 6) * 16384 + r * 128 + ((((r & 63) >> 3) ^ (r & 7)) << 4) +
+                                               (r & 7) * 2) = __float2bfloat16(0.f);
+        }
         float rf = 0.f, rb = 0.f;
         if (ok) {
             const float *sf = tab, *sb = tab + Q, *tf = tab + 2 * Q, *tb = tab + 3 * Q, *colF = tab + 4 * Q, *colB = tab + 5 * Q;
@@ -216,9 +221,9 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
                         const float wf = colF[s] * rF, wb = colB[s] * rB;
                         float wt = (s < l) ? wf : wb;
                         if (s == l) wt = wf + wf;                 // the diagonal counts once per direction in dCB
-                        const float tj = row_on ? v[j] * wt : 0.f;
+                        const float tj = v[j] * wt;               // rF = rB = 0 for a row past the sequence
                         acc[st * 16 + j] += tj;
-                        w[j] = (s == l) ? 0.f : tj * cbv[j];      // ... and not at all in the decay gradient
+                        w[j] = tj * cbv[j];                       // ... and not at all in the decay gradient: C.B^T's diagonal is zeroed
                     }
                 } else {
 #pragma unroll
@@ -228,7 +233,7 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
                         if (s == l) a += 1.f;                     // the diagonal counts once per direction in dCB
                         const float tj = row_on ? v[j] * ex2_approx(a) : 0.f;
                         acc[st * 16 + j] += tj;
-                        w[j] = (s == l) ? 0.f : tj * cbv[j];      // ... and not at all in the decay gradient
+                        w[j] = tj * cbv[j];                       // ... and not at all in the decay gradient: C.B^T's diagonal is zeroed
                     }
                 }
                 const uint4 q0 = make_uint4(pack2<__nv_bfloat16>(w[0], w[1]), pack2<__nv_bfloat16>(w[2], w[3]),
@@ -290,7 +295,8 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
                     tmem_ld32(tl + 128 + cbeg + c0, v);
                     if (lane == 31) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) tot[cbeg + c0 + j] = v[j];
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4 *>(&tot[cbeg + c0 + j]) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                     }
                 }
             }
