@@ -19,8 +19,8 @@
 // Q-long vectors (forward / reverse part): + column sums at its columns, - row sums at its rows, zero elsewhere;
 // cumsum_bwd adds the vectors of a chunk's tiles.  Tiles off the diagonal hold one direction only and no mixed strip.
 //
-// Tried and measured at the benchmark shape (this form: 175 us, 155 us since the strips were dealt alternately and
-// the diagonal strips factorised; the two separate kernels it replaces: 138 + 66 us):
+// Tried and measured at the benchmark shape (this form: 175 us at first, 140 us since the strips are dealt alternately,
+// the diagonal strips factorised and the per-head read-out trimmed; the two separate kernels it replaces: 138 + 66 us):
 // a 128 x Q tile per CTA with sixteen warps and the loads of the next head in flight (183 us); the 128 x 128 tile
 // with one CTA per SM and every stage of the chain double-buffered (232 us - the kernel is bound by instruction
 // issue, about twenty instructions per element and head, not by the chain's latencies).
