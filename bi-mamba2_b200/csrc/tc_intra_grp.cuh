@@ -266,15 +266,15 @@ intra_dcb_tile(Dims d, const __grid_constant__ CUtensorMap tmG, const __grid_con
         fence_async_smem();
         tc_fence_before();
         ok = __syncthreads_and(ok);                               // V complete, G2 fully read, tables free
-        if (hr + 1 < R) {                                         // single set of tables: the next head's go in here
-            write_tab();
-            if (hr + 2 < R) fetch_tab(hr + 2);
-        }
         if (tid == 0 && ok) {
             tc_fence_after();
             umma_issue_stage<false, true>(tD2, 128, 1, smTri, smV, 0u);
             umma_issue_stage<false, true>(tD2, 128, 1, smTri + 16384, smV + 16384, 1u);
             umma_commit(&sh.bar_m2);
+        }
+        if (hr + 1 < R) {                                         // single set of tables: the next head's go in here,
+            write_tab();                                          // while the triangular product runs
+            if (hr + 2 < R) fetch_tab(hr + 2);
         }
         ok = mbar_wait_cta(&sh.bar_m2, hr & 1, ok);               // column sums done: V (= g, x) may be overwritten
         tc_fence_after();
