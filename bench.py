@@ -165,7 +165,7 @@ def _source_hash(*files):
 # kernel's source file(s) at capture time; when the source has changed since, `traffic` prints as null instead of a
 # stale figure.  {kernel: (bytes per launch at batch 2, source files, hash)}
 NCU_TRAFFIC_B2 = {
-    "tc_intra_dcb_tile": (28.53e6, ("tc_intra_grp.cuh",), "6d998666ace90fcd"),
+    "tc_intra_dcb_tile": (28.53e6, ("tc_intra_grp.cuh",), "4be93440f93a1481"),
     "tc_dx_ws": (42.33e6, ("tc_scan_ws.cuh",), "b0a507b61400027a"),
     "tc_chunk_scan_ws": (43.41e6, ("tc_scan_ws.cuh",), "b0a507b61400027a"),
 }
