@@ -89,14 +89,64 @@ static cudaError_t launch_pdl(void (*kernel)(Exp...), dim3 grid, dim3 block, siz
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
 }
 
-#define BISSD_LAUNCH(name, ...)                                   \
+#define BISSD_LAUNCH_ON(stream, name, ...)                        \
     do {                                                          \
-        TraceScope ts_(name, s);                                  \
+        TraceScope ts_(name, stream);                             \
         __VA_ARGS__;                                              \
         ts_.end();                                                \
         int rc_ = note_cuda(cudaGetLastError(), name);            \
         if (rc_ != BISSD_OK) return rc_;                          \
     } while (0)
+#define BISSD_LAUNCH(name, ...) BISSD_LAUNCH_ON(s, name, __VA_ARGS__)
+
+// A second stream for the two group-walking backward kernels whose results nothing reads before the last product with
+// dCB (prev_terms_grp, dbc_accum_grp): they fork from the caller's stream after the dx kernel and join it again
+// before that product, so that they share the GPU with the fused dCB / decay-gradient kernel, which depends on
+// neither - each of the three leaves a seventh of the SMs idle when it runs alone.  Stream order as the caller sees it is unchanged, also
+// under stream capture (the side stream joins the capture through the event).  A call leases one (stream, two events)
+// set of its device for its duration; sets are created on first need - in practice by the first call on a device, so
+// not inside a later capture.  BISSD_NO_SIDE=1 keeps everything on the caller's stream.
+struct Side {
+    cudaStream_t st = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    int dev = -1;
+    bool busy = false;
+};
+static std::mutex g_side_mu;
+static std::vector<Side *> g_side;
+static Side *side_acquire() {
+    static const bool off = [] { const char *e = getenv("BISSD_NO_SIDE"); return e && e[0] == '1'; }();
+    if (off || g_trace_on.load(std::memory_order_relaxed)) return nullptr;   // traced runs time every kernel alone, in line
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lk(g_side_mu);
+    for (Side *sd : g_side)
+        if (sd->dev == dev && !sd->busy) {
+            sd->busy = true;
+            return sd;
+        }
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e0, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;                                           // no side stream: the launch stays in line
+    }
+    Side *sd = new Side;
+    sd->st = st; sd->fork = e0; sd->join = e1; sd->dev = dev; sd->busy = true;
+    g_side.push_back(sd);
+    return sd;
+}
+struct SideLease {                                                // gives the set back when the call returns
+    Side *sd = nullptr;
+    ~SideLease() {
+        if (sd) {
+            std::lock_guard<std::mutex> lk(g_side_mu);
+            sd->busy = false;
+        }
+    }
+};
 
 // C and B as (dstate, group, seqlen, batch) tensors read in boxes of 64 state columns x 128 rows
 template <class Args> static bool make_cb_maps(const Args &a, const Dims &d, CUtensorMap *mC, CUtensorMap *mB) {
@@ -534,6 +584,8 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
     bool have_fp32_cb = true;                                    // fp32 CB (and its transpose) are in the workspace
     bool use_u4 = false;                                         // decay gradients arrive as u_f / u_b (tc::intra_sums)
     bool fused_cb = false;                                       // the bf16 C.B^T tile for tc::intra_dcb_tile has been written
+    SideLease lease;
+    cudaStream_t s_side = s;                                     // where prev_terms_grp and dbc_accum_grp are launched
     int u4_tiles = 2;                                            // (u_f, u_b) vector pairs per chunk in u4
     int dd_slots = 0;                                            // dD partial rows per (b,c,h) when not nlt
     bool dd_compact = false;                                     // per-head D from the persistent dx kernel: dd_slots scalars, no channel axis
@@ -612,6 +664,13 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     else BISSD_DX_WS(1, 2);
 #undef BISSD_DX_WS
                     dx_done = true;
+                    if (fused_cb && (lease.sd = side_acquire()) != nullptr) {      // the two group-walking kernels branch off here
+                        if (cudaEventRecord(lease.sd->fork, s) == cudaSuccess && cudaStreamWaitEvent(lease.sd->st, lease.sd->fork, 0) == cudaSuccess) {
+                            s_side = lease.sd->st;
+                        } else {
+                            cudaGetLastError();
+                        }
+                    }
                     dd_slots = nlt_tc * 4;
                     if (d.has_D && !d.D_hdim) {
                         dd_slots = nlt_tc * 8;                       // one scalar per epilogue warp and tile
@@ -677,7 +736,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                         const size_t smem_g = tc::prev_grp_smem(d.N, d.Q);
                         const int ks = tc::state_grp_ksplit(d.b * d.nc * d.G, d.R, sm_count());
                         BISSD_ALLOW(tc::prev_terms_grp<T>, smem_g);
-                        BISSD_LAUNCH("tc_prev_terms_grp", launch_pdl(tc::prev_terms_grp<T>, dim3(d.b * d.nc * d.G * ks), tc::kPrevGrpThreads, smem_g, s, 
+                        BISSD_LAUNCH_ON(s_side, "tc_prev_terms_grp", launch_pdl(tc::prev_terms_grp<T>, dim3(d.b * d.nc * d.G * ks), tc::kPrevGrpThreads, smem_g, s_side, 
                             d, mC, mSf, mSb, mG128, ks, a.cs_f, a.cs_b, F(w.pf), F(w.pb), status));
                     } else {
                         BISSD_ALLOW(tc::prev_terms_tma<T>, smem_p);
@@ -688,7 +747,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     if (!no_ws() && tc::dbc_grp_ok(d.P, d.N, d.Q)) {
                         const size_t smem_g = tc::dbc_grp_smem(d.Q, std::min(d.N, 128));
                         BISSD_ALLOW(tc::dbc_accum_grp<T>, smem_g);
-                        BISSD_LAUNCH("tc_dbc_accum_grp", launch_pdl(tc::dbc_accum_grp<T>, dim3(d.b * d.nc * d.G * w.nsplit, 1, 2), tc::kDbcGrpThreads, smem_g, s, 
+                        BISSD_LAUNCH_ON(s_side, "tc_dbc_accum_grp", launch_pdl(tc::dbc_accum_grp<T>, dim3(d.b * d.nc * d.G * w.nsplit, 1, 2), tc::kDbcGrpThreads, smem_g, s_side, 
                             d, mEf, mEb, mSf, mSb, mX128, mG128, a.dt_out, a.cs_f, a.cs_b, F(w.dB_part), F(w.dC_part), status));
                     } else
                     BISSD_LAUNCH("tc_dbc_accum_tma", tc::dbc_accum_tma<T><<<dim3(d.b * d.nc * d.G * w.nsplit, nlt_tc, 2), tc::kThreads, smem_a, s>>>(
@@ -824,6 +883,12 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
         BISSD_ALLOW(simt::intra_decay_grad<T>, smem);
         BISSD_LAUNCH("intra_decay_grad", simt::intra_decay_grad<T><<<bch, simt::TB, smem, s>>>(
             d, x, z, dout, a.dt_out, a.cs_f, a.cs_b, F(w.cb), F(w.da_f), F(w.da_b)));
+    }
+    if (s_side != s) {                                           // the group-walking kernels rejoin before their results are read
+        int rcj = note_cuda(cudaEventRecord(lease.sd->join, s_side), "cudaEventRecord");
+        if (rcj == BISSD_OK) rcj = note_cuda(cudaStreamWaitEvent(s, lease.sd->join, 0), "cudaStreamWaitEvent");
+        if (rcj != BISSD_OK) return rcj;
+        s_side = s;
     }
     bool bmm_tc = false;
     if constexpr (TcKernels<T>::available) {
