@@ -941,6 +941,22 @@ __global__ void __launch_bounds__(256) cumsum_bwd(Dims d, const void *dt, int dt
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Sum of v over the block in a fixed order (lanes by butterfly, then the warps' totals by the first warp's butterfly),
+// returned to every thread of warp 0; `red` needs NT / 32 entries beyond any the caller still reads.  Two barriers.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    v = warp_sum(v);
+    __syncthreads();                                             // earlier readers of red are done
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    if (threadIdx.x < 32) {
+        t = (threadIdx.x < NT / 32) ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+    }
+    return t;
+}
+
 // Fixed-order reduction of the per-block partials into dA (H), ddt_bias (H) and dD (H or H*P).  grid (H), NT threads.
 // `compact` (per-head D only): dDpart holds nlt scalars per (batch, chunk, head) instead of nlt rows of P channel sums.
 template <int NT>
@@ -956,36 +972,19 @@ __global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, 
         sa += dApart[(long long)i * d.H + h];
         sbias += dbiaspart[(long long)i * d.H + h];
     }
-    red[threadIdx.x] = sa;
-    __syncthreads();
-    for (int o = NT / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) dA[h] = red[0];
-    __syncthreads();
-    red[threadIdx.x] = sbias;
-    __syncthreads();
-    for (int o = NT / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = red[0];
-    __syncthreads();
+    sa = block_sum<NT>(sa, red);
+    if (threadIdx.x == 0) dA[h] = sa;
+    sbias = block_sum<NT>(sbias, red);
+    if (threadIdx.x == 0 && ddt_bias) ddt_bias[h] = sbias;
     if (dD && dDpart && compact) {
-        float sd = 0.f;                                          // fixed order: strided per thread, then the tree below
+        float sd = 0.f;                                          // fixed order: strided per thread, then block_sum
         const int n = nbc * nlt;
         for (int i = threadIdx.x; i < n; i += NT) {
             const int bc = i / nlt, t = i - bc * nlt;
             sd += dDpart[((long long)bc * d.H + h) * nlt + t];
         }
-        red[threadIdx.x] = sd;
-        __syncthreads();
-        for (int o = NT / 2; o > 0; o >>= 1) {
-            if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-            __syncthreads();
-        }
-        if (threadIdx.x == 0) dD[h] = red[0];
+        sd = block_sum<NT>(sd, red);
+        if (threadIdx.x == 0) dD[h] = sd;
     } else if (dD && dDpart) {
         // rows of the partial buffer are split over NT / P thread groups, then the groups are added in a fixed order
         const int rows = nbc * nlt;
@@ -1023,13 +1022,8 @@ __global__ void __launch_bounds__(NT) final_reduce(Dims d, const float *dApart, 
         }
         if (!d.D_hdim) {
             __syncthreads();
-            red[threadIdx.x] = tot;
-            __syncthreads();
-            for (int o = NT / 2; o > 0; o >>= 1) {
-                if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-                __syncthreads();
-            }
-            if (threadIdx.x == 0) dD[h] = red[0];
+            tot = block_sum<NT>(tot, red);
+            if (threadIdx.x == 0) dD[h] = tot;
         }
     }
 }
