@@ -308,6 +308,23 @@ def test_two_head_problem_eight_seeds_thread_staged_family():
     assert not res["failures"], res["failures"]
 
 
+def test_two_head_problem_without_the_second_stream():
+    """The backward pass with every launch on the caller's stream (BISSD_NO_SIDE=1, read once per process: a child
+    process) meets the same bounds with the same kernels as the default, which runs two of them on a second stream."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import two_head_worker
+    env = dict(os.environ, BISSD_NO_SIDE="1")
+    p = subprocess.run([sys.executable, two_head_worker.__file__], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("TWO_HEAD_RESULT ")][-1]
+    res = json.loads(line[len("TWO_HEAD_RESULT "):])
+    assert "tc_intra_dcb_tile" in res["family"] and "tc_dbc_accum_grp" in res["family"], res["family"]
+    assert not res["failures"], res["failures"]
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # (b3) the benchmark configurations at their true sequence length / heads / head and state sizes, one batch row
 # ---------------------------------------------------------------------------------------------------------------
