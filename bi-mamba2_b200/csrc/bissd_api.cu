@@ -114,7 +114,7 @@ struct Side {
 };
 static std::mutex g_side_mu;
 static std::vector<Side *> g_side;
-static Side *side_acquire() {
+static Side *side_acquire(cudaStream_t s) {
     static const bool off = [] { const char *e = getenv("BISSD_NO_SIDE"); return e && e[0] == '1'; }();
     if (off || g_trace_on.load(std::memory_order_relaxed)) return nullptr;   // traced runs time every kernel alone, in line
     int dev = 0;
@@ -125,6 +125,12 @@ static Side *side_acquire() {
             sd->busy = true;
             return sd;
         }
+    // nothing free: make a set - but not while the caller's stream is being captured (creation belongs outside a capture)
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
@@ -664,7 +670,7 @@ static int backward_impl(const bissd_bwd_args &a, const Dims &d, char *ws, cudaS
                     else BISSD_DX_WS(1, 2);
 #undef BISSD_DX_WS
                     dx_done = true;
-                    if (fused_cb && (lease.sd = side_acquire()) != nullptr) {      // the two group-walking kernels branch off here
+                    if (fused_cb && (lease.sd = side_acquire(s)) != nullptr) {      // the two group-walking kernels branch off here
                         if (cudaEventRecord(lease.sd->fork, s) == cudaSuccess && cudaStreamWaitEvent(lease.sd->st, lease.sd->fork, 0) == cudaSuccess) {
                             s_side = lease.sd->st;
                         } else {

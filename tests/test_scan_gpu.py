@@ -325,6 +325,20 @@ def test_two_head_problem_without_the_second_stream():
     assert not res["failures"], res["failures"]
 
 
+def test_first_call_inside_a_graph_capture():
+    """A process whose first forward + backward happens inside a CUDA graph capture: the library creates no stream
+    there, the captured step replays correctly and equals, bit for bit, a later eager step (which runs two backward
+    kernels on the library's second stream)."""
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "capture_first_worker.py")
+    env = {k: v for k, v in os.environ.items() if k != "BISSD_CHECK_STATUS"}   # reading the status word synchronises
+    p = subprocess.run([sys.executable, worker], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert "CAPTURE_FIRST_CALL bit-equal" in p.stdout, p.stdout[-2000:]
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # (b3) the benchmark configurations at their true sequence length / heads / head and state sizes, one batch row
 # ---------------------------------------------------------------------------------------------------------------
