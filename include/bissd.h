@@ -15,8 +15,8 @@
  *     to void*; NULL = the legacy default stream): whatever the caller enqueues on it afterwards sees the call's
  *     results.  bissd_backward may run two of its kernels on a stream of the library's own beside a third one; they
  *     leave the caller's stream after its earlier work and rejoin it through events before the call returns, also
- *     inside a stream capture (the first call on a device creates that stream and two events - make it outside a
- *     capture; BISSD_NO_SIDE=1 in the environment keeps every launch on the caller's stream).
+ *     inside a stream capture (that stream and its two events are created by the first uncaptured call on a device;
+ *     until then, and with BISSD_NO_SIDE=1 in the environment, every launch stays on the caller's stream).
  *   - every function returns BISSD_OK (0) or a negative bissd_status; no C++ exception crosses the boundary.
  *   - tensors named like the reference's: x (batch, seqlen, nheads, headdim), dt (batch, seqlen, nheads),
  *     A (nheads), B and C (batch, seqlen, ngroups, dstate), D (nheads) or (nheads, headdim),
